@@ -1,0 +1,622 @@
+// Window + pivot attention with per-key softmax column sums (H2O scores), head_dim 64, bf16.
+//
+// Replaces the reference's attn_cuda.flash_attn_bias_colsum (attn-cuda/csrc/launch.cu:87-158,
+// kernels fwd_kernel.h:78-485 and colsum_kernel.h:22-325) and its Triton twin
+// (stac/flash_attn_triton.py:900-1006).  Semantics: S = q k^T * scale + bias[n], softmax over
+// the keys, O = P v, lse = logsumexp, colsum[n] = sum over (optionally strided) query rows of
+// exp(S - lse) times M / M_sub.  Keys come from two segments that are never concatenated in
+// memory: the hot cache rows [0, T_hot) of a head and the retrieved pivots [0, T_ret) with a
+// per-key bias (log C, or -inf for padding).
+//
+// Two kernels, both tcgen05 + TMA:
+//   attn_fwd_kernel     one CTA per (128 query rows, head): S = Q K^T into TMEM, online softmax
+//                       by two warpgroups that take alternate key tiles (each with its own
+//                       running max/sum/accumulator, merged at the end), P staged in shared
+//                       memory as bf16, O_tile = P V into TMEM and folded into registers.
+//   attn_colsum_kernel  one CTA per (128 keys, head): S^T = K Q^T into TMEM so that each thread
+//                       owns one key (TMEM lane) and sums exp2(S^T - lse[m]) over the query
+//                       columns in registers: no shuffles, no atomics, deterministic.
+#include "common.cuh"
+#include "stac_internal.h"
+
+namespace stac {
+
+namespace {
+
+constexpr int kD = 64;
+constexpr int kBM = 128;
+constexpr int kBN = 128;
+constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 bf16
+constexpr int kFwdStages = 4;
+constexpr int kFwdThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9 two softmax warpgroups
+constexpr int kColStages = 4;
+constexpr int kColThreads = 320;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct FwdSmem {
+  uint8_t q[kTileBytes];
+  uint8_t k[kFwdStages][kTileBytes];
+  uint8_t v[kFwdStages][kTileBytes];
+  uint8_t p[2][2 * kTileBytes];  // per warpgroup: 128 rows x 128 keys bf16 as two 64-key atoms
+  float bias2[2][kBN];
+  float xm[kBM];
+  float xl[kBM];
+  uint64_t bar_q;
+  uint64_t kv_full[kFwdStages];
+  uint64_t kv_empty[kFwdStages];
+  uint64_t s_full[2];
+  uint64_t s_free[2];
+  uint64_t p_full[2];
+  uint64_t o_full[2];
+  uint64_t o_free[2];
+  uint32_t tmem_base;
+};
+
+struct FwdParams {
+  int M, H;
+  int T_hot, T_ret;
+  int n_hot_tiles, n_ret_tiles;
+  float scale_log2;
+  const float* bias_ret;
+  long long bias_head_stride;
+  __nv_bfloat16* out;
+  long long out_row_stride;  // elements between query rows
+  float* lse;                // [H, M] natural log or nullptr
+  float* lse2;               // [H, lse2_stride] log2 domain
+  long long lse2_stride;
+  int* err;
+};
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
+                const __grid_constant__ CUtensorMap tm_v_hot, const __grid_constant__ CUtensorMap tm_k_ret,
+                const __grid_constant__ CUtensorMap tm_v_ret, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  FwdSmem& sm = *reinterpret_cast<FwdSmem*>(align1024(smem_raw));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x;
+  const int h = blockIdx.y;
+  const int n_hot = p.n_hot_tiles;
+  const int n_tiles = p.n_hot_tiles + p.n_ret_tiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.bar_q, 1);
+    for (int s = 0; s < kFwdStages; ++s) {
+      mbar_init(&sm.kv_full[s], 1);
+      mbar_init(&sm.kv_empty[s], 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&sm.s_full[g], 1);
+      mbar_init(&sm.s_free[g], 128);
+      mbar_init(&sm.p_full[g], 128);
+      mbar_init(&sm.o_full[g], 1);
+      mbar_init(&sm.o_free[g], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k_hot);
+      tma_prefetch_desc(&tm_v_hot);
+      mbar_arrive_expect_tx(&sm.bar_q, kTileBytes);
+      tma_load_3d(sm.q, &tm_q, &sm.bar_q, 0, h, m_tile * kBM);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % kFwdStages;
+        const int round = j / kFwdStages;
+        if (round > 0) mbar_wait(&sm.kv_empty[s], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_arrive_expect_tx(&sm.kv_full[s], 2 * kTileBytes);
+        if (j < n_hot) {
+          tma_load_3d(sm.k[s], &tm_k_hot, &sm.kv_full[s], 0, j * kBN, h);
+          tma_load_3d(sm.v[s], &tm_v_hot, &sm.kv_full[s], 0, j * kBN, h);
+        } else {
+          tma_load_3d(sm.k[s], &tm_k_ret, &sm.kv_full[s], 0, (j - n_hot) * kBN, h);
+          tma_load_3d(sm.v[s], &tm_v_ret, &sm.kv_full[s], 0, (j - n_hot) * kBN, h);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBM, kBN, 0);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(kBM, kD, 1);
+      mbar_wait(&sm.bar_q, 0, p.err, DEV_TIMEOUT_TMA);
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q));
+      auto issue_s = [&](int j) {
+        const int g = j & 1, it = j >> 1, s = j % kFwdStages;
+        mbar_wait(&sm.kv_full[s], (j / kFwdStages) & 1, p.err, DEV_TIMEOUT_TMA);
+        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+        const uint64_t k_desc = smem_desc_sw128(smem_u32(sm.k[s]));
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk)
+          umma_ss(tmem + g * kBN, q_desc + 2 * kk, k_desc + 2 * kk, idesc_s, kk > 0);
+        umma_commit(&sm.s_full[g]);
+      };
+      auto issue_pv = [&](int j) {
+        const int g = j & 1, it = j >> 1, s = j % kFwdStages;
+        mbar_wait(&sm.p_full[g], it & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        if (it > 0) mbar_wait(&sm.o_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          const uint64_t a = smem_desc_sw128(smem_u32(sm.p[g]) + (kk >> 2) * kTileBytes) + 2 * (kk & 3);
+          const uint64_t b = smem_desc_sw128(smem_u32(sm.v[s]) + kk * 2048);
+          umma_ss(tmem + 2 * kBN + g * kD, a, b, idesc_o, kk > 0);
+        }
+        umma_commit(&sm.o_full[g]);
+        umma_commit(&sm.kv_empty[s]);
+      };
+      if (n_tiles > 0) issue_s(0);
+      for (int j = 0; j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) issue_s(j + 1);
+        issue_pv(j);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int g = (warp - 2) >> 2;
+    const int wq = warp & 3;                 // TMEM lane quarter this warp may touch
+    const int row = wq * 32 + lane;          // query row inside the tile
+    const int t = ((warp - 2) & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float c2 = p.scale_log2;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    float acc[kD];
+#pragma unroll
+    for (int i = 0; i < kD; ++i) acc[i] = 0.f;
+    uint32_t r[32];
+    int it = 0;
+    for (int j = g; j < n_tiles; j += 2, ++it) {
+      const bool is_ret = j >= n_hot;
+      const int n0 = (is_ret ? j - n_hot : j) * kBN;
+      const int valid = min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0);
+      const bool need_bias = is_ret || valid < kBN;
+      if (need_bias) {
+        named_bar_sync(1 + g, 128);
+        float b = -INFINITY;
+        if (t < valid) b = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + t] * kLog2e : 0.f;
+        sm.bias2[g][t] = b;
+        named_bar_sync(1 + g, 128);
+      }
+      mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      // pass 1 over the S tile: row maximum in the log2 domain
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(tmem + lane_base + g * kBN + c * 32, r);
+        tmem_ld_wait();
+        if (need_bias) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(r[i]), c2, sm.bias2[g][c * 32 + i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * c2);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = fast_exp2(m_run - m_use);
+      // fold the previous P V tile of this warpgroup into the register accumulator
+      if (it > 0) {
+        mbar_wait(&sm.o_full[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld32(tmem + lane_base + 2 * kBN + g * kD + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
+        }
+        tc_fence_before();
+        mbar_arrive(&sm.o_free[g]);
+      }
+      // pass 2: probabilities relative to the new maximum, bf16 into shared memory
+      float rs = 0.f;
+      uint8_t* prow = sm.p[g] + row * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(tmem + lane_base + g * kBN + c * 32, r);
+        tmem_ld_wait();
+        float pv[32];
+        if (need_bias) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), c2, sm.bias2[g][c * 32 + i]) - m_use);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), c2, -m_use));
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) rs += pv[i];
+        // keys c*32 .. c*32+31 -> atom c/2, 16-byte chunks (c&1)*4 .. +3 of this row
+        uint8_t* atom = prow + (c >> 1) * kTileBytes;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c & 1) * 4 + q4;
+          uint4 val;
+          val.x = pack_bf16x2(pv[q4 * 8 + 0], pv[q4 * 8 + 1]);
+          val.y = pack_bf16x2(pv[q4 * 8 + 2], pv[q4 * 8 + 3]);
+          val.z = pack_bf16x2(pv[q4 * 8 + 4], pv[q4 * 8 + 5]);
+          val.w = pack_bf16x2(pv[q4 * 8 + 6], pv[q4 * 8 + 7]);
+          *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = val;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&sm.s_free[g]);
+      l_run = fmaf(l_run, alpha, rs);
+      m_run = m_new;
+      alpha_prev = alpha;
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.p_full[g]);
+    }
+    if (it > 0) {
+      mbar_wait(&sm.o_full[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld32(tmem + lane_base + 2 * kBN + g * kD + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
+      }
+      tc_fence_before();
+    }
+    // merge the two warpgroups' partial softmax states (warpgroup 1 -> shared -> warpgroup 0)
+    float* xacc = reinterpret_cast<float*>(sm.p[1]);  // [64][128] floats = 32 KB, P[1] is idle now
+    if (g == 1) {
+#pragma unroll
+      for (int i = 0; i < kD; ++i) xacc[i * kBM + row] = acc[i];
+      sm.xm[row] = m_run;
+      sm.xl[row] = l_run;
+    }
+    named_bar_sync(3, 256);
+    if (g == 0) {
+      const float m1 = sm.xm[row], l1 = sm.xl[row];
+      const float m = fmaxf(m_run, m1);
+      const float m_use = (m == -INFINITY) ? 0.f : m;
+      const float e0 = fast_exp2(m_run - m_use), e1 = fast_exp2(m1 - m_use);
+      const float l = l_run * e0 + l1 * e1;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int mrow = m_tile * kBM + row;
+      if (mrow < p.M) {
+        __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
+#pragma unroll
+        for (int q8 = 0; q8 < kD / 8; ++q8) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = (acc[q8 * 8 + i] * e0 + xacc[(q8 * 8 + i) * kBM + row] * e1) * inv;
+          uint4 val;
+          val.x = pack_bf16x2(o[0], o[1]);
+          val.y = pack_bf16x2(o[2], o[3]);
+          val.z = pack_bf16x2(o[4], o[5]);
+          val.w = pack_bf16x2(o[6], o[7]);
+          *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
+        }
+        const float l2 = m_use + log2f(l);
+        if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
+        p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Column sums.  lse2 holds the row log-sum-exp in the log2 domain for the rows actually
+// used (already gathered when rows are sub-sampled); entries past M_sub are +inf so padded
+// query columns contribute exp2(-inf) = 0.
+// ---------------------------------------------------------------------------------------
+struct ColSmem {
+  uint8_t k[kTileBytes];
+  uint8_t q[kColStages][kTileBytes];
+  float xsum[kBN];
+  uint64_t bar_k;
+  uint64_t q_full[kColStages];
+  uint64_t q_empty[kColStages];
+  uint64_t s_full[2];
+  uint64_t s_free[2];
+  uint32_t tmem_base;
+  alignas(16) float lse2[4];  // flexible: n_q_tiles * 128 floats follow
+};
+
+struct ColParams {
+  int M_sub, H;
+  int row_stride;  // query row sub-sampling stride
+  int T_hot, T_ret;
+  int n_hot_tiles;
+  int n_q_tiles;
+  float scale_log2;
+  float correction;
+  const float* bias_ret;
+  long long bias_head_stride;
+  const float* lse2;
+  long long lse2_stride;
+  float* colsum;  // [H, colsum_stride], hot keys first then retrieved
+  long long colsum_stride;
+  int* err;
+};
+
+__global__ void __launch_bounds__(kColThreads, 1)
+attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
+                   const __grid_constant__ CUtensorMap tm_k_ret, const ColParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  ColSmem& sm = *reinterpret_cast<ColSmem*>(align1024(smem_raw));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int j = blockIdx.x;  // key tile over [hot | retrieved]
+  const int h = blockIdx.y;
+  const bool is_ret = j >= p.n_hot_tiles;
+  const int n0 = (is_ret ? j - p.n_hot_tiles : j) * kBN;
+  const int valid = min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0);
+  const int nq = p.n_q_tiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.bar_k, 1);
+    for (int s = 0; s < kColStages; ++s) {
+      mbar_init(&sm.q_full[s], 1);
+      mbar_init(&sm.q_empty[s], 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&sm.s_full[g], 1);
+      mbar_init(&sm.s_free[g], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 256);
+    tmem_relinquish();
+  }
+  // stage the row log-sum-exps of this head (all threads)
+  for (int i = threadIdx.x; i < nq * kBM; i += kColThreads) {
+    float v = INFINITY;
+    if (i < p.M_sub) v = p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(i) * p.row_stride];
+    sm.lse2[i] = v;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      mbar_arrive_expect_tx(&sm.bar_k, kTileBytes);
+      tma_load_3d(sm.k, is_ret ? &tm_k_ret : &tm_k_hot, &sm.bar_k, 0, n0, h);
+      for (int i = 0; i < nq; ++i) {
+        const int s = i % kColStages, round = i / kColStages;
+        if (round > 0) mbar_wait(&sm.q_empty[s], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
+        tma_load_3d(sm.q[s], &tm_q, &sm.q_full[s], 0, h, i * kBM);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(kBN, kBM, 0);
+      mbar_wait(&sm.bar_k, 0, p.err, DEV_TIMEOUT_TMA);
+      const uint64_t k_desc = smem_desc_sw128(smem_u32(sm.k));
+      for (int i = 0; i < nq; ++i) {
+        const int g = i & 1, it = i >> 1, s = i % kColStages;
+        mbar_wait(&sm.q_full[s], (i / kColStages) & 1, p.err, DEV_TIMEOUT_TMA);
+        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+        const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q[s]));
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk)
+          umma_ss(tmem + g * kBM, k_desc + 2 * kk, q_desc + 2 * kk, idesc, kk > 0);
+        umma_commit(&sm.s_full[g]);
+        umma_commit(&sm.q_empty[s]);
+      }
+    }
+  } else {
+    const int g = (warp - 2) >> 2;
+    const int wq = warp & 3;
+    const int key = wq * 32 + lane;  // key inside the tile = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float c2 = p.scale_log2;
+    float b2 = -INFINITY;
+    if (key < valid) b2 = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e : 0.f;
+    float csum = 0.f;
+    uint32_t r[32];
+    int it = 0;
+    for (int i = g; i < nq; i += 2, ++it) {
+      mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      const float4* l4 = reinterpret_cast<const float4*>(&sm.lse2[i * kBM]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(tmem + lane_base + g * kBM + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          const float4 l = l4[c * 8 + q4];
+          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 0]), c2, b2 - l.x));
+          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 1]), c2, b2 - l.y));
+          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 2]), c2, b2 - l.z));
+          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 3]), c2, b2 - l.w));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&sm.s_free[g]);
+    }
+    if (g == 1) sm.xsum[key] = csum;
+    named_bar_sync(3, 256);
+    if (g == 0 && key < valid) {
+      const float total = (csum + sm.xsum[key]) * p.correction;
+      p.colsum[static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key] = total;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 tensor seen as [d2][d1][64]; box = 64 x box1 x box2 elements, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+             uint64_t stride2_bytes, uint32_t box1, uint32_t box2) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return STAC_ERR_CUDA;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(kD), d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kD), box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? STAC_OK : STAC_ERR_CUDA;
+}
+
+}  // namespace
+
+void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* correction) {
+  // attn-cuda/csrc/bindings.cpp:63-83
+  if (ratio >= 0.999999f) {
+    *m_sub = M; *stride = 1; *correction = 1.f;
+    return;
+  }
+  int ms = static_cast<int>(M * ratio);
+  if (ms < 128) ms = 128;
+  ms = (ms / 128) * 128;
+  if (ms >= M) {
+    *m_sub = M; *stride = 1; *correction = 1.f;
+  } else {
+    *m_sub = ms;
+    *stride = M / ms < 1 ? 1 : M / ms;
+    *correction = static_cast<float>(M) / static_cast<float>(ms);
+  }
+}
+
+size_t attn_lse2_elems(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M); }
+
+int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t stream) {
+  if (a.D != kD) return STAC_ERR_BAD_ARG;
+  if (a.M <= 0 || a.H <= 0 || a.T_hot < 0 || a.T_ret < 0 || a.T_hot + a.T_ret <= 0) return STAC_ERR_BAD_ARG;
+  if (a.T_ret > 0 && (a.k_ret == nullptr || a.v_ret == nullptr || a.bias_ret == nullptr)) return STAC_ERR_BAD_ARG;
+  if (a.T_hot > 0 && (a.k_hot == nullptr || a.v_hot == nullptr)) return STAC_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k_hot) | reinterpret_cast<uintptr_t>(a.v_hot) |
+       reinterpret_cast<uintptr_t>(a.k_ret) | reinterpret_cast<uintptr_t>(a.v_ret) |
+       reinterpret_cast<uintptr_t>(a.out)) & 15)
+    return STAC_ERR_BAD_ARG;
+
+  static bool attr_done = false;
+  const int fwd_smem = static_cast<int>(sizeof(FwdSmem)) + 1024;
+  int m_sub, stride;
+  float corr;
+  attn_subsample_plan(a.M, a.subsample_ratio, &m_sub, &stride, &corr);
+  const int nq = (m_sub + kBM - 1) / kBM;
+  const int col_smem = static_cast<int>(sizeof(ColSmem)) + nq * kBM * 4 + 1024;
+  if (col_smem > 227 * 1024) return STAC_ERR_BAD_ARG;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem) != cudaSuccess)
+      return STAC_ERR_CUDA;
+    if (cudaFuncSetAttribute(attn_colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+        cudaSuccess)
+      return STAC_ERR_CUDA;
+    attr_done = true;
+  }
+
+  const uint64_t eb = 2;  // bytes per element
+  CUtensorMap tm_q, tm_qs, tm_kh, tm_vh, tm_kr, tm_vr;
+  int rc;
+  // q[m, h, :]: dims {64, H, M}
+  rc = make_map(&tm_q, a.q, a.H, a.M, kD * eb, a.q_row_stride * eb, 1, kBM);
+  if (rc) return rc;
+  rc = make_map(&tm_qs, a.q, a.H, m_sub, kD * eb, a.q_row_stride * eb * stride, 1, kBM);
+  if (rc) return rc;
+  // placeholders keep the maps valid when a segment is empty
+  const void* kh = a.T_hot > 0 ? a.k_hot : a.k_ret;
+  const void* vh = a.T_hot > 0 ? a.v_hot : a.v_ret;
+  const int th = a.T_hot > 0 ? a.T_hot : a.T_ret;
+  const long long sh = a.T_hot > 0 ? a.hot_head_stride : a.ret_head_stride;
+  const long long rh = a.T_hot > 0 ? a.hot_row_stride : a.ret_row_stride;
+  const void* kr = a.T_ret > 0 ? a.k_ret : a.k_hot;
+  const void* vr = a.T_ret > 0 ? a.v_ret : a.v_hot;
+  const int tr = a.T_ret > 0 ? a.T_ret : a.T_hot;
+  const long long sr = a.T_ret > 0 ? a.ret_head_stride : a.hot_head_stride;
+  const long long rr = a.T_ret > 0 ? a.ret_row_stride : a.hot_row_stride;
+  rc = make_map(&tm_kh, kh, th, a.H, rh * eb, sh * eb, kBN, 1);
+  if (rc) return rc;
+  rc = make_map(&tm_vh, vh, th, a.H, rh * eb, sh * eb, kBN, 1);
+  if (rc) return rc;
+  rc = make_map(&tm_kr, kr, tr, a.H, rr * eb, sr * eb, kBN, 1);
+  if (rc) return rc;
+  rc = make_map(&tm_vr, vr, tr, a.H, rr * eb, sr * eb, kBN, 1);
+  if (rc) return rc;
+
+  const float scale_log2 = a.scale * kLog2e;
+  FwdParams fp;
+  fp.M = a.M; fp.H = a.H; fp.T_hot = a.T_hot; fp.T_ret = a.T_ret;
+  fp.n_hot_tiles = (a.T_hot + kBN - 1) / kBN;
+  fp.n_ret_tiles = (a.T_ret + kBN - 1) / kBN;
+  fp.scale_log2 = scale_log2;
+  fp.bias_ret = a.bias_ret; fp.bias_head_stride = a.bias_head_stride;
+  fp.out = static_cast<__nv_bfloat16*>(a.out); fp.out_row_stride = a.out_row_stride;
+  fp.lse = a.lse; fp.lse2 = lse2; fp.lse2_stride = a.M;
+  fp.err = err;
+  dim3 grid_f((a.M + kBM - 1) / kBM, a.H);
+  attn_fwd_kernel<<<grid_f, kFwdThreads, fwd_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
+  if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
+
+  if (a.colsum != nullptr) {
+    ColParams cp;
+    cp.M_sub = m_sub; cp.H = a.H; cp.row_stride = stride;
+    cp.T_hot = a.T_hot; cp.T_ret = a.T_ret;
+    cp.n_hot_tiles = fp.n_hot_tiles; cp.n_q_tiles = nq;
+    cp.scale_log2 = scale_log2; cp.correction = corr;
+    cp.bias_ret = a.bias_ret; cp.bias_head_stride = a.bias_head_stride;
+    cp.lse2 = lse2; cp.lse2_stride = a.M;
+    cp.colsum = a.colsum; cp.colsum_stride = a.colsum_head_stride;
+    cp.err = err;
+    dim3 grid_c(fp.n_hot_tiles + fp.n_ret_tiles, a.H);
+    attn_colsum_kernel<<<grid_c, kColThreads, col_smem, stream>>>(tm_qs, tm_kh, tm_kr, cp);
+    if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
+  }
+  return STAC_OK;
+}
+
+}  // namespace stac

@@ -1,0 +1,41 @@
+// Internal declarations shared by the translation units of libstac_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/stac_b200.h"
+
+namespace stac {
+
+struct AttnArgs {
+  const void* q;            // bf16 [M, H, 64] with row stride q_row_stride elements
+  long long q_row_stride;
+  const void* k_hot;        // bf16; key n, head h at n*hot_row_stride + h*hot_head_stride
+  const void* v_hot;
+  long long hot_row_stride;
+  long long hot_head_stride;
+  int T_hot;
+  const void* k_ret;        // bf16 [H, >=T_ret, 64]
+  const void* v_ret;
+  long long ret_row_stride;
+  long long ret_head_stride;
+  int T_ret;
+  const float* bias_ret;    // [H, >=T_ret]
+  long long bias_head_stride;
+  void* out;                // bf16, same layout as q
+  long long out_row_stride;
+  float* lse;               // [H, M] or nullptr
+  float* colsum;            // [H, colsum_head_stride] or nullptr
+  long long colsum_head_stride;
+  int M, H, D;
+  float scale;
+  float subsample_ratio;
+};
+
+void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* correction);
+size_t attn_lse2_elems(int M, int H);
+int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t stream);
+
+}  // namespace stac

@@ -1,0 +1,109 @@
+"""Parity of the tcgen05 column-sum attention against the fp32 oracle, through the C ABI.
+Tolerances: output 2e-2 absolute (bf16), column sums and lse 1e-3 relative (fp32)."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle.attention import attn_colsum as oracle_attn
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(x):
+    return torch.from_numpy(x).to(torch.bfloat16)
+
+
+def _run_two_segment(M, H, T_hot, T_ret, seed, T_buf=None, subsample=1.0, spread=1.0):
+    from stac_b200 import ops
+    rs = np.random.RandomState(seed)
+    D = 64
+    T_buf = T_buf or (T_hot + 37)
+    q = _bf16(rs.randn(M, H, D).astype(np.float32) * spread)
+    kh = _bf16(rs.randn(H, T_buf, D).astype(np.float32) * spread)
+    vh = _bf16(rs.randn(H, T_buf, D).astype(np.float32))
+    kr = _bf16(rs.randn(H, max(T_ret, 1), D).astype(np.float32) * spread)
+    vr = _bf16(rs.randn(H, max(T_ret, 1), D).astype(np.float32))
+    bias = np.log(rs.randint(1, 9, size=(H, max(T_ret, 1))).astype(np.float32))
+    bias[rs.rand(H, max(T_ret, 1)) < 0.25] = -np.inf
+    dev = torch.device("cuda:0")
+    status = ops.DeviceStatus(dev)
+    out, lse, cs = ops.attn_colsum(q.to(dev), kh.to(dev), vh.to(dev), T_hot,
+                                   kr.to(dev) if T_ret else None, vr.to(dev) if T_ret else None,
+                                   torch.from_numpy(bias).to(dev) if T_ret else None, T_ret,
+                                   subsample_ratio=subsample, want_lse=True, status=status)
+    torch.cuda.synchronize()
+    status.raise_if_set("attention")
+    k_all = torch.cat([kh[:, :T_hot], kr[:, :T_ret]], 1).float().numpy().transpose(1, 0, 2)
+    v_all = torch.cat([vh[:, :T_hot], vr[:, :T_ret]], 1).float().numpy().transpose(1, 0, 2)
+    b_all = None
+    if T_ret:
+        b_all = np.concatenate([np.zeros((H, T_hot), np.float32), bias[:, :T_ret]], 1)
+    o_ref, lse_ref, cs_ref = oracle_attn(q.float().numpy(), k_all, v_all, b_all, subsample_ratio=subsample)
+    return (out.float().cpu().numpy(), lse.cpu().numpy(), cs.cpu().numpy()), (o_ref, lse_ref, cs_ref)
+
+
+def _assert_close(got, ref):
+    (o, lse, cs), (o_ref, lse_ref, cs_ref) = got, ref
+    assert np.isfinite(o).all() and np.isfinite(cs).all()
+    assert np.abs(o - o_ref).max() <= 2e-2
+    np.testing.assert_allclose(lse, lse_ref, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(cs, cs_ref, rtol=1e-3, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,H,T_hot,T_ret", [
+    (128, 1, 128, 0),      # one tile, one warpgroup idle
+    (70, 2, 200, 0),       # ragged rows and keys
+    (130, 2, 236, 64),     # two query tiles, pivots with -inf padding
+    (1041, 3, 1300, 200),  # frame-sized query block
+    (257, 2, 0, 300),      # retrieved keys only
+    (64, 1, 5, 3),         # tiny
+])
+def test_two_segment(M, H, T_hot, T_ret):
+    got, ref = _run_two_segment(M, H, T_hot, T_ret, seed=M + T_hot)
+    _assert_close(got, ref)
+
+
+def test_peaked_scores():
+    """Large logits exercise the running-max rescale of the online softmax."""
+    got, ref = _run_two_segment(300, 2, 700, 130, seed=5, spread=3.0)
+    _assert_close(got, ref)
+
+
+@pytest.mark.parametrize("ratio", [0.25, 0.5])
+def test_subsampled_colsum(ratio):
+    got, ref = _run_two_segment(1041, 2, 900, 0, seed=9, subsample=ratio)
+    _assert_close(got, ref)
+
+
+@pytest.mark.parametrize("name", list(cases.ATTENTION))
+def test_reference_layout_entry(name, golden_dir):
+    """flash_attn_bias_colsum with the reference's [B,T,H,D] tensors against the committed
+    torch-generated fixture."""
+    import os
+    from stac_b200 import ops
+    g = np.load(os.path.join(golden_dir, "attention.npz"))
+    q, k, v, bias = cases.attention_inputs(name)
+    dev = torch.device("cuda:0")
+    tq, tk, tv = (_bf16(x)[None].to(dev) for x in (q, k, v))
+    tb = None if bias is None else torch.from_numpy(bias)[None, :, None, :].to(dev)
+    out, lse, cs = ops.flash_attn_bias_colsum(tq, tk, tv, bias=tb, return_colsum=True)
+    torch.cuda.synchronize()
+    assert np.abs(out[0].float().cpu().numpy() - g[f"{name}_out"]).max() <= 2e-2
+    np.testing.assert_allclose(lse[0].cpu().numpy(), g[f"{name}_lse"], rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(cs[0].cpu().numpy(), g[f"{name}_colsum"], rtol=1e-3, atol=1e-6)
+
+
+def test_bounded_wait_reports_and_returns():
+    """A wait on a barrier nothing completes runs out, sets the status word and the kernel
+    returns; the context stays usable."""
+    from stac_b200 import _lib, ops
+    dev = torch.device("cuda:0")
+    status = ops.DeviceStatus(dev)
+    rc = _lib.lib().stac_selftest_bounded_wait(2000, _lib.ptr(status.word), _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.read() == 6
+    status.clear()
+    assert float(torch.ones(4, device=dev).sum().item()) == 4.0
