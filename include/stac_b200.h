@@ -80,6 +80,134 @@ int stac_attn_colsum(const void* q, int64_t q_row_stride,
                      void* workspace, size_t workspace_bytes,
                      int* dev_status, stac_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Voxel table: packed 63-bit key -> stable voxel id (append-only; id = insertion rank).
+ *
+ * Stands in for BinaryVoxel.upsert / neighbors (stac/voxel.py:195-324, :371-521) as called by
+ * STACVoxelKV.append_positions and _search_recent_neighbors (stac/stac_voxel.py:326-365,
+ * :294-323).  The caller owns all arrays:
+ *   table_keys  i64 [table_cap]   packed key of voxel id i
+ *   hash_keys   u64 [hash_cap], hash_vals i32 [hash_cap]: open-addressing table, hash_cap a
+ *               power of two, kept at most half full by the caller (stac_voxel_rehash to grow)
+ *   n_voxels    i32 device scalar, number of voxels in the table
+ * ------------------------------------------------------------------------------------- */
+#define STAC_VOXEL_MAX_POINTS 16384 /* points per stac_voxel_upsert call */
+
+size_t stac_voxel_scratch_bytes(int n_points);
+
+/* Mark every slot of the hash table empty. */
+int stac_voxel_hash_clear(void* hash_keys, int64_t hash_cap, stac_stream_t stream);
+
+/* Clear a (new, larger) hash table and re-insert ids [0, *n_voxels). */
+int stac_voxel_rehash(const int64_t* table_keys, const int* n_voxels, int table_cap, void* hash_keys,
+                      int* hash_vals, int64_t hash_cap, stac_stream_t stream);
+
+/* ijk = floor(points / voxel_size) (fp32, true division), key = (i+2^20) + (j+2^20)*2^21 +
+ * (k+2^20)*2^42; known keys keep their id, keys new in this call get *n_voxels + rank among
+ * the sorted new unique keys.  points f32 [n,3], or ijk i32 [n,3] already quantised (exactly
+ * one of the two non-NULL); mask u8 [n] or NULL (0 -> id -1); ids_out i32 [n].  *n_voxels is
+ * updated on the device; no host synchronisation. */
+int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* mask, int n_points, float voxel_size,
+                      int64_t* table_keys, int table_cap, void* hash_keys, int* hash_vals, int64_t hash_cap,
+                      int* n_voxels, int* ids_out, void* scratch, size_t scratch_bytes,
+                      int* dev_status, stac_stream_t stream);
+
+/* Ascending unique ids of the existing voxels inside the Chebyshev cube of `radius_cells`
+ * around the voxels of `token_voxel_ids` (negative entries ignored); with all_ids != 0 every id
+ * in the table instead.  flags u8 [table_cap] must be zero on entry and is zero on exit;
+ * out_ids i32 [table_cap], *out_count i32 on the device. */
+int stac_voxel_neighbors(const int* token_voxel_ids, int n_tokens, int radius_cells, int all_ids,
+                         const int64_t* table_keys, const int* n_voxels, int table_cap,
+                         const void* hash_keys, const int* hash_vals, int64_t hash_cap,
+                         uint8_t* flags, int* out_ids, int* out_count, stac_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * H2O bookkeeping on the hot cache (rows = managed layers x heads).
+ * ------------------------------------------------------------------------------------- */
+
+/* HeavyHittersKV._update_scores (stac/h2o.py:177-216) for one layer: s = colsum * T_live / Tq;
+ * positions >= old_T take s, older ones score * temperature + s; counts += 1. */
+int stac_scores_update(const float* colsum, int64_t colsum_head_stride, float* scores, float* counts,
+                       int64_t row_stride, int H, int T_live, int old_T, int Tq, float temperature,
+                       stac_stream_t stream);
+
+/* Keep set of HeavyHittersKV._parallel_prune_kv (stac/h2o.py:244-354): per row, positions with
+ * is_base[t] != 0 (pinned and recent tokens) plus the highest-scoring others, n_keep in total
+ * (ties at the cut: lower position first).  keep_idx i32 [n_rows, n_keep] and drop_idx i32
+ * [n_rows, T - n_keep], both ascending. */
+int stac_h2o_select(const float* scores, int64_t row_stride, int n_rows, const uint8_t* is_base, int T,
+                    int n_keep, int* keep_idx, int* drop_idx, stac_stream_t stream);
+
+/* Gather-compaction of the cache into a second set of buffers
+ * (stac/h2o.py:356-436, stac/stac_voxel.py:409-419): dst[row, j] = src[row, keep[row, j]] for
+ * K, V [n_rows, T_buf, head_dim], token ids i64, scores, counts f32 and voxel ids i32
+ * [n_rows, T_buf]; tails [n_keep, T_buf) of the small arrays are reset (-1 / 0).
+ * vx_src / vx_dst may both be NULL. */
+int stac_compact(const int* keep_idx, int n_rows, int n_keep, int T_buf, int head_dim, int elem_bytes,
+                 const void* k_src, const void* v_src, void* k_dst, void* v_dst,
+                 const int64_t* ti_src, int64_t* ti_dst, const float* s_src, float* s_dst,
+                 const float* c_src, float* c_dst, const int* vx_src, int* vx_dst, stac_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Voxel memory: per (pool head, voxel) row up to budget_cap buffered tokens and pivot_cap
+ * pivots, one token per pool segment.  Same observable state as the reference's
+ * SegmentedSlabPool with seg_size = 1 (stac/allocator.py:2036-2506): row_seg[row][column] is
+ * the segment id, row_cnt[row] the occupied columns, a LIFO free list plus a bump counter.
+ * Rows are laid out [heads][voxel_cap].  The caller owns and grows every array.
+ * ------------------------------------------------------------------------------------- */
+enum stac_meta_index {       /* int32 counters in device memory, pool->meta[STAC_META_SIZE] */
+  STAC_META_BUF_TOP = 0,     /* fresh buffer segment ids handed out so far */
+  STAC_META_BUF_FREE_LEN = 1,/* entries in the buffer free list */
+  STAC_META_PIV_TOP = 2,     /* pivot segment ids handed out so far */
+  STAC_META_OVER_COUNT = 3,  /* tokens in the carried overflow list */
+  STAC_META_BUF_USED = 4,    /* tokens currently buffered */
+  STAC_META_PIV_USED = 5,    /* pivots currently stored */
+  STAC_META_SIZE = 8
+};
+
+typedef struct stac_pool {
+  int heads, head_dim, elem_bytes;   /* elem_bytes: 2 = bf16, 4 = f32 storage of K and V */
+  int pivot_cap, budget_cap;         /* P <= 4, B <= 8 */
+  int voxel_cap, voxel_used;         /* row stride per head; voxels known at the last insert */
+  float sim_thresh, replace_thresh, score_thresh;
+  void* buf_K; void* buf_V; float* buf_S;       /* [buf_cap][head_dim], [buf_cap] */
+  int* buf_row_seg; int* buf_row_cnt; int* buf_free; int buf_cap;
+  void* piv_K; void* piv_V; float* piv_W; float* piv_S; float* piv_C;
+  int* piv_row_seg; int* piv_row_cnt; int piv_cap;
+  /* carried overflow tokens: list read by this call and list written by it (the caller swaps) */
+  const void* over_K_in; const void* over_V_in; const float* over_S_in;
+  const int* over_hv_in;      /* [n][2] (head, voxel) */
+  const int* over_start_in;   /* [heads + 1] first list entry of each head */
+  void* over_K_out; void* over_V_out; float* over_S_out; int* over_hv_out; int* over_start_out;
+  int over_cap;
+  int* meta;
+} stac_pool;
+
+typedef struct stac_evicted {
+  const void* k; const void* v;      /* token at position t of head h: k + h*kv_head_stride + t*kv_row_stride */
+  int64_t kv_head_stride, kv_row_stride;
+  const float* scores; const int* voxel_ids; /* [heads][meta_head_stride] indexed by position */
+  int64_t meta_head_stride;
+  const int* positions;              /* [heads][tokens_per_head] ascending positions, or NULL = 0..n-1 */
+  int tokens_per_head;
+} stac_evicted;
+
+size_t stac_merge_scratch_bytes(int heads, int list_cap_per_head, int buf_cap);
+
+/* One VoxelKVMerger.insert_and_merge call (stac/merger.py:1157-1255 and :765-918) with the
+ * evicted tokens read in place.  list_cap_per_head bounds (evicted + carried overflow) tokens
+ * of one head (<= 32767).  Counters in pool->meta are updated on the device. */
+int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scratch, size_t scratch_bytes,
+                      int list_cap_per_head, int* dev_status, stac_stream_t stream);
+
+/* VoxelKVMerger.retrieve with retrieve_size > 0 (stac/merger.py:1377-1482): per head the
+ * pivots of the queried voxels (ascending ids < voxel_used) by W descending; out_K/out_V
+ * [heads][R][head_dim], out_mask u8, out_bias f32 = log(max(C,1e-9)) or -inf, sel i32 scratch
+ * [heads][R], out_idx i32 [heads][R][2] = (voxel, slot) or NULL.  R <= 4096. */
+int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_count, int retrieve_size,
+                  int* sel, void* out_K, void* out_V, uint8_t* out_mask, float* out_bias, int* out_idx,
+                  stac_stream_t stream);
+
 /* Self-test of the bounded-wait mechanism: launches one CTA that waits on a barrier nothing
  * ever completes; the wait gives up after about `max_polls` polls, writes
  * STAC_DEV_TEST_TIMEOUT to *dev_status and the kernel exits normally. */

@@ -10,6 +10,44 @@ LIB_PATH = os.path.join(HERE, "libstac_b200.so")
 c_void_p, c_int, c_i64, c_f32, c_size_t = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64,
                                            ctypes.c_float, ctypes.c_size_t)
 
+
+
+class StacPool(ctypes.Structure):
+    """Mirror of `struct stac_pool` (include/stac_b200.h)."""
+    _fields_ = [
+        ("heads", c_int), ("head_dim", c_int), ("elem_bytes", c_int),
+        ("pivot_cap", c_int), ("budget_cap", c_int),
+        ("voxel_cap", c_int), ("voxel_used", c_int),
+        ("sim_thresh", c_f32), ("replace_thresh", c_f32), ("score_thresh", c_f32),
+        ("buf_K", c_void_p), ("buf_V", c_void_p), ("buf_S", c_void_p),
+        ("buf_row_seg", c_void_p), ("buf_row_cnt", c_void_p), ("buf_free", c_void_p), ("buf_cap", c_int),
+        ("piv_K", c_void_p), ("piv_V", c_void_p), ("piv_W", c_void_p), ("piv_S", c_void_p), ("piv_C", c_void_p),
+        ("piv_row_seg", c_void_p), ("piv_row_cnt", c_void_p), ("piv_cap", c_int),
+        ("over_K_in", c_void_p), ("over_V_in", c_void_p), ("over_S_in", c_void_p),
+        ("over_hv_in", c_void_p), ("over_start_in", c_void_p),
+        ("over_K_out", c_void_p), ("over_V_out", c_void_p), ("over_S_out", c_void_p),
+        ("over_hv_out", c_void_p), ("over_start_out", c_void_p),
+        ("over_cap", c_int),
+        ("meta", c_void_p),
+    ]
+
+
+class StacEvicted(ctypes.Structure):
+    """Mirror of `struct stac_evicted` (include/stac_b200.h)."""
+    _fields_ = [
+        ("k", c_void_p), ("v", c_void_p),
+        ("kv_head_stride", c_i64), ("kv_row_stride", c_i64),
+        ("scores", c_void_p), ("voxel_ids", c_void_p),
+        ("meta_head_stride", c_i64),
+        ("positions", c_void_p),
+        ("tokens_per_head", c_int),
+    ]
+
+
+META_BUF_TOP, META_BUF_FREE_LEN, META_PIV_TOP, META_OVER_COUNT, META_BUF_USED, META_PIV_USED = range(6)
+META_SIZE = 8
+VOXEL_MAX_POINTS = 16384
+
 # name -> (restype, argtypes); must list every function declared in include/stac_b200.h
 SIGNATURES = {
     "stac_status_string": (ctypes.c_char_p, [c_int]),
@@ -19,6 +57,24 @@ SIGNATURES = {
                                  c_i64, c_i64, c_int, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p, c_i64,
                                  c_int, c_int, c_int, c_f32, c_f32, c_void_p, c_size_t, c_void_p, c_void_p]),
     "stac_selftest_bounded_wait": (c_int, [c_int, c_void_p, c_void_p]),
+    "stac_voxel_scratch_bytes": (c_size_t, [c_int]),
+    "stac_voxel_hash_clear": (c_int, [c_void_p, c_i64, c_void_p]),
+    "stac_voxel_rehash": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_i64, c_void_p]),
+    "stac_voxel_upsert": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_f32, c_void_p, c_int, c_void_p, c_void_p, c_i64,
+                                  c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "stac_voxel_neighbors": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                     c_i64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "stac_scores_update": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_int, c_int, c_int, c_int, c_f32,
+                                   c_void_p]),
+    "stac_h2o_select": (c_int, [c_void_p, c_i64, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "stac_compact": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p]),
+    "stac_merge_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "stac_merge_insert": (c_int, [ctypes.POINTER(StacPool), ctypes.POINTER(StacEvicted), c_void_p, c_size_t, c_int,
+                                  c_void_p, c_void_p]),
+    "stac_retrieve": (c_int, [ctypes.POINTER(StacPool), c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libstac_b200.so")
-SOURCES = ["abi.cu", "attn_colsum.cu"]
+SOURCES = ["abi.cu", "attn_colsum.cu", "voxel.cu", "h2o.cu", "merge.cu", "retrieve.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -1,0 +1,1094 @@
+// Eviction into the voxel memory: deterministic segmented merge of evicted K/V into the
+// per-(head, voxel) pools.
+//
+// Replaces VoxelKVMerger.insert_and_merge and its helpers on the reference's Python path
+// (stac/merger.py:1157-1255 filter + stable sort by row, :765-918 order of operations,
+// :586-760 token -> pivot merge, :408-461 full buffer -> one pivot, :462-582 pivot insert /
+// victim re-merge) together with the Top-B append and the segment allocator
+// (stac/allocator.py:559-723, :2237-2345, :2306-2319), and the merger-cuda pipeline that the
+// reference uses on the GPU (merger-cuda/csrc/kernels/merger_kernels.cu).
+//
+// Every output is a pure function of the inputs: per-(head, voxel) work is done by one warp
+// in token order, and everything that depends on an order across rows (which segment id a
+// row gets, where its overflow lands, where freed ids go) is computed from exclusive scans
+// over the rows in (head, voxel) order.  No floating-point atomics and no slot pops by
+// atomics, so keys, slot maps and merged values repeat bit for bit from run to run.
+//
+// Kernels, in launch order:
+//   sort_tokens_kernel   one CTA per pool head: list the head's valid evicted tokens followed
+//                        by its carried overflow tokens, stable LSD radix sort by voxel id,
+//                        emit the unique rows (CSR).
+//   rows_phase_a_kernel  one warp per row: merge tokens into existing pivots (cosine >= sim),
+//                        select the rest, rank existing buffer tokens + selected tokens by
+//                        (score desc, arrival order), count new segments / overflow / full.
+//   scan_heads_kernel /  exclusive scans of those counts, allocation plan (k ids from the top
+//   scan_plan_kernel     of the free list, the rest fresh), capacity checks.
+//   rows_phase_b_kernel  one warp per row: hand out segment ids, place buffer tokens at
+//                        column = rank, emit overflow, turn full buffers into a pivot, insert
+//                        it (folding the lowest-weight pivot into its nearest neighbour when
+//                        the row is saturated), stage the freed segment ids.
+//   finalize_kernel      append staged ids to the free list, publish counters.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "stac_internal.h"
+
+namespace stac {
+namespace {
+
+constexpr int kMaxB = 8;
+constexpr int kMaxP = 4;
+constexpr unsigned kFull = 0xffffffffu;
+
+// ------------------------------------------------------------------------------------ helpers
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ float load_cg(const float* p) { return __ldcg(p); }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float round(float v) { return v; }
+  static constexpr bool kIsBf16 = false;
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ float load_cg(const __nv_bfloat16* p) {
+    const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(p));
+    return __uint_as_float(static_cast<unsigned int>(u) << 16);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+  static constexpr bool kIsBf16 = true;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+  return v;
+}
+
+struct MergeParams {
+  // geometry
+  int heads, D, P, B, voxel_cap, voxel_used;
+  float sim_thresh, replace_thresh, score_thresh;
+  // evicted tokens: token j of head h lives at position pos = idx ? idx[h*n_new + j] : j
+  const void* k_src;
+  const void* v_src;
+  const float* s_src;
+  const int* vx_src;
+  const int* idx;
+  long long src_head_stride;   // elements between heads in k_src / v_src
+  long long src_row_stride;    // elements between positions
+  long long meta_head_stride;  // elements between heads in s_src / vx_src
+  int n_new;                   // tokens per head
+  // pools
+  void* buf_K; void* buf_V; float* buf_S;
+  int* buf_row_seg; int* buf_row_cnt; int* buf_free; int buf_cap;
+  void* piv_K; void* piv_V; float* piv_W; float* piv_S; float* piv_C;
+  int* piv_row_seg; int* piv_row_cnt; int piv_cap;
+  // overflow lists
+  const void* over_K_in; const void* over_V_in; const float* over_S_in; const int* over_hv_in;
+  const int* over_start_in;  // [heads + 1]
+  void* over_K_out; void* over_V_out; float* over_S_out; int* over_hv_out;
+  int* over_start_out;
+  int over_cap;
+  int* meta;  // device ints, see STAC_META_*
+  // scratch
+  int ncap;            // per-head capacity of the token lists
+  unsigned int* keys_a; unsigned int* keys_b;  // [heads][ncap]
+  int* vals_a; int* vals_b;                    // [heads][ncap]
+  int* n_tok;          // [heads]
+  int* n_rows;         // [heads]
+  int* row_vx;         // [heads][ncap]
+  int* row_start;      // [heads][ncap + 1]
+  int4* row_info;      // [heads][ncap]: add_cnt, over_cnt, flags, n_sel
+  int4* row_pref;      // [heads][ncap]: exclusive prefixes inside the head
+  short* old_dest;     // [heads][ncap][8]
+  int* tok_dest;       // [heads][ncap]
+  float* tok_sim;      // [heads][ncap]
+  float* tok_score;    // [heads][ncap]
+  int4* head_tot;      // [heads]
+  int4* head_base;     // [heads]
+  int* plan;           // device ints, see kPlan*
+  int* free_stage;     // [buf_cap]
+  int passes;          // radix passes (8 bits each)
+  int* err;
+};
+
+enum { kPlanK = 0, kPlanFreeLen, kPlanBufTop, kPlanPivTop, kPlanTotalAdd, kPlanTotalFull, kPlanTotalOver,
+       kPlanAnyValid, kPlanAbort, kPlanSize = 16 };
+
+// Block-wide exclusive scan, 1024 threads.
+__device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sums[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(kFull, w, o);
+      if (lane >= o) w += t;
+    }
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  const int excl = (warp > 0 ? warp_sums[warp - 1] : 0) + incl - v;
+  if (threadIdx.x == 0) *total = warp_sums[31];
+  __syncthreads();
+  return excl;
+}
+
+// ------------------------------------------------------------------------------------ sort
+__global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams p) {
+  __shared__ int hist[256 * 32];  // [digit][warp]
+  __shared__ int warp_sums[32];
+  __shared__ int sh_total;
+  __shared__ int sh_carry;
+  const int h = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned int* ka = p.keys_a + static_cast<long long>(h) * p.ncap;
+  unsigned int* kb = p.keys_b + static_cast<long long>(h) * p.ncap;
+  int* va = p.vals_a + static_cast<long long>(h) * p.ncap;
+  int* vb = p.vals_b + static_cast<long long>(h) * p.ncap;
+
+  // 1. valid evicted tokens in position order
+  if (threadIdx.x == 0) sh_carry = 0;
+  __syncthreads();
+  for (int base = 0; base < p.n_new; base += 1024) {
+    const int j = base + threadIdx.x;
+    int vx = -1;
+    if (j < p.n_new) {
+      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + j] : j;
+      vx = p.vx_src[h * p.meta_head_stride + pos];
+    }
+    const int ok = (vx >= 0 && vx < p.voxel_used) ? 1 : 0;
+    const int off = sh_carry + block_scan(ok, warp_sums, &sh_total);
+    if (ok) {
+      ka[off] = static_cast<unsigned int>(vx);
+      va[off] = j;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) sh_carry += sh_total;
+    __syncthreads();
+  }
+  const int n_valid = sh_carry;
+  if (n_valid > 0 && threadIdx.x == 0) atomicOr(&p.plan[kPlanAnyValid], 1);
+  // 2. carried overflow tokens of this head, in list order
+  const int os = p.over_start_in[h], oe = p.over_start_in[h + 1];
+  int n = n_valid + (oe - os);
+  if (n > p.ncap) {
+    if (threadIdx.x == 0) report_error(p.err, DEV_SORT_CAPACITY);
+    n = p.ncap;
+  }
+  for (int o = os + threadIdx.x; o < oe; o += 1024) {
+    const int dst = n_valid + (o - os);
+    if (dst < n) {
+      ka[dst] = static_cast<unsigned int>(p.over_hv_in[2 * o + 1]);
+      va[dst] = ~o;
+    }
+  }
+  __syncthreads();
+  // 3. stable LSD radix sort by voxel id.  Each warp owns a contiguous chunk of the list so
+  //    that (warp, position in chunk) preserves the input order.
+  const int chunk = ((n + 31) / 32 + 31) / 32 * 32;  // items per warp, multiple of 32
+  const int c0 = warp * chunk;
+  const int c1 = min(n, c0 + chunk);
+  unsigned int* kin = ka; int* vin = va; unsigned int* kout = kb; int* vout = vb;
+  for (int pass = 0; pass < p.passes; ++pass) {
+    const int shift = pass * 8;
+    for (int i = threadIdx.x; i < 256 * 32; i += 1024) hist[i] = 0;
+    __syncthreads();
+    for (int base = c0; base < c1; base += 32) {
+      const int i = base + lane;
+      const bool in = i < c1;
+      const unsigned int d = in ? ((kin[i] >> shift) & 255u) : (256u + lane);
+      const unsigned int peers = __match_any_sync(kFull, d);
+      if (in && (peers & ((1u << lane) - 1)) == 0) hist[d * 32 + warp] += __popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();
+    // exclusive scan of hist in (digit, warp) order: 8 consecutive entries per thread
+    int loc[8];
+    int sum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      loc[e] = hist[threadIdx.x * 8 + e];
+      sum += loc[e];
+    }
+    int run = block_scan(sum, warp_sums, &sh_total);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      hist[threadIdx.x * 8 + e] = run;
+      run += loc[e];
+    }
+    __syncthreads();
+    for (int base = c0; base < c1; base += 32) {
+      const int i = base + lane;
+      const bool in = i < c1;
+      unsigned int key = 0;
+      int val = 0;
+      if (in) {
+        key = kin[i];
+        val = vin[i];
+      }
+      const unsigned int d = in ? ((key >> shift) & 255u) : (256u + lane);
+      const unsigned int peers = __match_any_sync(kFull, d);
+      const unsigned int before = peers & ((1u << lane) - 1);
+      if (in) {
+        const int dst = hist[d * 32 + warp] + __popc(before);
+        kout[dst] = key;
+        vout[dst] = val;
+      }
+      __syncwarp();
+      if (in && before == 0) hist[d * 32 + warp] += __popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();
+    unsigned int* tk = kin; kin = kout; kout = tk;
+    int* tv = vin; vin = vout; vout = tv;
+  }
+  // 4. unique rows of the sorted list (kin / vin now hold the result)
+  if (threadIdx.x == 0) sh_carry = 0;
+  __syncthreads();
+  int* rvx = p.row_vx + static_cast<long long>(h) * p.ncap;
+  int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + threadIdx.x;
+    int head_flag = 0;
+    unsigned int key = 0;
+    if (i < n) {
+      key = kin[i];
+      head_flag = (i == 0 || kin[i - 1] != key) ? 1 : 0;
+    }
+    const int r = sh_carry + block_scan(head_flag, warp_sums, &sh_total);
+    if (head_flag) {
+      rvx[r] = static_cast<int>(key);
+      rst[r] = i;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) sh_carry += sh_total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    rst[sh_carry] = n;
+    p.n_rows[h] = sh_carry;
+    p.n_tok[h] = n;
+  }
+}
+
+// ------------------------------------------------------------------------------------ token access
+template <typename T, int EPL>
+struct TokenReader {
+  const MergeParams& p;
+  int h, lane;
+  __device__ TokenReader(const MergeParams& p_, int h_, int lane_) : p(p_), h(h_), lane(lane_) {}
+  // code >= 0: evicted token index; code < 0: ~index into the carried overflow list
+  __device__ __forceinline__ void load_k(int code, float (&k)[EPL]) const {
+    const T* base;
+    if (code >= 0) {
+      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+      base = static_cast<const T*>(p.k_src) + h * p.src_head_stride + pos * p.src_row_stride;
+    } else {
+      base = static_cast<const T*>(p.over_K_in) + static_cast<long long>(~code) * p.D;
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) k[e] = Elem<T>::load(base + lane * EPL + e);
+  }
+  __device__ __forceinline__ void load_v(int code, float (&v)[EPL]) const {
+    const T* base;
+    if (code >= 0) {
+      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+      base = static_cast<const T*>(p.v_src) + h * p.src_head_stride + pos * p.src_row_stride;
+    } else {
+      base = static_cast<const T*>(p.over_V_in) + static_cast<long long>(~code) * p.D;
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = Elem<T>::load(base + lane * EPL + e);
+  }
+  __device__ __forceinline__ float load_s(int code) const {
+    if (code >= 0) {
+      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+      return p.s_src[h * p.meta_head_stride + pos];
+    }
+    return p.over_S_in[~code];
+  }
+};
+
+template <int EPL>
+__device__ __forceinline__ float norm_inv_denom(const float (&x)[EPL]) {
+  float s = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) s += x[e] * x[e];
+  return fmaxf(sqrtf(warp_sum(s)), 1e-6f);
+}
+
+// ------------------------------------------------------------------------------------ phase A
+template <typename T, int EPL>
+__global__ void __launch_bounds__(256) rows_phase_a_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int ri = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p.plan[kPlanAnyValid] == 0) return;
+  if (ri >= p.n_rows[h]) return;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int vx = p.row_vx[hb + ri];
+  const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
+  const int s0 = rst[ri], s1 = rst[ri + 1];
+  const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
+  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+  const int npiv = p.piv_row_cnt[r];
+  const int nbuf = p.buf_row_cnt[r];
+  TokenReader<T, EPL> rd(p, h, lane);
+  float* tsim = p.tok_sim + hb;
+  float* tscore = p.tok_score + hb;
+  int* tdest = p.tok_dest + hb;
+
+  if (npiv > 0) {
+    // ---- tokens against the row's pivots (stac/merger.py:586-760)
+    float kp[kMaxP][EPL], vp[kMaxP][EPL], kpn[kMaxP][EPL];
+    float Wp[kMaxP], Sp[kMaxP], Cp[kMaxP];
+    int seg[kMaxP];
+    float accK[kMaxP][EPL], accV[kMaxP][EPL], accA[kMaxP], accS[kMaxP], accC[kMaxP];
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      seg[q] = -1;
+      Wp[q] = Sp[q] = Cp[q] = 0.f;
+      accA[q] = accS[q] = accC[q] = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) kp[q][e] = vp[q][e] = kpn[q][e] = accK[q][e] = accV[q][e] = 0.f;
+      if (q < npiv) {
+        seg[q] = p.piv_row_seg[r * p.P + q];
+        const T* kb = static_cast<const T*>(p.piv_K) + static_cast<long long>(seg[q]) * p.D;
+        const T* vb = static_cast<const T*>(p.piv_V) + static_cast<long long>(seg[q]) * p.D;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          kp[q][e] = Elem<T>::load(kb + lane * EPL + e);
+          vp[q][e] = Elem<T>::load(vb + lane * EPL + e);
+        }
+        Wp[q] = p.piv_W[seg[q]];
+        Sp[q] = p.piv_S[seg[q]];
+        Cp[q] = p.piv_C[seg[q]];
+        const float den = norm_inv_denom<EPL>(kp[q]);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) kpn[q][e] = __fdiv_rn(kp[q][e], den);
+      }
+    }
+    for (int i = s0; i < s1; ++i) {
+      const int code = codes[i];
+      float k[EPL];
+      rd.load_k(code, k);
+      const float s_raw = rd.load_s(code);
+      const float s_t = fmaxf(s_raw, 1e-6f);
+      const float den = norm_inv_denom<EPL>(k);
+      float best_sim = -INFINITY;
+      int best = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxP; ++q) {
+        if (q < npiv) {
+          float d = 0.f;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) d += __fdiv_rn(k[e], den) * kpn[q][e];
+          d = fminf(1.f, fmaxf(-1.f, warp_sum(d)));
+          if (d > best_sim) {
+            best_sim = d;
+            best = q;
+          }
+        }
+      }
+      if (lane == 0) {
+        tsim[i] = best_sim;
+        tscore[i] = s_raw;
+      }
+      if (best_sim >= p.sim_thresh) {
+        const float a = expf(best_sim);
+        float v[EPL];
+        rd.load_v(code, v);
+#pragma unroll
+        for (int q = 0; q < kMaxP; ++q) {
+          if (q == best) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+              accK[q][e] = __fadd_rn(accK[q][e], __fmul_rn(a, k[e]));
+              accV[q][e] = __fadd_rn(accV[q][e], __fmul_rn(a, v[e]));
+            }
+            accA[q] = __fadd_rn(accA[q], a);
+            accS[q] = __fadd_rn(accS[q], s_t);
+            accC[q] = __fadd_rn(accC[q], 1.f);
+          }
+        }
+      }
+    }
+    float sumS = 0.f, sumC = 0.f;
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      if (q < npiv) {
+        if (accA[q] > 0.f) {
+          const float denom = fmaxf(__fadd_rn(Wp[q], accA[q]), 1e-8f);
+          const float fo = __fdiv_rn(Wp[q], denom), fn = __fdiv_rn(1.0f, denom);
+          T* kb = static_cast<T*>(p.piv_K) + static_cast<long long>(seg[q]) * p.D;
+          T* vb = static_cast<T*>(p.piv_V) + static_cast<long long>(seg[q]) * p.D;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) {
+            Elem<T>::store(kb + lane * EPL + e, __fadd_rn(__fmul_rn(fo, kp[q][e]), __fmul_rn(fn, accK[q][e])));
+            Elem<T>::store(vb + lane * EPL + e, __fadd_rn(__fmul_rn(fo, vp[q][e]), __fmul_rn(fn, accV[q][e])));
+          }
+          Wp[q] = denom;
+          Sp[q] = __fadd_rn(Sp[q], accS[q]);
+          Cp[q] = __fadd_rn(Cp[q], accC[q]);
+          if (lane == 0) {
+            p.piv_W[seg[q]] = Wp[q];
+            p.piv_S[seg[q]] = Sp[q];
+            p.piv_C[seg[q]] = Cp[q];
+          }
+        }
+        sumS = __fadd_rn(sumS, Sp[q]);
+        sumC = __fadd_rn(sumC, Cp[q]);
+      }
+    }
+    const float gate = __fmul_rn(__fdiv_rn(sumS, fmaxf(sumC, 1e-6f)), p.score_thresh);
+    __syncwarp();
+    for (int i = s0 + lane; i < s1; i += 32) {
+      const bool sel = (tsim[i] < p.replace_thresh) && (fmaxf(tscore[i], 1e-6f) > gate);
+      tdest[i] = sel ? 0 : -1;
+    }
+  } else {
+    for (int i = s0 + lane; i < s1; i += 32) {
+      tscore[i] = rd.load_s(codes[i]);
+      tdest[i] = 0;
+    }
+  }
+  __syncwarp();
+  // ---- rank existing buffer tokens and selected tokens by (score desc, arrival order)
+  float ex_s = 0.f;
+  if (lane < nbuf) ex_s = p.buf_S[p.buf_row_seg[r * p.B + lane]];
+  int n_sel = 0;
+  for (int base = s0; base < s1; base += 32) {
+    const int i = base + lane;
+    const bool sel = i < s1 && tdest[i] >= 0;
+    n_sel += __popc(__ballot_sync(kFull, sel));
+  }
+  // existing tokens
+  int ex_rank = 0;
+  for (int c = 0; c < nbuf; ++c) {
+    const float sc = __shfl_sync(kFull, ex_s, c);
+    if (lane < nbuf && (sc > ex_s || (sc == ex_s && c < lane))) ++ex_rank;
+  }
+  for (int base = s0; base < s1; base += 32) {
+    const int i = base + lane;
+    const bool sel = i < s1 && tdest[i] >= 0;
+    const float sc = sel ? tscore[i] : 0.f;
+    const unsigned m = __ballot_sync(kFull, sel);
+    for (unsigned mm = m; mm; mm &= mm - 1) {
+      const int src = __ffs(mm) - 1;
+      const float s2 = __shfl_sync(kFull, sc, src);
+      if (lane < nbuf && s2 > ex_s) ++ex_rank;  // tokens arrive after every existing entry
+    }
+  }
+  short* od = p.old_dest + (hb + ri) * kMaxB;
+  if (lane < nbuf) od[lane] = static_cast<short>(min(ex_rank, 32767));
+  // selected tokens
+  for (int base = s0; base < s1; base += 32) {
+    const int i = base + lane;
+    const bool sel = i < s1 && tdest[i] >= 0;
+    const float mine = sel ? tscore[i] : 0.f;
+    int rank = 0;
+    for (int c = 0; c < nbuf; ++c) {
+      const float sc = __shfl_sync(kFull, ex_s, c);
+      if (sc >= mine) ++rank;  // existing entries win ties
+    }
+    if (sel) {
+      for (int i2 = s0; i2 < s1; ++i2) {
+        if (tdest[i2] >= 0) {
+          const float s2 = tscore[i2];
+          if (s2 > mine || (s2 == mine && i2 < i)) ++rank;
+        }
+      }
+    }
+    __syncwarp();
+    if (sel) tdest[i] = rank;
+  }
+  if (lane == 0) {
+    const int n_cand = nbuf + n_sel;
+    const int newcnt = min(p.B, n_cand);
+    const int full = (n_sel > 0 && newcnt == p.B) ? 1 : 0;
+    int4 info;
+    info.x = newcnt - nbuf;
+    info.y = max(0, n_cand - p.B);
+    info.z = full | ((full && npiv < p.P) ? 2 : 0);
+    info.w = n_sel;
+    p.row_info[hb + ri] = info;
+  }
+}
+
+// ------------------------------------------------------------------------------------ scans
+__global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p) {
+  __shared__ int warp_sums[32];
+  __shared__ int sh_total;
+  __shared__ int carry[4];
+  const int h = blockIdx.x;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int n = p.plan[kPlanAnyValid] ? p.n_rows[h] : 0;
+  if (threadIdx.x < 4) carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + threadIdx.x;
+    int4 info = make_int4(0, 0, 0, 0);
+    if (i < n) info = p.row_info[hb + i];
+    int4 pref;
+    const int v0 = info.x, v1 = info.y, v2 = info.z & 1, v3 = (info.z >> 1) & 1;
+    pref.x = carry[0] + block_scan(v0, warp_sums, &sh_total);
+    const int t0 = sh_total;
+    pref.y = carry[1] + block_scan(v1, warp_sums, &sh_total);
+    const int t1 = sh_total;
+    pref.z = carry[2] + block_scan(v2, warp_sums, &sh_total);
+    const int t2 = sh_total;
+    pref.w = carry[3] + block_scan(v3, warp_sums, &sh_total);
+    const int t3 = sh_total;
+    if (i < n) p.row_pref[hb + i] = pref;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      carry[0] += t0; carry[1] += t1; carry[2] += t2; carry[3] += t3;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) p.head_tot[h] = make_int4(carry[0], carry[1], carry[2], carry[3]);
+}
+
+__global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p) {
+  __shared__ int warp_sums[32];
+  __shared__ int sh_total;
+  __shared__ int carry[4];
+  if (threadIdx.x < 4) carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int base = 0; base < p.heads; base += 1024) {
+    const int h = base + threadIdx.x;
+    int4 t = make_int4(0, 0, 0, 0);
+    if (h < p.heads) t = p.head_tot[h];
+    int4 b;
+    b.x = carry[0] + block_scan(t.x, warp_sums, &sh_total);
+    const int t0 = sh_total;
+    b.y = carry[1] + block_scan(t.y, warp_sums, &sh_total);
+    const int t1 = sh_total;
+    b.z = carry[2] + block_scan(t.z, warp_sums, &sh_total);
+    const int t2 = sh_total;
+    b.w = carry[3] + block_scan(t.w, warp_sums, &sh_total);
+    const int t3 = sh_total;
+    if (h < p.heads) {
+      p.head_base[h] = b;
+      p.over_start_out[h] = b.y;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      carry[0] += t0; carry[1] += t1; carry[2] += t2; carry[3] += t3;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const int any = p.plan[kPlanAnyValid];
+    const int total_add = carry[0], total_over = carry[1], total_full = carry[2], total_piv = carry[3];
+    const int free_len = p.meta[STAC_META_BUF_FREE_LEN];
+    const int buf_top = p.meta[STAC_META_BUF_TOP];
+    const int piv_top = p.meta[STAC_META_PIV_TOP];
+    const int k = min(total_add, free_len);
+    p.plan[kPlanK] = k;
+    p.plan[kPlanFreeLen] = free_len;
+    p.plan[kPlanBufTop] = buf_top;
+    p.plan[kPlanPivTop] = piv_top;
+    p.plan[kPlanTotalAdd] = total_add;
+    p.plan[kPlanTotalFull] = total_full;
+    p.plan[kPlanTotalOver] = total_over;
+    int abort = 0;
+    if (any) {
+      if (buf_top + (total_add - k) > p.buf_cap || piv_top + total_piv > p.piv_cap || total_over > p.over_cap ||
+          free_len - k + total_full * p.B > p.buf_cap)
+        abort = 1;
+    }
+    p.plan[kPlanAbort] = abort;
+    if (abort) report_error(p.err, DEV_POOL_CAPACITY);
+    if (any && !abort) {
+      p.over_start_out[p.heads] = total_over;
+      p.meta[STAC_META_BUF_TOP] = buf_top + (total_add - k);
+      p.meta[STAC_META_PIV_TOP] = piv_top + total_piv;
+      p.meta[STAC_META_OVER_COUNT] = total_over;
+      p.meta[STAC_META_BUF_FREE_LEN] = free_len - k + total_full * p.B;
+      p.meta[STAC_META_BUF_USED] += total_add - total_full * p.B;
+      p.meta[STAC_META_PIV_USED] += total_piv;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ phase B
+template <typename T, int EPL>
+__global__ void __launch_bounds__(256) rows_phase_b_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int ri = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
+  if (ri >= p.n_rows[h]) return;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int vx = p.row_vx[hb + ri];
+  const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
+  const int s0 = rst[ri], s1 = rst[ri + 1];
+  const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
+  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+  const int4 info = p.row_info[hb + ri];
+  if (info.w == 0) return;  // nothing selected: the buffer is untouched
+  const int4 pref = p.row_pref[hb + ri];
+  const int4 hbase = p.head_base[h];
+  const int add_off = hbase.x + pref.x, over_off = hbase.y + pref.y;
+  const int full_off = hbase.z + pref.z, piv_off = hbase.w + pref.w;
+  const int nbuf = p.buf_row_cnt[r];
+  const int newcnt = nbuf + info.x;
+  const int B = p.B, D = p.D;
+  const int* tdest = p.tok_dest + hb;
+  TokenReader<T, EPL> rd(p, h, lane);
+  T* bK = static_cast<T*>(p.buf_K);
+  T* bV = static_cast<T*>(p.buf_V);
+  T* oK = static_cast<T*>(p.over_K_out);
+  T* oV = static_cast<T*>(p.over_V_out);
+
+  // existing tokens into registers (their column may change)
+  float exK[kMaxB][EPL], exV[kMaxB][EPL];
+  float exS = 0.f;
+  int exDest = -1;
+  const short* od = p.old_dest + (hb + ri) * kMaxB;
+  int my_seg = -1;
+  if (lane < nbuf) {
+    my_seg = p.buf_row_seg[r * B + lane];
+    exS = p.buf_S[my_seg];
+    exDest = od[lane];
+  }
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    const int sg = __shfl_sync(kFull, my_seg, c);
+    if (c < nbuf) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        exK[c][e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
+        exV[c][e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) exK[c][e] = exV[c][e] = 0.f;
+    }
+  }
+  // new segment ids for columns nbuf .. newcnt-1
+  const int k_take = p.plan[kPlanK], free_len = p.plan[kPlanFreeLen], buf_top = p.plan[kPlanBufTop];
+  if (lane >= nbuf && lane < newcnt) {
+    const int q = add_off + (lane - nbuf);
+    const int id = q < k_take ? p.buf_free[free_len - k_take + q] : buf_top + (q - k_take);
+    p.buf_row_seg[r * B + lane] = id;
+    my_seg = id;
+  }
+  __syncwarp();
+  // place existing tokens
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    const int d = __shfl_sync(kFull, exDest, c);
+    const float sc = __shfl_sync(kFull, exS, c);
+    if (c < nbuf) {
+      if (d < B) {
+        const int sg = __shfl_sync(kFull, my_seg, d);
+        if (d != c) {
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) {
+            Elem<T>::store(bK + static_cast<long long>(sg) * D + lane * EPL + e, exK[c][e]);
+            Elem<T>::store(bV + static_cast<long long>(sg) * D + lane * EPL + e, exV[c][e]);
+          }
+          if (lane == 0) p.buf_S[sg] = sc;
+        }
+      } else {
+        const long long o = over_off + (d - B);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          Elem<T>::store(oK + o * D + lane * EPL + e, exK[c][e]);
+          Elem<T>::store(oV + o * D + lane * EPL + e, exV[c][e]);
+        }
+        if (lane == 0) {
+          p.over_S_out[o] = sc;
+          p.over_hv_out[2 * o] = h;
+          p.over_hv_out[2 * o + 1] = vx;
+        }
+      }
+    }
+  }
+  // place selected tokens
+  for (int i = s0; i < s1; ++i) {
+    const int d = tdest[i];
+    if (d < 0) continue;
+    const int code = codes[i];
+    float k[EPL], v[EPL];
+    rd.load_k(code, k);
+    rd.load_v(code, v);
+    const float sc = rd.load_s(code);
+    if (d < B) {
+      const int sg = __shfl_sync(kFull, my_seg, d);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        Elem<T>::store(bK + static_cast<long long>(sg) * D + lane * EPL + e, k[e]);
+        Elem<T>::store(bV + static_cast<long long>(sg) * D + lane * EPL + e, v[e]);
+      }
+      if (lane == 0) p.buf_S[sg] = sc;
+    } else {
+      const long long o = over_off + (d - B);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        Elem<T>::store(oK + o * D + lane * EPL + e, k[e]);
+        Elem<T>::store(oV + o * D + lane * EPL + e, v[e]);
+      }
+      if (lane == 0) {
+        p.over_S_out[o] = sc;
+        p.over_hv_out[2 * o] = h;
+        p.over_hv_out[2 * o + 1] = vx;
+      }
+    }
+  }
+  if (!(info.z & 1)) {
+    if (lane == 0) p.buf_row_cnt[r] = newcnt;
+    return;
+  }
+  // ---- the buffer is full: B tokens -> one pivot (stac/merger.py:408-461)
+  __threadfence();
+  __syncwarp();
+  float tk[kMaxB][EPL], tv[kMaxB][EPL];
+  float ts = 0.f;
+  if (lane < B) ts = fmaxf(__ldcg(p.buf_S + my_seg), 1e-6f);
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    const int sg = __shfl_sync(kFull, my_seg, c);
+    if (c < B) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        tk[c][e] = Elem<T>::load_cg(bK + static_cast<long long>(sg) * D + lane * EPL + e);
+        tv[c][e] = Elem<T>::load_cg(bV + static_cast<long long>(sg) * D + lane * EPL + e);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) tk[c][e] = tv[c][e] = 0.f;
+    }
+  }
+  int seed = 0;
+  float seed_s = -INFINITY, sumS = 0.f;
+  for (int c = 0; c < B; ++c) {
+    const float sc = __shfl_sync(kFull, ts, c);
+    if (sc > seed_s) {
+      seed_s = sc;
+      seed = c;
+    }
+    sumS = __fadd_rn(sumS, sc);
+  }
+  float kn_seed[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) kn_seed[e] = 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    if (c == seed) {
+      const float den = norm_inv_denom<EPL>(tk[c]);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) kn_seed[e] = __fdiv_rn(tk[c][e], den);
+    }
+  }
+  float w[kMaxB];
+  float Wsum = 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    w[c] = 0.f;
+    if (c < B) {
+      const float den = norm_inv_denom<EPL>(tk[c]);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) d += __fdiv_rn(tk[c][e], den) * kn_seed[e];
+      d = fminf(1.f, fmaxf(-1.f, warp_sum(d)));
+      w[c] = expf(d);
+      Wsum = __fadd_rn(Wsum, w[c]);
+    }
+  }
+  float nk[EPL], nv[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) nk[e] = nv[e] = 0.f;
+  const float wden = __fadd_rn(Wsum, 1e-8f);
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    if (c < B) {
+      const float cn = __fdiv_rn(w[c], wden);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        nk[e] = __fadd_rn(nk[e], __fmul_rn(cn, tk[c][e]));
+        nv[e] = __fadd_rn(nv[e], __fmul_rn(cn, tv[c][e]));
+      }
+    }
+  }
+  // ---- insert the pivot (stac/merger.py:462-582)
+  T* pK = static_cast<T*>(p.piv_K);
+  T* pV = static_cast<T*>(p.piv_V);
+  const int npiv = p.piv_row_cnt[r];
+  int slot, pseg;
+  if (npiv < p.P) {
+    slot = npiv;
+    pseg = p.plan[kPlanPivTop] + piv_off;
+    if (lane == 0) {
+      p.piv_row_seg[r * p.P + slot] = pseg;
+      p.piv_row_cnt[r] = npiv + 1;
+    }
+  } else {
+    // saturated: fold the lowest-weight pivot into its most similar neighbour, reuse its slot
+    float pk[kMaxP][EPL], pkn[kMaxP][EPL];
+    float pw[kMaxP];
+    int ps[kMaxP];
+    int victim = 0;
+    float wmin = INFINITY;
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      ps[q] = -1;
+      pw[q] = INFINITY;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) pk[q][e] = pkn[q][e] = 0.f;
+      if (q < p.P) {
+        ps[q] = p.piv_row_seg[r * p.P + q];
+        pw[q] = p.piv_W[ps[q]];
+        if (pw[q] < wmin) {
+          wmin = pw[q];
+          victim = q;
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) pk[q][e] = Elem<T>::load(pK + static_cast<long long>(ps[q]) * D + lane * EPL + e);
+        // the reference normalises in the pool dtype here (stac/merger.py:493-495)
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) s += pk[q][e] * pk[q][e];
+        float nrm = Elem<T>::round(sqrtf(warp_sum(s)));
+        nrm = fmaxf(nrm, Elem<T>::round(1e-6f));
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) pkn[q][e] = Elem<T>::round(__fdiv_rn(pk[q][e], nrm));
+      }
+    }
+    float vn[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) vn[e] = 0.f;
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q)
+      if (q == victim) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) vn[e] = pkn[q][e];
+      }
+    int nb = 0;
+    float best = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      if (q < p.P && q != victim) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) d += pkn[q][e] * vn[e];
+        d = Elem<T>::round(warp_sum(d));
+        if (d > best) {
+          best = d;
+          nb = q;
+        }
+      }
+    }
+    if (p.P == 1) {  // no neighbour to fold into: the victim is simply replaced
+      nb = victim;
+    }
+    float scale;
+    if (Elem<T>::kIsBf16) scale = Elem<T>::round(expf(Elem<T>::round(best - 1.0f)));
+    else scale = expf(best - 1.0f);
+    int vseg = -1, nseg = -1;
+    float Wv = 0.f, Wn = 0.f;
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      if (q == victim) { vseg = ps[q]; Wv = pw[q]; }
+      if (q == nb) { nseg = ps[q]; Wn = pw[q]; }
+    }
+    if (p.P > 1) {
+      const float Wj = __fmul_rn(Wv, scale);
+      const float denom = fmaxf(__fadd_rn(Wj, Wn), 1e-8f);
+      const float fj = __fdiv_rn(Wj, denom), fk = __fdiv_rn(Wn, denom);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const long long oj = static_cast<long long>(vseg) * D + lane * EPL + e;
+        const long long ok = static_cast<long long>(nseg) * D + lane * EPL + e;
+        const float kj = Elem<T>::load(pK + oj), kk = Elem<T>::load(pK + ok);
+        const float vj = Elem<T>::load(pV + oj), vk = Elem<T>::load(pV + ok);
+        Elem<T>::store(pK + ok, __fadd_rn(__fmul_rn(fj, kj), __fmul_rn(fk, kk)));
+        Elem<T>::store(pV + ok, __fadd_rn(__fmul_rn(fj, vj), __fmul_rn(fk, vk)));
+      }
+      if (lane == 0) {
+        p.piv_W[nseg] = denom;
+        p.piv_S[nseg] = __fadd_rn(p.piv_S[vseg], p.piv_S[nseg]);
+        p.piv_C[nseg] = __fadd_rn(p.piv_C[vseg], p.piv_C[nseg]);
+      }
+    }
+    __syncwarp();
+    slot = victim;
+    pseg = vseg;
+  }
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    Elem<T>::store(pK + static_cast<long long>(pseg) * D + lane * EPL + e, nk[e]);
+    Elem<T>::store(pV + static_cast<long long>(pseg) * D + lane * EPL + e, nv[e]);
+  }
+  if (lane == 0) {
+    p.piv_W[pseg] = Wsum;
+    p.piv_S[pseg] = sumS;
+    p.piv_C[pseg] = static_cast<float>(B);
+  }
+  // ---- release the buffer row: segment ids go to the staging area in column order
+  if (lane < B) {
+    p.free_stage[full_off * B + lane] = my_seg;
+    p.buf_row_seg[r * B + lane] = -1;
+  }
+  if (lane == 0) p.buf_row_cnt[r] = 0;
+}
+
+// Freed ids are appended after the part of the free list that was not handed out.
+__global__ void finalize_kernel(const MergeParams p) {
+  const int any = p.plan[kPlanAnyValid];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (any && p.plan[kPlanAbort] == 0) {
+    const int n_freed = p.plan[kPlanTotalFull] * p.B;
+    const int base = p.plan[kPlanFreeLen] - p.plan[kPlanK];
+    if (i < n_freed) p.buf_free[base + i] = p.free_stage[i];
+  }
+}
+
+// No valid evicted token in the whole call: the reference returns before touching the
+// carried overflow (stac/merger.py:1203-1208), so the list is carried over unchanged.
+template <typename T>
+__global__ void carry_overflow_kernel(const MergeParams p) {
+  if (p.plan[kPlanAnyValid] != 0 && p.plan[kPlanAbort] == 0) return;
+  const int n = p.over_start_in[p.heads];
+  const long long total = static_cast<long long>(n) * p.D;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    static_cast<T*>(p.over_K_out)[i] = static_cast<const T*>(p.over_K_in)[i];
+    static_cast<T*>(p.over_V_out)[i] = static_cast<const T*>(p.over_V_in)[i];
+  }
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    p.over_S_out[i] = p.over_S_in[i];
+    p.over_hv_out[2 * i] = p.over_hv_in[2 * i];
+    p.over_hv_out[2 * i + 1] = p.over_hv_in[2 * i + 1];
+  }
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i <= p.heads; i += stride)
+    p.over_start_out[i] = p.over_start_in[i];
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct ScratchLayout {
+  size_t keys_a, keys_b, vals_a, vals_b, n_tok, n_rows, row_vx, row_start, row_info, row_pref, old_dest, tok_dest,
+      tok_sim, tok_score, head_tot, head_base, plan, free_stage, total;
+};
+
+ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
+  ScratchLayout L;
+  size_t off = 0;
+  const size_t hn = static_cast<size_t>(heads) * ncap;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off = align_up(off + bytes, 256);
+    return o;
+  };
+  L.keys_a = take(hn * 4); L.keys_b = take(hn * 4); L.vals_a = take(hn * 4); L.vals_b = take(hn * 4);
+  L.n_tok = take(static_cast<size_t>(heads) * 4); L.n_rows = take(static_cast<size_t>(heads) * 4);
+  L.row_vx = take(hn * 4); L.row_start = take(static_cast<size_t>(heads) * (ncap + 1) * 4);
+  L.row_info = take(hn * 16); L.row_pref = take(hn * 16); L.old_dest = take(hn * kMaxB * 2);
+  L.tok_dest = take(hn * 4); L.tok_sim = take(hn * 4); L.tok_score = take(hn * 4);
+  L.head_tot = take(static_cast<size_t>(heads) * 16); L.head_base = take(static_cast<size_t>(heads) * 16);
+  L.plan = take(kPlanSize * 4); L.free_stage = take(static_cast<size_t>(buf_cap) * 4);
+  L.total = off;
+  return L;
+}
+
+template <typename T>
+int launch_merge(MergeParams& mp, cudaStream_t st) {
+  if (cudaMemsetAsync(mp.plan, 0, kPlanSize * 4, st) != cudaSuccess) return STAC_ERR_CUDA;
+  sort_tokens_kernel<<<mp.heads, 1024, 0, st>>>(mp);
+  const int warps = 8;
+  dim3 grid_rows((mp.ncap + warps - 1) / warps, mp.heads);
+  rows_phase_a_kernel<T, 2><<<grid_rows, warps * 32, 0, st>>>(mp);
+  scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp);
+  scan_plan_kernel<<<1, 1024, 0, st>>>(mp);
+  rows_phase_b_kernel<T, 2><<<grid_rows, warps * 32, 0, st>>>(mp);
+  const int fin_blocks = (mp.buf_cap + 255) / 256;
+  finalize_kernel<<<fin_blocks, 256, 0, st>>>(mp);
+  carry_overflow_kernel<T><<<148, 256, 0, st>>>(mp);
+  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+}
+
+}  // namespace
+}  // namespace stac
+
+extern "C" {
+
+size_t stac_merge_scratch_bytes(int heads, int tokens_per_head, int buf_cap) {
+  if (heads <= 0 || tokens_per_head <= 0 || buf_cap < 0) return 0;
+  return stac::scratch_layout(heads, tokens_per_head, buf_cap).total;
+}
+
+int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scratch, size_t scratch_bytes,
+                      int list_cap_per_head, int* dev_status, stac_stream_t stream) {
+  if (pool == nullptr || ev == nullptr || scratch == nullptr) return STAC_ERR_BAD_ARG;
+  if (pool->head_dim != 64 || (pool->elem_bytes != 2 && pool->elem_bytes != 4)) return STAC_ERR_BAD_ARG;
+  if (pool->pivot_cap < 1 || pool->pivot_cap > stac::kMaxP || pool->budget_cap < 1 ||
+      pool->budget_cap > stac::kMaxB)
+    return STAC_ERR_BAD_ARG;
+  if (pool->heads <= 0 || pool->voxel_cap <= 0 || pool->voxel_used < 0 || pool->voxel_used > pool->voxel_cap)
+    return STAC_ERR_BAD_ARG;
+  if (ev->tokens_per_head <= 0 || list_cap_per_head < ev->tokens_per_head || list_cap_per_head > 32767)
+    return STAC_ERR_BAD_ARG;
+  const stac::ScratchLayout L = stac::scratch_layout(pool->heads, list_cap_per_head, pool->buf_cap);
+  if (scratch_bytes < L.total) return STAC_ERR_CAPACITY;
+  stac::MergeParams mp;
+  mp.heads = pool->heads; mp.D = pool->head_dim; mp.P = pool->pivot_cap; mp.B = pool->budget_cap;
+  mp.voxel_cap = pool->voxel_cap; mp.voxel_used = pool->voxel_used;
+  mp.sim_thresh = pool->sim_thresh; mp.replace_thresh = pool->replace_thresh; mp.score_thresh = pool->score_thresh;
+  mp.k_src = ev->k; mp.v_src = ev->v; mp.s_src = ev->scores; mp.vx_src = ev->voxel_ids; mp.idx = ev->positions;
+  mp.src_head_stride = ev->kv_head_stride; mp.src_row_stride = ev->kv_row_stride;
+  mp.meta_head_stride = ev->meta_head_stride; mp.n_new = ev->tokens_per_head;
+  mp.buf_K = pool->buf_K; mp.buf_V = pool->buf_V; mp.buf_S = pool->buf_S;
+  mp.buf_row_seg = pool->buf_row_seg; mp.buf_row_cnt = pool->buf_row_cnt; mp.buf_free = pool->buf_free;
+  mp.buf_cap = pool->buf_cap;
+  mp.piv_K = pool->piv_K; mp.piv_V = pool->piv_V; mp.piv_W = pool->piv_W; mp.piv_S = pool->piv_S;
+  mp.piv_C = pool->piv_C; mp.piv_row_seg = pool->piv_row_seg; mp.piv_row_cnt = pool->piv_row_cnt;
+  mp.piv_cap = pool->piv_cap;
+  mp.over_K_in = pool->over_K_in; mp.over_V_in = pool->over_V_in; mp.over_S_in = pool->over_S_in;
+  mp.over_hv_in = pool->over_hv_in; mp.over_start_in = pool->over_start_in;
+  mp.over_K_out = pool->over_K_out; mp.over_V_out = pool->over_V_out; mp.over_S_out = pool->over_S_out;
+  mp.over_hv_out = pool->over_hv_out; mp.over_start_out = pool->over_start_out; mp.over_cap = pool->over_cap;
+  mp.meta = pool->meta;
+  mp.ncap = list_cap_per_head;
+  char* base = static_cast<char*>(scratch);
+  mp.keys_a = reinterpret_cast<unsigned int*>(base + L.keys_a);
+  mp.keys_b = reinterpret_cast<unsigned int*>(base + L.keys_b);
+  mp.vals_a = reinterpret_cast<int*>(base + L.vals_a);
+  mp.vals_b = reinterpret_cast<int*>(base + L.vals_b);
+  mp.n_tok = reinterpret_cast<int*>(base + L.n_tok);
+  mp.n_rows = reinterpret_cast<int*>(base + L.n_rows);
+  mp.row_vx = reinterpret_cast<int*>(base + L.row_vx);
+  mp.row_start = reinterpret_cast<int*>(base + L.row_start);
+  mp.row_info = reinterpret_cast<int4*>(base + L.row_info);
+  mp.row_pref = reinterpret_cast<int4*>(base + L.row_pref);
+  mp.old_dest = reinterpret_cast<short*>(base + L.old_dest);
+  mp.tok_dest = reinterpret_cast<int*>(base + L.tok_dest);
+  mp.tok_sim = reinterpret_cast<float*>(base + L.tok_sim);
+  mp.tok_score = reinterpret_cast<float*>(base + L.tok_score);
+  mp.head_tot = reinterpret_cast<int4*>(base + L.head_tot);
+  mp.head_base = reinterpret_cast<int4*>(base + L.head_base);
+  mp.plan = reinterpret_cast<int*>(base + L.plan);
+  mp.free_stage = reinterpret_cast<int*>(base + L.free_stage);
+  int bits = 1;
+  while ((1ll << bits) < pool->voxel_used) ++bits;
+  mp.passes = (bits + 7) / 8;
+  mp.err = dev_status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pool->elem_bytes == 2) return stac::launch_merge<__nv_bfloat16>(mp, st);
+  return stac::launch_merge<float>(mp, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,221 @@
+// Pivot retrieval: for every pool head, the pivots of the queried voxels ordered by weight W
+// (descending), the first R of them copied out with bias log C.
+//
+// Replaces VoxelKVMerger.retrieve on the reference's Python path (stac/merger.py:1377-1482:
+// gather of all [H, Q*P] pivots, argsort by W, three more gathers, index_put compaction) and
+// MergerWrapper.retrieve_seg with its torch sort (merger-cuda/csrc/merger_wrapper.cu:3148-3221).
+//
+// retrieve_select_kernel  one CTA per head streams the (voxel, slot) candidates of the queried
+//                         voxels, keeps the best R in shared memory (threshold filter + bitonic
+//                         sort of 64-bit keys = weight bits | inverted candidate index, so equal
+//                         weights resolve to the earlier candidate) and writes their order.
+// retrieve_gather_kernel  copies K/V of the selected pivots with 16-byte vectors, writes mask
+//                         and bias, zero-fills the padding.
+#include "common.cuh"
+#include "stac_internal.h"
+
+namespace stac {
+namespace {
+
+constexpr int kSelCap = 8192;   // shared-memory candidate buffer (64-bit keys)
+constexpr int kSelBatch = 1024; // voxels examined per iteration (one per thread)
+
+__device__ __forceinline__ unsigned int wkey(float f) {
+  const unsigned int u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ void bitonic_desc(unsigned long long* a, int n) {
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const unsigned long long x = a[i], y = a[ixj];
+          const bool desc = (i & k) == 0;
+          if ((x < y) == desc) {
+            a[i] = y;
+            a[ixj] = x;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+struct RetrieveParams {
+  int heads, D, P, voxel_cap, voxel_used, R;
+  const int* query_ids;    // ascending voxel ids
+  const int* query_count;  // device scalar
+  const int* piv_row_seg;
+  const int* piv_row_cnt;
+  const void* piv_K;
+  const void* piv_V;
+  const float* piv_W;
+  const float* piv_C;
+  int* sel;        // [heads][R] candidate index q*P + slot, -1 = padding
+  void* out_K;     // [heads][R][D]
+  void* out_V;
+  unsigned char* out_mask;  // [heads][R]
+  float* out_bias;          // [heads][R]
+  int* out_idx;             // [heads][R][2] (voxel, slot) or nullptr
+};
+
+__global__ void __launch_bounds__(1024, 1) retrieve_select_kernel(const RetrieveParams p) {
+  extern __shared__ unsigned long long cand[];  // kSelCap keys
+  __shared__ int warp_sums[32];
+  __shared__ int sh_count;
+  __shared__ unsigned int sh_thr;
+  const int h = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int Q = *p.query_count;
+  const int R = p.R;
+  if (threadIdx.x == 0) {
+    sh_count = 0;
+    sh_thr = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < Q; base += kSelBatch) {
+    const int q = base + threadIdx.x;
+    unsigned long long mine[4];
+    int n_mine = 0;
+    if (q < Q) {
+      const int v = p.query_ids[q];
+      if (v >= 0 && v < p.voxel_used) {
+        const long long r = static_cast<long long>(h) * p.voxel_cap + v;
+        const int n = p.piv_row_cnt[r];
+        const unsigned int thr = sh_thr;
+        for (int s = 0; s < n && s < 4; ++s) {
+          const int seg = p.piv_row_seg[r * p.P + s];
+          const unsigned int wk = wkey(p.piv_W[seg]);
+          if (wk > thr || sh_count < R) {
+            mine[n_mine++] = (static_cast<unsigned long long>(wk) << 32) |
+                             static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<unsigned int>(q * p.P + s));
+          }
+        }
+      }
+    }
+    // ordered append
+    int incl = n_mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += t;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int off = sh_count + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - n_mine;
+    for (int s = 0; s < n_mine; ++s) cand[off + s] = mine[s];
+    __syncthreads();
+    if (threadIdx.x == 0) sh_count += warp_sums[31];
+    __syncthreads();
+    // keep the buffer small enough for the next batch
+    if (sh_count + kSelBatch * 4 > kSelCap) {
+      const int cnt = sh_count;
+      int np2 = 1;
+      while (np2 < cnt) np2 <<= 1;
+      for (int i = cnt + threadIdx.x; i < np2; i += blockDim.x) cand[i] = 0ull;
+      __syncthreads();
+      bitonic_desc(cand, np2);
+      if (threadIdx.x == 0) {
+        sh_count = min(cnt, R);
+        if (cnt >= R) sh_thr = static_cast<unsigned int>(cand[R - 1] >> 32);
+      }
+      __syncthreads();
+    }
+  }
+  {
+    const int cnt = sh_count;
+    int np2 = 1;
+    while (np2 < cnt) np2 <<= 1;
+    for (int i = cnt + threadIdx.x; i < np2; i += blockDim.x) cand[i] = 0ull;
+    __syncthreads();
+    if (cnt > 1) bitonic_desc(cand, np2);
+    const int keep = min(cnt, R);
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+      int c = -1;
+      if (i < keep) c = static_cast<int>(0xFFFFFFFFu - static_cast<unsigned int>(cand[i] & 0xFFFFFFFFull));
+      p.sel[static_cast<long long>(h) * R + i] = c;
+    }
+  }
+}
+
+__global__ void retrieve_gather_kernel(const RetrieveParams p, int vec_per_token) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int h = blockIdx.y;
+  const long long tok = gid / vec_per_token;
+  const int part = static_cast<int>(gid % vec_per_token);
+  if (tok >= p.R) return;
+  const long long o = static_cast<long long>(h) * p.R + tok;
+  const int c = p.sel[o];
+  uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+  int seg = -1, v = -1, slot = -1;
+  if (c >= 0) {
+    v = p.query_ids[c / p.P];
+    slot = c % p.P;
+    seg = p.piv_row_seg[(static_cast<long long>(h) * p.voxel_cap + v) * p.P + slot];
+    kv = static_cast<const uint4*>(p.piv_K)[static_cast<long long>(seg) * vec_per_token + part];
+    vv = static_cast<const uint4*>(p.piv_V)[static_cast<long long>(seg) * vec_per_token + part];
+  }
+  static_cast<uint4*>(p.out_K)[o * vec_per_token + part] = kv;
+  static_cast<uint4*>(p.out_V)[o * vec_per_token + part] = vv;
+  if (part == 0) {
+    p.out_mask[o] = c >= 0 ? 1 : 0;
+    p.out_bias[o] = c >= 0 ? logf(fmaxf(p.piv_C[seg], 1e-9f)) : -INFINITY;
+    if (p.out_idx != nullptr) {
+      p.out_idx[2 * o] = v;
+      p.out_idx[2 * o + 1] = slot;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace stac
+
+extern "C" {
+
+int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_count, int retrieve_size, int* sel,
+                  void* out_K, void* out_V, uint8_t* out_mask, float* out_bias, int* out_idx, stac_stream_t stream) {
+  if (pool == nullptr || query_ids == nullptr || query_count == nullptr || sel == nullptr || out_K == nullptr ||
+      out_V == nullptr || out_mask == nullptr || out_bias == nullptr)
+    return STAC_ERR_BAD_ARG;
+  if (retrieve_size <= 0 || retrieve_size > 4096 || pool->pivot_cap > 4) return STAC_ERR_BAD_ARG;
+  const int token_bytes = pool->head_dim * pool->elem_bytes;
+  if (token_bytes % 16 != 0) return STAC_ERR_BAD_ARG;
+  stac::RetrieveParams rp;
+  rp.heads = pool->heads; rp.D = pool->head_dim; rp.P = pool->pivot_cap; rp.voxel_cap = pool->voxel_cap;
+  rp.voxel_used = pool->voxel_used; rp.R = retrieve_size;
+  rp.query_ids = query_ids; rp.query_count = query_count;
+  rp.piv_row_seg = pool->piv_row_seg; rp.piv_row_cnt = pool->piv_row_cnt;
+  rp.piv_K = pool->piv_K; rp.piv_V = pool->piv_V; rp.piv_W = pool->piv_W; rp.piv_C = pool->piv_C;
+  rp.sel = sel; rp.out_K = out_K; rp.out_V = out_V; rp.out_mask = out_mask; rp.out_bias = out_bias;
+  rp.out_idx = out_idx;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  static bool attr_done = false;
+  const int smem = stac::kSelCap * 8;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(stac::retrieve_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
+      return STAC_ERR_CUDA;
+    attr_done = true;
+  }
+  stac::retrieve_select_kernel<<<pool->heads, 1024, smem, st>>>(rp);
+  const int vpt = token_bytes / 16;
+  const long long total = static_cast<long long>(retrieve_size) * vpt;
+  dim3 grid(static_cast<unsigned>((total + 255) / 256), pool->heads);
+  stac::retrieve_gather_kernel<<<grid, 256, 0, st>>>(rp, vpt);
+  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+}
+
+}  // extern "C"

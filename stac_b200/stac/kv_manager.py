@@ -1,0 +1,302 @@
+"""Sliding-window KV manager behind the reference's ``KVManager`` interface
+(stac/kv_manager.py:13-530): a pre-allocated hot cache [L, H, T_buf, D] with token indices,
+recent + pinned pruning with gather-compaction.
+
+Differences that do not change results: the cache is double-buffered so compaction is a pure
+gather into the second buffer (the attributes ``key_cache_hot`` / ``value_cache_hot`` always
+name the live one); attention reads the [H, T, D] cache in place.  The reference's CPU spill
+ring for buffers longer than ``gpu_limit`` frames (stac/kv_manager.py:244-283) is not provided:
+appending beyond the GPU buffer raises.
+"""
+
+import gc
+import logging
+import warnings
+from typing import List, Optional, Tuple, Union
+
+import numpy as np
+import torch
+
+from .. import _lib, ops
+from .._lib import check, ptr, stream_ptr
+
+logger = logging.getLogger(__name__)
+
+
+class KVManager:
+    def __init__(self, num_layers: int, num_heads: int, head_dim: int, token_per_frame: int,
+                 register_layers: Optional[List[int]] = None, chunk_size: int = 1, buffer_size: int = 8,
+                 recent_size: int = 1, pinned_idx: Optional[List[int]] = None,
+                 dtype: torch.dtype = torch.float16, device: Optional[torch.device] = None,
+                 debug: bool = False, gpu_limit: int = 250, **kwargs):
+        self.num_layers = int(num_layers)
+        self.num_heads = int(num_heads)
+        self.head_dim = int(head_dim)
+        self.token_per_f = int(token_per_frame)
+        self.reserved_buffer_size = int(buffer_size)
+        if register_layers is None:
+            managed = list(range(self.num_layers))
+        else:
+            managed = sorted({l for l in register_layers if 0 <= l < self.num_layers})
+        if len(managed) == 0:
+            raise ValueError("register_layers is empty after filtering valid indices.")
+        self._managed_layers: List[int] = managed
+        self._L_eff = len(managed)
+        self._layer2slot = [-1] * self.num_layers
+        for s, l in enumerate(managed):
+            self._layer2slot[l] = s
+        self.recent_size = int(recent_size)
+        self.cache_size = self.recent_size
+        pinned = [int(i) for i in (pinned_idx or [])]
+        self.pinned_size = len(pinned)
+        self.chunk_size = int(chunk_size)
+        self.hot_size = self.cache_size + self.pinned_size
+        if self.reserved_buffer_size < self.hot_size + self.chunk_size:
+            warnings.warn(f"Warning: buffer_size {self.reserved_buffer_size} is smaller than "
+                          f"hh_size+recent_size+pinned ({self.hot_size}). This may lead to no pruning.")
+            self.reserved_buffer_size = self.hot_size + self.chunk_size
+        self.reserved_buffer_size_cpu = max(self.reserved_buffer_size - gpu_limit, 0)
+        self.reserved_buffer_size = min(self.reserved_buffer_size, gpu_limit)
+        assert self.token_per_f > 0, "token_per_frame must be positive."
+        assert self.recent_size >= 0, "recent_size and hh_size must be non-negative."
+        assert self.cache_size > 0, "At least one of hh_size, recent_size, pinned_idx must be non-zero."
+        self.recent_token_size = int(self.recent_size * self.token_per_f)
+        self.cache_token_size = int(self.cache_size * self.token_per_f)
+        self.reserved_buffer_token_size = int(self.reserved_buffer_size * self.token_per_f)
+        self.reserved_buffer_token_size_cpu = int(self.reserved_buffer_size_cpu * self.token_per_f)
+        self.hot_token_size = int(self.hot_size * self.token_per_f)
+        self.chunk_token_size = int(self.chunk_size * self.token_per_f)
+        tok = []
+        for idx in pinned:
+            if idx < 0:
+                continue
+            tok.extend(range(idx * self.token_per_f, (idx + 1) * self.token_per_f))
+        self._pinned_token_index = torch.tensor(tok, dtype=torch.long)
+        if dtype not in (torch.bfloat16,):
+            raise ValueError("the sm_100a path computes in bfloat16; pass dtype=torch.bfloat16")
+        self.dtype = dtype
+        self.device = torch.device(device) if device is not None else torch.device("cuda")
+        if self.device.type != "cuda":
+            raise _lib.StacError("stac_b200 has no CPU path: a CUDA device is required")
+        self.debug = debug
+        self.key_cache_hot = None
+        self.value_cache_hot = None
+        self._token_indices_hot = None
+        self._offset_hot = None
+        self.use_cpu = False
+        self._status = None
+        self._base_cache = {}
+
+    # ------------------------------------------------------------------ utilities
+    def is_managed(self, layer_idx: int) -> bool:
+        return self._layer2slot[layer_idx] >= 0
+
+    def _to_slot(self, layer_idx: int, *, strict: bool = True) -> int:
+        s = self._layer2slot[layer_idx]
+        if s < 0 and strict:
+            raise ValueError(f"Layer {layer_idx} is not managed by HeavyHittersKV.")
+        return s
+
+    def _layers_to_slots(self, layers: Union[List[int], torch.Tensor]) -> torch.Tensor:
+        if isinstance(layers, torch.Tensor):
+            layers = layers.tolist()
+        return torch.tensor([self._layer2slot[l] for l in layers if self._layer2slot[l] >= 0],
+                            dtype=torch.long, device=self.device)
+
+    # ------------------------------------------------------------------ reset / free
+    def _alloc_cache(self):
+        L, H, T, D = self._L_eff, self.num_heads, self.reserved_buffer_token_size, self.head_dim
+        dev = self.device
+        self._kv = [(torch.empty(L, H, T, D, dtype=self.dtype, device=dev),
+                     torch.empty(L, H, T, D, dtype=self.dtype, device=dev)) for _ in range(2)]
+        self._ti = [torch.full((L, H, T), -1, dtype=torch.long, device=dev) for _ in range(2)]
+        self._cur = 0
+        self._bind()
+
+    def _bind(self):
+        self.key_cache_hot, self.value_cache_hot = self._kv[self._cur]
+        self._token_indices_hot = self._ti[self._cur]
+
+    def reset(self):
+        self._processed_frames = 0
+        self._status = ops.DeviceStatus(self.device)
+        self._alloc_cache()
+        self._offset_hot = [0] * self._L_eff
+        self._offset_hot_cpu = [0] * self._L_eff
+
+    def free(self):
+        self._processed_frames = 0
+        self.key_cache_hot = self.value_cache_hot = self._token_indices_hot = None
+        self._kv = self._ti = None
+        self._offset_hot = None
+        self._offset_hot_cpu = None
+        gc.collect()
+        torch.cuda.synchronize(self.device)
+        torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ append
+    def append_kv(self, key_states, value_states, layer_idx: int):
+        """key_states, value_states: [B, H, T_new, D] with B == 1."""
+        B, H, new_T, D = key_states.shape
+        assert H == self.num_heads and D == self.head_dim, "Incompatible head or head_dim."
+        assert B == 1, "Batch size > 1 not supported in append_kv()."
+        assert new_T % self.token_per_f == 0, "T_new must be a multiple of token_per_frame in append_kv()."
+        slot = self._to_slot(layer_idx, strict=True)
+        old_T = self._offset_hot[slot]
+        if old_T + new_T > self.reserved_buffer_token_size:
+            raise RuntimeError(f"hot cache overflow ({old_T}+{new_T} > {self.reserved_buffer_token_size} tokens); "
+                               "the CPU spill ring of the reference is not provided")
+        self.key_cache_hot[slot, :, old_T:old_T + new_T, :].copy_(key_states[0])
+        self.value_cache_hot[slot, :, old_T:old_T + new_T, :].copy_(value_states[0])
+        self._offset_hot[slot] = old_T + new_T
+        F_new = new_T // self.token_per_f
+        ids = torch.arange(self._processed_frames * self.token_per_f,
+                           (self._processed_frames + F_new) * self.token_per_f, device=self.device)
+        self._token_indices_hot[slot, :, old_T:old_T + new_T].copy_(ids.expand(H, -1))
+        if slot == self._L_eff - 1:
+            self._processed_frames += F_new
+
+    @torch.no_grad()
+    def prefill(self, query_states, key_states, value_states, layer_idx: int):
+        """query/key/value [B, T, H, D] (stac/kv_manager.py:195-224)."""
+        B, T, H, D = query_states.shape
+        assert H == self.num_heads and D == self.head_dim and B == 1
+        assert T % self.token_per_f == 0
+        self.reset()
+        slot = self._to_slot(layer_idx, strict=True)
+        self.key_cache_hot[slot, :, :T, :].copy_(key_states[0].transpose(0, 1))
+        self.value_cache_hot[slot, :, :T, :].copy_(value_states[0].transpose(0, 1))
+        self._offset_hot[slot] = T
+        out = self.decode_sparse_attn(query_states, layer_idx)
+        F = T // self.token_per_f
+        self._processed_frames = F
+        self._token_indices_hot[slot, :, :T].copy_(torch.arange(T, device=self.device).expand(H, -1))
+        return out
+
+    # ------------------------------------------------------------------ attention
+    def _attend(self, query_states, slot, k_ret=None, v_ret=None, bias_ret=None, T_ret=0,
+                want_colsum=False, subsample_ratio=1.0):
+        B, Tq, H, D = query_states.shape
+        assert H == self.num_heads and D == self.head_dim, "Incompatible head or head_dim."
+        assert B == 1, "Batch size > 1 not supported in decode_sparse_attn()."
+        assert query_states.is_cuda, "decode_sparse_attn requires CUDA tensors"
+        assert query_states.dtype == torch.bfloat16, "q must be bf16"
+        q = query_states[0]
+        if q.stride(2) != 1 or q.stride(1) != D:
+            q = q.contiguous()
+        T_main = self._offset_hot[slot]
+        out, _, colsum = ops.attn_colsum(q, self.key_cache_hot[slot], self.value_cache_hot[slot], T_main,
+                                         k_ret, v_ret, bias_ret, T_ret, subsample_ratio=subsample_ratio,
+                                         want_colsum=want_colsum, status=self._status)
+        return out.unsqueeze(0), colsum
+
+    @torch.no_grad()
+    def decode_sparse_attn(self, query_states: torch.Tensor, layer_idx: int) -> torch.Tensor:
+        """Plain attention over the hot cache; query_states [B, Tq, H, D] -> [B, Tq, H, D]."""
+        slot = self._to_slot(layer_idx, strict=True)
+        out, _ = self._attend(query_states, slot)
+        return out
+
+    # ------------------------------------------------------------------ prune
+    def _base_mask(self, T):
+        """uint8 [T] device mask of the always-kept positions (pinned < T and the recent tail),
+        plus its size (stac/kv_manager.py:381-391, stac/h2o.py:279-295)."""
+        hit = self._base_cache.get(T)
+        if hit is None:
+            m = np.zeros(T, np.uint8)
+            m[T - min(self.recent_token_size, T):] = 1
+            pinned = self._pinned_token_index.numpy()
+            pinned = pinned[(pinned >= 0) & (pinned < T)]
+            m[pinned] = 1
+            hit = (torch.from_numpy(m).to(self.device), int(m.sum()))
+            self._base_cache = {T: hit}
+        return hit
+
+    def _select(self, scores_rows, row_stride, n_rows, T, n_keep):
+        base, _ = self._base_mask(T)
+        keep = torch.empty((n_rows, n_keep), dtype=torch.int32, device=self.device)
+        drop = torch.empty((n_rows, T - n_keep), dtype=torch.int32, device=self.device)
+        check(_lib.lib().stac_h2o_select(ptr(scores_rows), row_stride, n_rows, ptr(base), T, n_keep,
+                                         ptr(keep), ptr(drop), stream_ptr()), "stac_h2o_select")
+        return keep, drop
+
+    @torch.no_grad()
+    def prune_kv(self):
+        """Keep pinned + recent tokens, compact (stac/kv_manager.py:362-441), all layers at once."""
+        L, H = self._L_eff, self.num_heads
+        T = self._offset_hot[0]
+        if T == 0 or any(o != T for o in self._offset_hot):
+            if T == 0:
+                return
+            raise RuntimeError(f"prune_kv requires equal live lengths, got {self._offset_hot}")
+        if T <= max(self.hot_token_size, self.recent_token_size):
+            return
+        _, n_base = self._base_mask(T)
+        if n_base == T:
+            return
+        zeros = torch.zeros((L * H, T), dtype=torch.float32, device=self.device)
+        keep, _ = self._select(zeros, T, L * H, T, n_base)
+        self._compact(keep)
+
+    def _compact(self, keep):
+        """Gather-compaction into the idle buffers, then swap."""
+        L, H, Tb, D = self._L_eff, self.num_heads, self.reserved_buffer_token_size, self.head_dim
+        n_keep = keep.shape[1]
+        src, dst = self._cur, 1 - self._cur
+        zs = getattr(self, "_zero_meta", None)
+        if zs is None:
+            zs = [torch.zeros((L, H, Tb), dtype=torch.float32, device=self.device) for _ in range(2)]
+            self._zero_meta = zs
+        check(_lib.lib().stac_compact(ptr(keep), L * H, n_keep, Tb, D, 2,
+                                      ptr(self._kv[src][0]), ptr(self._kv[src][1]),
+                                      ptr(self._kv[dst][0]), ptr(self._kv[dst][1]),
+                                      ptr(self._ti[src]), ptr(self._ti[dst]),
+                                      ptr(zs[0]), ptr(zs[1]), ptr(zs[0]), ptr(zs[1]), None, None,
+                                      stream_ptr()), "stac_compact")
+        self._cur = dst
+        self._bind()
+        self._offset_hot = [n_keep] * L
+
+    @torch.no_grad()
+    def retrieve_kv(self, layer_idx: int, **kwargs) -> Tuple[int, int]:
+        raise NotImplementedError("retrieve_kv() is not implemented for HeavyHittersKV.")
+
+    @torch.no_grad()
+    def append_positions(self, new_positions: torch.Tensor, new_pos_mask: torch.Tensor):
+        raise NotImplementedError("append_positions() is not implemented for HeavyHittersKV.")
+
+    # ------------------------------------------------------------------ public API
+    def get_token_indices(self) -> torch.Tensor:
+        return self._token_indices_hot.clone().cpu()
+
+    def get_layers(self) -> List[int]:
+        return self._managed_layers.copy()
+
+    def get_kv(self):
+        return self.key_cache_hot.clone().cpu(), self.value_cache_hot.clone().cpu()
+
+    def get_offset(self) -> List[int]:
+        return self._offset_hot.copy()
+
+    def get_offset_cpu(self) -> List[int]:
+        return [0] * self._L_eff
+
+    def get_cpu_memory_usage(self) -> Tuple[float, float]:
+        return 0.0, 0.0
+
+    def get_memory_usage(self) -> Tuple[float, float]:
+        eb = torch.finfo(self.dtype).bits // 8
+        mb = 1024.0 ** 2
+        usage = sum(2 * self.num_heads * T * self.head_dim * eb for T in self._offset_hot) / mb
+        alloc = self._L_eff * 2 * self.reserved_buffer_token_size * self.num_heads * self.head_dim * eb / mb
+        return usage, alloc
+
+    def get_memory_details(self) -> dict:
+        used, alloc = self.get_memory_usage()
+        return {"total_usage": used, "total_alloc": alloc, "temporal_cache_usage": used,
+                "temporal_cache_alloc": alloc, "spatial_cache_usage": 0.0}
+
+    def check_status(self):
+        """Synchronise and raise if any kernel reported a device-side error."""
+        if self._status is not None:
+            self._status.raise_if_set(type(self).__name__)

@@ -1,0 +1,350 @@
+"""Voxel KV memory behind the reference's ``VoxelKVMerger`` interface (stac/merger.py:50-1602)
+with the production allocator (``allocator="segment"``, ``seg_size=1``).
+
+The object owns the pool tensors (the reference's MergerWrapper pattern,
+merger-cuda/csrc/merger_wrapper.h:4-9): segment storage for buffered tokens and pivots, the
+row -> segment maps, the free list and the carried overflow lists.  All arithmetic happens in
+libstac_b200.so (stac_merge_insert, stac_retrieve); this class sizes the arrays, keeps their
+pointers in a ``stac_pool`` struct and reads the pool counters back after each insert.
+"""
+
+import ctypes
+
+import torch
+
+from .. import _lib
+from .._lib import META_BUF_FREE_LEN, META_BUF_TOP, META_BUF_USED, META_OVER_COUNT, META_PIV_TOP, META_PIV_USED
+from .._lib import StacEvicted, StacPool, check, ptr, stream_ptr
+
+MAX_LIST = 32767
+
+
+class VoxelKVMerger:
+    def __init__(self, num_heads: int, head_dim: int, init_voxels: int = 0, pivot_cap: int = 4,
+                 budget_cap: int = 32, sim_thresh: float = 0.75, replace_thresh: float = 0.5,
+                 score_thresh: float = 0.2, dtype: torch.dtype = torch.float16,
+                 device=torch.device("cuda"), weight_fn=None, backend: str = "cuda", status=None, **kwargs):
+        if head_dim != 64:
+            raise ValueError("the sm_100a voxel memory supports head_dim 64 only")
+        if not (1 <= int(pivot_cap) <= 4 and 1 <= int(budget_cap) <= 8):
+            raise ValueError("supported capacities: pivot_cap <= 4, budget_cap <= 8 "
+                             f"(got {pivot_cap}, {budget_cap})")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("pool dtype must be bfloat16 or float32")
+        if weight_fn is not None:
+            raise ValueError("custom weight_fn is not supported; the merge weight is exp(similarity)")
+        alloc = kwargs.get("allocator", "segment")
+        if alloc != "segment" or int(kwargs.get("seg_size", 1)) != 1:
+            # the other allocators of the reference differ only in slot numbering
+            self._alloc_note = f"allocator={alloc!r} mapped to segment/seg_size=1"
+        assert replace_thresh <= sim_thresh
+        self.H, self.D, self.P, self.B = int(num_heads), int(head_dim), int(pivot_cap), int(budget_cap)
+        self.dtype, self.device = dtype, torch.device(device)
+        self.debug = kwargs.get("debug", False)
+        self.backend = backend
+        self.sim_threshold = float(sim_thresh)
+        self.replace_threshold = float(replace_thresh)
+        self.score_threshold = float(score_thresh)
+        self._voxel_alloc = max(1, int(init_voxels))
+        self._voxel_offset = 0
+        self._token_count = 0
+        self._status = status
+        self._slab_cap = int(kwargs.get("slab_cap", 1024))
+        dev = self.device
+        H, P, B, D = self.H, self.P, self.B, self.D
+        V = self._voxel_alloc
+        self._buf_row_seg = torch.full((H, V, B), -1, dtype=torch.int32, device=dev)
+        self._buf_row_cnt = torch.zeros((H, V), dtype=torch.int32, device=dev)
+        self._piv_row_seg = torch.full((H, V, P), -1, dtype=torch.int32, device=dev)
+        self._piv_row_cnt = torch.zeros((H, V), dtype=torch.int32, device=dev)
+        self._buf_cap = 0
+        self._piv_cap = 0
+        self._buf_K = self._buf_V = self._buf_S = self._buf_free = None
+        self._piv_K = self._piv_V = self._piv_W = self._piv_S = self._piv_C = None
+        self._grow_buf(max(1024, self._slab_cap * B))
+        self._grow_piv(max(1024, V))
+        self._over = [self._new_over(1), self._new_over(1)]
+        self._over_cur = 0
+        self._over_cap = 1
+        self._meta = torch.zeros(_lib.META_SIZE, dtype=torch.int32, device=dev)
+        self._meta_host = [0] * _lib.META_SIZE
+        self._over_max_head = 0
+        self._scratch = None
+        self._ret_sel = None
+
+    # ------------------------------------------------------------------ storage
+    def _new_over(self, cap):
+        dev = self.device
+        return {"K": torch.empty((cap, self.D), dtype=self.dtype, device=dev),
+                "V": torch.empty((cap, self.D), dtype=self.dtype, device=dev),
+                "S": torch.empty(cap, dtype=torch.float32, device=dev),
+                "hv": torch.empty((cap, 2), dtype=torch.int32, device=dev),
+                "start": torch.zeros(self.H + 1, dtype=torch.int32, device=dev)}
+
+    @staticmethod
+    def _extend(old, shape, dtype, device, fill=None):
+        new = torch.empty(shape, dtype=dtype, device=device) if fill is None else \
+            torch.full(shape, fill, dtype=dtype, device=device)
+        if old is not None and old.numel() > 0:
+            new[: old.shape[0]].copy_(old)
+        return new
+
+    def _grow_buf(self, cap):
+        if cap <= self._buf_cap:
+            return
+        dev = self.device
+        self._buf_K = self._extend(self._buf_K, (cap, self.D), self.dtype, dev)
+        self._buf_V = self._extend(self._buf_V, (cap, self.D), self.dtype, dev)
+        self._buf_S = self._extend(self._buf_S, (cap,), torch.float32, dev)
+        self._buf_free = self._extend(self._buf_free, (cap,), torch.int32, dev)
+        self._buf_cap = cap
+
+    def _grow_piv(self, cap):
+        if cap <= self._piv_cap:
+            return
+        dev = self.device
+        self._piv_K = self._extend(self._piv_K, (cap, self.D), self.dtype, dev)
+        self._piv_V = self._extend(self._piv_V, (cap, self.D), self.dtype, dev)
+        self._piv_W = self._extend(self._piv_W, (cap,), torch.float32, dev)
+        self._piv_S = self._extend(self._piv_S, (cap,), torch.float32, dev)
+        self._piv_C = self._extend(self._piv_C, (cap,), torch.float32, dev)
+        self._piv_cap = cap
+
+    def _grow_rows(self, V_new):
+        dev = self.device
+        H, P, B = self.H, self.P, self.B
+        V_old = self._buf_row_cnt.shape[1]
+        if V_new <= V_old:
+            return
+        brs = torch.full((H, V_new, B), -1, dtype=torch.int32, device=dev)
+        brc = torch.zeros((H, V_new), dtype=torch.int32, device=dev)
+        prs = torch.full((H, V_new, P), -1, dtype=torch.int32, device=dev)
+        prc = torch.zeros((H, V_new), dtype=torch.int32, device=dev)
+        brs[:, :V_old].copy_(self._buf_row_seg)
+        brc[:, :V_old].copy_(self._buf_row_cnt)
+        prs[:, :V_old].copy_(self._piv_row_seg)
+        prc[:, :V_old].copy_(self._piv_row_cnt)
+        self._buf_row_seg, self._buf_row_cnt, self._piv_row_seg, self._piv_row_cnt = brs, brc, prs, prc
+
+    def reset(self):
+        pass
+
+    def update_voxel_zones(self, voxel_zones):
+        """Morton zones only steer the reference's CUDA pivot allocator; nothing to do here."""
+
+    def ensure_capacity(self, V_needed: int):
+        """Voxel rows grow by x1.5 as in stac/merger.py:218-239."""
+        self._voxel_offset = max(int(V_needed), self._voxel_offset)
+        if V_needed <= self._voxel_alloc:
+            return
+        V_new = max(int(V_needed), int(self._voxel_alloc * 1.5))
+        while V_new < V_needed:
+            V_new = int(V_new * 1.5)
+        self._voxel_alloc = V_new
+        self._grow_rows(V_new)
+
+    def _pool_struct(self):
+        cur, nxt = self._over[self._over_cur], self._over[1 - self._over_cur]
+        s = StacPool()
+        s.heads, s.head_dim, s.elem_bytes = self.H, self.D, 2 if self.dtype == torch.bfloat16 else 4
+        s.pivot_cap, s.budget_cap = self.P, self.B
+        s.voxel_cap, s.voxel_used = int(self._buf_row_cnt.shape[1]), int(self._voxel_offset)
+        s.sim_thresh, s.replace_thresh, s.score_thresh = (self.sim_threshold, self.replace_threshold,
+                                                          self.score_threshold)
+        s.buf_K, s.buf_V, s.buf_S = self._buf_K.data_ptr(), self._buf_V.data_ptr(), self._buf_S.data_ptr()
+        s.buf_row_seg, s.buf_row_cnt = self._buf_row_seg.data_ptr(), self._buf_row_cnt.data_ptr()
+        s.buf_free, s.buf_cap = self._buf_free.data_ptr(), self._buf_cap
+        s.piv_K, s.piv_V = self._piv_K.data_ptr(), self._piv_V.data_ptr()
+        s.piv_W, s.piv_S, s.piv_C = self._piv_W.data_ptr(), self._piv_S.data_ptr(), self._piv_C.data_ptr()
+        s.piv_row_seg, s.piv_row_cnt, s.piv_cap = (self._piv_row_seg.data_ptr(), self._piv_row_cnt.data_ptr(),
+                                                   self._piv_cap)
+        s.over_K_in, s.over_V_in, s.over_S_in = cur["K"].data_ptr(), cur["V"].data_ptr(), cur["S"].data_ptr()
+        s.over_hv_in, s.over_start_in = cur["hv"].data_ptr(), cur["start"].data_ptr()
+        s.over_K_out, s.over_V_out, s.over_S_out = nxt["K"].data_ptr(), nxt["V"].data_ptr(), nxt["S"].data_ptr()
+        s.over_hv_out, s.over_start_out = nxt["hv"].data_ptr(), nxt["start"].data_ptr()
+        s.over_cap = self._over_cap
+        s.meta = self._meta.data_ptr()
+        return s
+
+    def _read_meta(self):
+        meta = self._meta.cpu().tolist()
+        start = self._over[self._over_cur]["start"].cpu()
+        self._meta_host = meta
+        self._over_max_head = int((start[1:] - start[:-1]).max().item()) if self.H > 0 else 0
+
+    # ------------------------------------------------------------------ insert
+    @torch.no_grad()
+    def insert_evicted(self, k_cache, v_cache, scores, voxel_ids, positions, tokens_per_head, num_voxels):
+        """Evicted tokens read in place: token j of pool head h sits at position
+        positions[h, j] of k_cache/v_cache [H, T, D], scores/voxel_ids [H, T]
+        (positions None = the first tokens_per_head positions)."""
+        H, D = self.H, self.D
+        Tn = int(tokens_per_head)
+        if Tn == 0:
+            return
+        assert k_cache.dtype == self.dtype and v_cache.dtype == self.dtype
+        assert k_cache.stride(-1) == 1 and k_cache.stride(1) == D and v_cache.stride() == k_cache.stride()
+        assert scores.dtype == torch.float32 and voxel_ids.dtype == torch.int32
+        assert scores.stride(1) == 1 and voxel_ids.stride() == scores.stride()
+        self._token_count += H * Tn
+        self.ensure_capacity(num_voxels)
+        over_in = self._meta_host[META_OVER_COUNT]
+        E = H * Tn + over_in
+        # worst-case needs of this call (see the capacity notes in the module docstring)
+        need_buf = self._meta_host[META_BUF_TOP] + max(0, E - self._meta_host[META_BUF_FREE_LEN])
+        if need_buf > self._buf_cap:
+            self._grow_buf(max(need_buf, int(self._buf_cap * 1.5)))
+        need_piv = self._meta_host[META_PIV_TOP] + (self._meta_host[META_BUF_USED] + E) // self.B + 1
+        if need_piv > self._piv_cap:
+            self._grow_piv(max(need_piv, int(self._piv_cap * 1.5)))
+        if E > self._over_cap:
+            cap = max(E, int(self._over_cap * 1.5))
+            cur = self._over[self._over_cur]
+            new_cur = self._new_over(cap)
+            n = over_in
+            for f in ("K", "V", "S", "hv"):
+                new_cur[f][:n].copy_(cur[f][:n])
+            new_cur["start"].copy_(cur["start"])
+            self._over[self._over_cur] = new_cur
+            self._over[1 - self._over_cur] = self._new_over(cap)
+            self._over_cap = cap
+        ncap = Tn + self._over_max_head
+        if ncap > MAX_LIST:
+            raise _lib.StacError(f"{ncap} tokens for one pool head in one call; the limit is {MAX_LIST}")
+        need = _lib.lib().stac_merge_scratch_bytes(H, ncap, self._buf_cap)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(int(need * 1.25), dtype=torch.uint8, device=self.device)
+        pool = self._pool_struct()
+        ev = StacEvicted()
+        ev.k, ev.v = k_cache.data_ptr(), v_cache.data_ptr()
+        ev.kv_head_stride, ev.kv_row_stride = k_cache.stride(0), k_cache.stride(1)
+        ev.scores, ev.voxel_ids = scores.data_ptr(), voxel_ids.data_ptr()
+        ev.meta_head_stride = scores.stride(0)
+        ev.positions = positions.data_ptr() if positions is not None else None
+        ev.tokens_per_head = Tn
+        if positions is not None:
+            assert positions.dtype == torch.int32 and positions.is_contiguous()
+            assert tuple(positions.shape) == (H, Tn)
+        st = _lib.lib().stac_merge_insert(ctypes.byref(pool), ctypes.byref(ev), ptr(self._scratch),
+                                          self._scratch.numel(), ncap,
+                                          ptr(self._status.word) if self._status is not None else None,
+                                          stream_ptr())
+        check(st, "stac_merge_insert")
+        self._over_cur = 1 - self._over_cur
+        self._read_meta()
+        if self._status is not None:
+            self._status.raise_if_set("voxel merge")
+
+    @torch.no_grad()
+    def insert_and_merge(self, K_new, V_new, S_new, I_new, VX_new, num_voxels: int, mode: str = "default"):
+        """Reference signature (stac/merger.py:1157-1255): K_new/V_new [H,Tn,D], S_new [H,Tn]
+        fp32, I_new ignored, VX_new [H,Tn] voxel ids."""
+        H, Tn, D = K_new.shape
+        assert H == self.H and D == self.D
+        assert V_new.shape == K_new.shape and S_new.shape == VX_new.shape == (H, Tn)
+        if Tn == 0:
+            return {}
+        self.insert_evicted(K_new.to(self.dtype).contiguous(), V_new.to(self.dtype).contiguous(),
+                            S_new.to(torch.float32).contiguous(), VX_new.to(torch.int32).contiguous(),
+                            None, Tn, num_voxels)
+        return {"init_time": 0.0, "append_time": 0.0, "merge_all2one_time": 0.0, "merge_one2one_time": 0.0}
+
+    # ------------------------------------------------------------------ retrieve
+    @torch.no_grad()
+    def retrieve_device(self, query_ids, query_count, retrieve_size, want_idx=False):
+        """query_ids int32 ascending (device), query_count int32 [1] (device).  Returns
+        K, V [H,R,D], mask bool [H,R], bias fp32 [H,R] (and idx int32 [H,R,2])."""
+        R = int(retrieve_size)
+        if not (0 < R <= 4096):
+            raise ValueError("retrieve_size must be in 1..4096")
+        dev = self.device
+        K = torch.empty((self.H, R, self.D), dtype=self.dtype, device=dev)
+        V = torch.empty((self.H, R, self.D), dtype=self.dtype, device=dev)
+        M = torch.empty((self.H, R), dtype=torch.uint8, device=dev)
+        Bz = torch.empty((self.H, R), dtype=torch.float32, device=dev)
+        idx = torch.empty((self.H, R, 2), dtype=torch.int32, device=dev) if want_idx else None
+        if self._ret_sel is None or self._ret_sel.numel() < self.H * R:
+            self._ret_sel = torch.empty(self.H * R, dtype=torch.int32, device=dev)
+        pool = self._pool_struct()
+        st = _lib.lib().stac_retrieve(ctypes.byref(pool), ptr(query_ids), ptr(query_count), R,
+                                      ptr(self._ret_sel), ptr(K), ptr(V), ptr(M), ptr(Bz), ptr(idx),
+                                      stream_ptr())
+        check(st, "stac_retrieve")
+        out = (K, V, M.bool(), Bz)
+        return out + (idx,) if want_idx else out
+
+    @torch.no_grad()
+    def retrieve(self, voxel_ids=None, return_buf: bool = False, retrieve_size=None, want_idx=False):
+        """Reference signature (stac/merger.py:1377-1543) for retrieve_size > 0: fixed-size
+        output, pivots ordered by W descending, bias log C, padding -inf.  With a positive
+        retrieve_size the reference never returns buffer tokens, whatever return_buf says."""
+        req = int(retrieve_size) if retrieve_size is not None else -1
+        if req <= 0:
+            raise NotImplementedError("unbounded retrieval (retrieve_size <= 0) is not provided by the "
+                                      "sm_100a path; pass a positive retrieve_size")
+        dev = self.device
+        if voxel_ids is None:
+            ids = torch.arange(int(self._voxel_offset), device=dev, dtype=torch.int32)
+        else:
+            ids = torch.unique(voxel_ids.to(device=dev, dtype=torch.int64))
+            ids = ids[(ids >= 0) & (ids < self._voxel_offset)].to(torch.int32).contiguous()
+        cnt = torch.tensor([ids.numel()], dtype=torch.int32, device=dev)
+        if ids.numel() == 0:
+            ids = torch.zeros(1, dtype=torch.int32, device=dev)
+        return self.retrieve_device(ids, cnt, req, want_idx)
+
+    # ------------------------------------------------------------------ stats
+    def _pool_counts(self):
+        m = self._meta_host
+        return m[META_BUF_USED], self._buf_cap, m[META_PIV_USED], self._piv_cap
+
+    def info(self) -> dict:
+        buf_data, buf_alloc, piv_data, piv_alloc = self._pool_counts()
+        tc = float(self._token_count + 1e-6)
+        return dict(head_dim=self.D, num_heads=self.H, pivot_capacity=self.P, buffer_capacity=self.B,
+                    used_voxels=self._voxel_offset, allocated_voxels=self._voxel_alloc,
+                    token_count=self._token_count, merge_compress_ratio=piv_data / tc,
+                    best_compress_ratio=(piv_data + buf_data) / tc,
+                    real_compress_ratio=(piv_alloc + buf_alloc) / tc,
+                    pivot_pool_used=piv_data, pivot_pool_alloc=piv_alloc,
+                    buffer_pool_used=buf_data, buffer_pool_alloc=buf_alloc)
+
+    def memory(self) -> dict:
+        buf_data, buf_alloc, piv_data, piv_alloc = self._pool_counts()
+        kvb = 2 if self.dtype == torch.bfloat16 else 4
+        mb = 1024 ** 2
+        return dict(buffer_used_mem=buf_data * (self.D * 2 * kvb + 4) / mb,
+                    buffer_alloc_mem=buf_alloc * (self.D * 2 * kvb + 4) / mb,
+                    pivot_used_mem=piv_data * (self.D * 2 * kvb + 8) / mb,
+                    pivot_alloc_mem=piv_alloc * (self.D * 2 * kvb + 8) / mb)
+
+    # ------------------------------------------------------------------ test hooks
+    def snapshot(self):
+        """Host copies of the slot maps and pool contents over the used voxels (tests)."""
+        V = int(self._voxel_offset)
+        m = self._meta.cpu().tolist()
+        cur = self._over[self._over_cur]
+        n_over = m[META_OVER_COUNT]
+        brs = self._buf_row_seg[:, :V].cpu()
+        prs = self._piv_row_seg[:, :V].cpu()
+
+        def gather(pool, seg):
+            idx = seg.clamp(min=0).long()
+            out = pool.float().cpu()[idx]
+            mask = (seg >= 0)
+            return out * mask.reshape(mask.shape + (1,) * (out.dim() - mask.dim())).float()
+
+        return {
+            "buf_offset": self._buf_row_cnt[:, :V].cpu().numpy(), "buf_seg": brs.numpy(),
+            "piv_offset": self._piv_row_cnt[:, :V].cpu().numpy(), "piv_seg": prs.numpy(),
+            "buf_top": m[META_BUF_TOP], "piv_top": m[META_PIV_TOP],
+            "buf_free": self._buf_free[: m[META_BUF_FREE_LEN]].cpu().numpy(),
+            "buf_K": gather(self._buf_K, brs).numpy(), "buf_V": gather(self._buf_V, brs).numpy(),
+            "buf_S": gather(self._buf_S, brs).numpy(),
+            "piv_K": gather(self._piv_K, prs).numpy(), "piv_V": gather(self._piv_V, prs).numpy(),
+            "piv_W": gather(self._piv_W, prs).numpy(), "piv_S": gather(self._piv_S, prs).numpy(),
+            "piv_C": gather(self._piv_C, prs).numpy(),
+            "over_hv": cur["hv"][:n_over].cpu().numpy().astype("int64"),
+            "over_K": cur["K"][:n_over].float().cpu().numpy(), "over_V": cur["V"][:n_over].float().cpu().numpy(),
+            "over_S": cur["S"][:n_over].cpu().numpy(),
+        }

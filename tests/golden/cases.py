@@ -36,11 +36,24 @@ MERGER = {
 }
 
 
+# GPU-vs-oracle cases (no reference fixture needed: the oracle is pinned by the cases above)
+MERGER_GPU = {
+    "gpu_f32": dict(_M, H=4, D=64, N=1536, steps=10, init_voxels=32, dtype="f32", seed=51, n_sites=96),
+    "gpu_bf16": dict(_M, H=4, D=64, N=1536, steps=10, init_voxels=32, dtype="bf16", seed=52, n_sites=96),
+    "gpu_wide": dict(_M, H=6, D=64, N=4000, steps=4, init_voxels=4096, dtype="bf16", seed=53, n_sites=2500),
+    "gpu_crowded": dict(_M, H=2, D=64, N=3000, steps=5, init_voxels=8, dtype="f32", seed=54, n_sites=3),
+}
+
+
+def merger_config(name):
+    return MERGER[name] if name in MERGER else MERGER_GPU[name]
+
+
 def merger_inputs(name):
     """Yields (points [N,3], K [H,N,D], V [H,N,D], S [H,N]) per step.  Points visit a slowly
     growing set of sites so that buffers fill, pivots appear, saturate and get re-merged;
     part of the keys cluster around a per-site direction so the similarity merge triggers."""
-    c = MERGER[name]
+    c = merger_config(name)
     rs = np.random.RandomState(c["seed"])
     H, D, N = c["H"], c["D"], c["N"]
     sites = (rs.rand(c["n_sites"] * 3, 3).astype(np.float32) - 0.5) * np.float32(1.5)
@@ -75,9 +88,14 @@ MANAGER = dict(L=2, H=2, D=16, tpf=21, special=5, chunk=2, window=3, hh=1, buffe
                seed=31)
 
 
-def manager_inputs():
+MANAGER_GPU = dict(L=2, H=3, D=64, tpf=41, special=5, chunk=2, window=3, hh=1, buffer=7, steps=18,
+                   voxel_size=0.05, init_voxels=32, retrieval=1, retrieve_steps=(6, 8, 10, 12, 14, 16),
+                   seed=61)
+
+
+def manager_inputs(c=None):
     """Yields per chunk: k, v [L,H,Tn,D], column sums [L,H,T_buf], points [Tn,3], mask [Tn]."""
-    c = MANAGER
+    c = MANAGER if c is None else c
     rs = np.random.RandomState(c["seed"])
     L, H, D, tpf = c["L"], c["H"], c["D"], c["tpf"]
     Tn = c["chunk"] * tpf

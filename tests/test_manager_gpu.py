@@ -1,0 +1,179 @@
+"""The drop-in manager classes on the GPU against the oracle manager, chunk by chunk, in the
+reference's call order.  Column sums are injected through `_update_scores` (as the reference's
+own CPU trace does) so that both sides select from identical scores; a second test drives the
+real attention kernel and checks the scores it produces."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle.attention import attn_colsum as oracle_attn
+from oracle.manager import StacManager
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _make(c, **over):
+    from stac_b200.stac import STACVoxelKV
+    kw = dict(num_layers=c["L"], num_heads=c["H"], head_dim=c["D"], token_per_frame=c["tpf"],
+              buffer_size=c["buffer"], chunk_size=c["chunk"], recent_size=c["window"], pinned_idx=[0],
+              hh_size=c["hh"], temperature=0.9, device=torch.device(DEV), dtype=torch.bfloat16,
+              voxel_size=c["voxel_size"], init_voxels=c["init_voxels"], voxel_buf_cap=8, voxel_piv_cap=4,
+              voxel_backend="cuda", sim_threshold=0.8, replace_threshold=0.8, score_threshold=0.2,
+              slab_growth=1024, slab_cap=10000, seg_size=1, retrieval_size=c["retrieval"],
+              allocator="segment", attn_backend="cuda", some_unknown_cli_flag=1)
+    kw.update(over)
+    kv = STACVoxelKV(**kw)
+    kv.reset()
+    return kv
+
+
+def test_trace_matches_oracle():
+    c = cases.MANAGER_GPU
+    kv = _make(c)
+    ref = StacManager(c["L"], c["H"], c["D"], c["tpf"], c["buffer"], chunk_size=c["chunk"],
+                      recent_size=c["window"], pinned_idx=(0,), hh_size=c["hh"], temperature=0.9,
+                      voxel_size=c["voxel_size"], init_voxels=c["init_voxels"],
+                      retrieval_size=c["retrieval"], dtype="bf16")
+    L, H, D = c["L"], c["H"], c["D"]
+    retrieved = 0
+    for step, (k, v, cs, pts, mask) in enumerate(cases.manager_inputs(c)):
+        Tq = k.shape[2]
+        for l in range(L):
+            tk = torch.from_numpy(k[l]).to(torch.bfloat16)
+            tv = torch.from_numpy(v[l]).to(torch.bfloat16)
+            kv.append_kv(tk[None].to(DEV), tv[None].to(DEV), l)
+            ref.append_kv(tk.float().numpy(), tv.float().numpy(), l)
+            T_live = kv._offset_hot[l]
+            kv._last_query_offset[l] = Tq
+            kv._update_scores(torch.from_numpy(cs[l][:, :T_live])[None, :, None, :].to(DEV), l)
+            ref.update_scores(cs[l][:, :T_live], l, Tq)
+        kv.append_positions(torch.from_numpy(pts).to(DEV), torch.from_numpy(mask).to(DEV))
+        ref.append_positions(pts, mask)
+        if ref.recent_ids is not None:
+            ids, cnt = kv._recent_voxel_ids
+            n = int(cnt.item())
+            assert np.array_equal(ids[:n].cpu().numpy().astype(np.int64), np.unique(ref.recent_ids)), step
+        if step in c["retrieve_steps"]:
+            for l in range(L):
+                kv.retrieve_kv(l, return_buf=True)
+            ref.ret = None
+            ref.retrieve(return_buf=True)
+            R = kv.retrieval_token_size
+            assert kv.get_retrieval_size() == [R] * L
+            Kr, Vr, Br, Mr, _ = ref.ret
+            gk = torch.stack(kv.key_cache_retrieval).float().cpu().numpy().reshape(L * H, R, D)
+            gb = torch.stack(kv._bias_retrieval).cpu().numpy().reshape(L * H, R)
+            fin = np.isfinite(Br)
+            assert np.array_equal(np.isfinite(gb), fin), step
+            np.testing.assert_allclose(gb[fin], Br[fin], rtol=1e-5, atol=1e-6)
+            np.testing.assert_allclose(gk, Kr, rtol=8e-3, atol=1e-3)
+            retrieved += int(fin.sum())
+        kv.prune_kv()
+        ref.prune()
+        T = ref.off[0]
+        assert kv.get_offset() == [T] * L, step
+        assert np.array_equal(kv._token_indices_hot[:, :, :T].cpu().numpy(), ref.TI[:, :, :T]), step
+        assert np.array_equal(kv._token_voxel_indices[:, :, :T].cpu().numpy(), ref.VX[:, :, :T]), step
+        assert np.array_equal(kv._scores_hot[:, :, :T].cpu().numpy(), ref.S[:, :, :T]), step
+        assert np.array_equal(kv.key_cache_hot[:, :, :T].float().cpu().numpy(), ref.K[:, :, :T]), step
+        assert bool((kv._token_indices_hot[:, :, T:] == -1).all())
+        snap = kv._vstore.snapshot()
+        sm = ref.merger.slot_map()
+        for key in ("buf_offset", "buf_seg", "piv_offset", "piv_seg"):
+            assert np.array_equal(snap[key], sm[key]), (step, key)
+        assert np.array_equal(snap["buf_free"], sm["buf_free"]), step
+    kv.check_status()
+    assert retrieved > 0
+    det = kv.get_memory_details()
+    assert det["voxel_pivot_usage"] > 0 and det["total_usage"] > 0
+    assert kv.get_merger_info()["used_voxels"] == ref.merger.V_used
+    kv.free()
+
+
+def test_attention_drives_scores():
+    """decode_sparse_attn over [hot | retrieved] updates the hot scores with the column sums."""
+    c = dict(cases.MANAGER_GPU)
+    kv = _make(c)
+    L, H, D, tpf = c["L"], c["H"], c["D"], c["tpf"]
+    rs = np.random.RandomState(4)
+    Tn = c["chunk"] * tpf
+    k = torch.from_numpy(rs.randn(H, Tn, D).astype(np.float32)).to(torch.bfloat16)
+    v = torch.from_numpy(rs.randn(H, Tn, D).astype(np.float32)).to(torch.bfloat16)
+    q = torch.from_numpy(rs.randn(Tn, H, D).astype(np.float32)).to(torch.bfloat16)
+    kv.append_kv(k[None].to(DEV), v[None].to(DEV), 0)
+    # fake retrieved pivots for layer 0
+    R = 50
+    kr = torch.from_numpy(rs.randn(H, R, D).astype(np.float32)).to(torch.bfloat16)
+    vr = torch.from_numpy(rs.randn(H, R, D).astype(np.float32)).to(torch.bfloat16)
+    br = np.log(rs.randint(1, 9, size=(H, R)).astype(np.float32))
+    br[:, -7:] = -np.inf
+    kv.key_cache_retrieval[0], kv.value_cache_retrieval[0] = kr.to(DEV), vr.to(DEV)
+    kv._bias_retrieval[0] = torch.from_numpy(br).to(DEV)
+    kv._offset_retrieval[0] = R
+    out = kv.decode_sparse_attn(q[None].to(DEV), 0)
+    kv.check_status()
+    k_all = torch.cat([k, kr], 1).float().numpy().transpose(1, 0, 2)
+    v_all = torch.cat([v, vr], 1).float().numpy().transpose(1, 0, 2)
+    b_all = np.concatenate([np.zeros((H, Tn), np.float32), br], 1)
+    o_ref, _, cs_ref = oracle_attn(q.float().numpy(), k_all, v_all, b_all)
+    assert out.shape == (1, Tn, H, D)
+    assert np.abs(out[0].float().cpu().numpy() - o_ref).max() <= 2e-2
+    s_ref = cs_ref[:, :Tn] * np.float32(Tn) / np.float32(Tn)
+    np.testing.assert_allclose(kv.get_scores()[0, :, :Tn].cpu().numpy(), s_ref, rtol=1e-3, atol=1e-6)
+    assert float(kv._scores_hot_count[0, :, :Tn].min()) == 1.0
+    kv.free()
+
+
+def test_window_manager_and_h2o_manager():
+    """KVManager (recent + pinned) and HeavyHittersKV (no voxel memory) prune like the oracle."""
+    from oracle.manager import h2o_keep_indices
+    from stac_b200.stac import HeavyHittersKV, KVManager
+    L, H, D, tpf = 2, 2, 64, 16
+    rs = np.random.RandomState(2)
+    common = dict(num_layers=L, num_heads=H, head_dim=D, token_per_frame=tpf, chunk_size=1, recent_size=2,
+                  pinned_idx=[0], device=torch.device(DEV), dtype=torch.bfloat16)
+    win = KVManager(buffer_size=4, **common)
+    hh = HeavyHittersKV(buffer_size=5, hh_size=1, temperature=0.9, **common)
+    win.reset()
+    hh.reset()
+    scores_ref = np.zeros((L, H, 5 * tpf), np.float32)
+    ti_ref = np.full((L, H, 5 * tpf), -1, np.int64)
+    T_ref, last = 0, 0
+    for frame in range(7):
+        for l in range(L):
+            k = torch.from_numpy(rs.randn(1, H, tpf, D).astype(np.float32)).to(torch.bfloat16).to(DEV)
+            win.append_kv(k, k, l)
+            hh.append_kv(k, k, l)
+        ti_ref[:, :, T_ref:T_ref + tpf] = np.arange(frame * tpf, (frame + 1) * tpf)
+        T_ref += tpf
+        q = torch.from_numpy(rs.randn(1, tpf, H, D).astype(np.float32)).to(torch.bfloat16).to(DEV)
+        assert win.decode_sparse_attn(q, 0).shape == (1, tpf, H, D)
+        for l in range(L):
+            cs = rs.rand(H, T_ref).astype(np.float32)
+            hh._last_query_offset[l] = tpf
+            hh._update_scores(torch.from_numpy(cs)[None, :, None, :].to(DEV), l)
+            s = cs * np.float32(T_ref) / np.float32(tpf)
+            scores_ref[l, :, last:T_ref] = s[:, last:]
+            scores_ref[l, :, :last] = scores_ref[l, :, :last] * np.float32(0.9) + s[:, :last]
+        last = T_ref
+        win.prune_kv()
+        hh.prune_kv()
+        keep = h2o_keep_indices(scores_ref, T_ref, 2 * tpf, np.arange(tpf), tpf, 4 * tpf)
+        if keep is not None:
+            Tp = keep.shape[-1]
+            ti_ref[:, :, :Tp] = np.take_along_axis(ti_ref[:, :, :T_ref], keep, 2)
+            ti_ref[:, :, Tp:] = -1
+            scores_ref[:, :, :Tp] = np.take_along_axis(scores_ref[:, :, :T_ref], keep, 2)
+            scores_ref[:, :, Tp:] = 0
+            T_ref = Tp
+            last = min(last, Tp)
+        assert hh.get_offset() == [T_ref] * L
+        assert np.array_equal(hh.get_token_indices().numpy(), ti_ref)
+        assert np.array_equal(hh.get_scores().cpu().numpy(), scores_ref)
+        assert win.get_offset()[0] <= 3 * tpf + tpf
+    assert win.get_offset() == [3 * tpf] * L
+    first = win.get_token_indices()[0, 0, : 3 * tpf].numpy()
+    assert np.array_equal(first[:tpf], np.arange(tpf)) and np.array_equal(first[tpf:], np.arange(5 * tpf, 7 * tpf))
