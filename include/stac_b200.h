@@ -208,6 +208,29 @@ int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_
                   int* sel, void* out_K, void* out_V, uint8_t* out_mask, float* out_bias, int* out_idx,
                   stac_stream_t stream);
 
+/* Same computation and arguments as stac_attn_colsum, minus the workspace: the per-row
+ * scratch sits in a fixed 512 KB array inside the library image on each GPU, so this call
+ * never asks the driver for memory.  It has no counterpart in the reference.  It is meant
+ * for hosts that cannot allocate at call time: a serving process that handed the whole GPU
+ * to its own arena at start-up (a cudaMalloc would fail or fragment it), or a loop that cannot
+ * tolerate the device-wide synchronisation an allocation implies.
+ *   - M * H must not exceed STAC_ATTN_STATIC_MAX_ROWS, else STAC_ERR_CAPACITY.
+ *   - The first call on a device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's values;
+ *     nothing needs clearing because each call writes every entry it later reads, but two
+ *     calls that overlap on the GPU (different streams) race on it.  Serialise them. */
+#define STAC_ATTN_STATIC_MAX_ROWS 131072 /* floats of fixed scratch = max M * H */
+
+int stac_attn_colsum_noalloc(const void* q, int64_t q_row_stride,
+                             const void* k_hot, const void* v_hot, int64_t hot_row_stride, int64_t hot_head_stride, int T_hot,
+                             const void* k_ret, const void* v_ret, int64_t ret_row_stride, int64_t ret_head_stride, int T_ret,
+                             const float* bias_ret, int64_t bias_head_stride,
+                             void* out, int64_t out_row_stride,
+                             float* lse, float* colsum, int64_t colsum_head_stride,
+                             int M, int H, int D, float scale, float subsample_ratio,
+                             int* dev_status, stac_stream_t stream);
+
 /* Self-test of the bounded-wait mechanism: launches one CTA that waits on a barrier nothing
  * ever completes; the wait gives up after about `max_polls` polls, writes
  * STAC_DEV_TEST_TIMEOUT to *dev_status and the kernel exits normally. */

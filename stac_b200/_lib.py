@@ -56,6 +56,9 @@ SIGNATURES = {
     "stac_attn_colsum": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_i64, c_int, c_void_p, c_void_p,
                                  c_i64, c_i64, c_int, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p, c_i64,
                                  c_int, c_int, c_int, c_f32, c_f32, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "stac_attn_colsum_noalloc": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_i64, c_int, c_void_p,
+                                         c_void_p, c_i64, c_i64, c_int, c_void_p, c_i64, c_void_p, c_i64, c_void_p,
+                                         c_void_p, c_i64, c_int, c_int, c_int, c_f32, c_f32, c_void_p, c_void_p]),
     "stac_selftest_bounded_wait": (c_int, [c_int, c_void_p, c_void_p]),
     "stac_voxel_scratch_bytes": (c_size_t, [c_int]),
     "stac_voxel_hash_clear": (c_int, [c_void_p, c_i64, c_void_p]),

@@ -620,3 +620,67 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
 }
 
 }  // namespace stac
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant: the row log-sum-exp scratch lives in a fixed array inside the
+// loaded module instead of a caller-provided workspace.
+// ---------------------------------------------------------------------------------------
+namespace stac {
+namespace {
+
+// One float per (head, query row).  Every GPU that loads the library carries these 512 KB
+// until the process exits.
+static __device__ __align__(256) float g_static_lse2[STAC_ATTN_STATIC_MAX_ROWS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_lse2_ptr[kMaxDevices] = {nullptr};
+
+// The array's name is only a host-side handle; the kernels need its device address, which
+// differs per GPU.  Resolved once per device, with that device current.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return STAC_ERR_CUDA;
+  if (g_static_lse2_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_lse2) != cudaSuccess || ptr == nullptr) return STAC_ERR_CUDA;
+    g_static_lse2_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_static_lse2_ptr[dev];
+  return STAC_OK;
+}
+
+}  // namespace
+}  // namespace stac
+
+extern "C" int stac_attn_colsum_noalloc(const void* q, int64_t q_row_stride, const void* k_hot, const void* v_hot,
+                                        int64_t hot_row_stride, int64_t hot_head_stride, int T_hot,
+                                        const void* k_ret, const void* v_ret, int64_t ret_row_stride,
+                                        int64_t ret_head_stride, int T_ret, const float* bias_ret,
+                                        int64_t bias_head_stride, void* out, int64_t out_row_stride, float* lse,
+                                        float* colsum, int64_t colsum_head_stride, int M, int H, int D, float scale,
+                                        float subsample_ratio, int* dev_status, stac_stream_t stream) {
+  if (q == nullptr || out == nullptr) return STAC_ERR_BAD_ARG;
+  if (!(subsample_ratio > 0.f && subsample_ratio <= 1.f)) return STAC_ERR_BAD_ARG;
+  if (M <= 0 || H <= 0) return STAC_ERR_BAD_ARG;
+  // the fixed scratch holds H * M floats at most
+  if (static_cast<long long>(M) * H > STAC_ATTN_STATIC_MAX_ROWS) return STAC_ERR_CAPACITY;
+  if ((q_row_stride % 8) || (out_row_stride % 8) || (hot_head_stride % 8) || (ret_head_stride % 8) ||
+      (hot_row_stride % 8) || (ret_row_stride % 8))
+    return STAC_ERR_BAD_ARG;
+  float* scratch = nullptr;
+  const int rc = stac::static_scratch_for_current_device(&scratch);
+  if (rc != STAC_OK) return rc;
+  stac::AttnArgs a;
+  a.q = q; a.q_row_stride = q_row_stride;
+  a.k_hot = k_hot; a.v_hot = v_hot; a.hot_row_stride = hot_row_stride; a.hot_head_stride = hot_head_stride;
+  a.T_hot = T_hot;
+  a.k_ret = k_ret; a.v_ret = v_ret; a.ret_row_stride = ret_row_stride; a.ret_head_stride = ret_head_stride;
+  a.T_ret = T_ret;
+  a.bias_ret = bias_ret; a.bias_head_stride = bias_head_stride;
+  a.out = out; a.out_row_stride = out_row_stride;
+  a.lse = lse; a.colsum = colsum; a.colsum_head_stride = colsum_head_stride;
+  a.M = M; a.H = H; a.D = D; a.scale = scale; a.subsample_ratio = subsample_ratio;
+  // Every entry of the scratch that the column-sum pass reads (rows < M of each head) is
+  // written by the forward pass of this same call, so nothing has to be cleared first.
+  return stac::attn_colsum_launch(a, scratch, dev_status, reinterpret_cast<cudaStream_t>(stream));
+}
