@@ -212,6 +212,22 @@ class Stream:
         self.h2d, self.d2h = h2d, d2h
 
 
+def max_over_ranks(ms, device=None):
+    """Timed-region length of the job = the slowest rank's (device-timed) milliseconds."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(ms)
+    t = torch.tensor([float(ms)], device=device if device is not None else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def job_throughput(frames_per_rank, ms, world):
+    """Whole-job frames/s: every rank streams `frames_per_rank` frames in `ms` (max over ranks)."""
+    return frames_per_rank * world / (ms / 1e3)
+
+
 def attn_flops(M, N, r=1.0):
     return (4.0 + 2.0 * r) * CFG["heads"] * M * N * CFG["head_dim"]
 
@@ -253,12 +269,7 @@ def run_ours(args):
                 stream.step(pts_dev[i][0], pts_dev[i][1], time_kernels=timed)
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return max_over_ranks(e0.elapsed_time(e1), dev)
 
     run_phase(c["prefill_chunks"], False, False)   # fill the hot cache, start eviction + retrieval
     run_phase(W, False, False)                     # warm-up
@@ -270,9 +281,8 @@ def run_ours(args):
     ms_e2e = run_phase(K, True, False)             # timed, host buffers
     stream.kv.check_status()
 
-    frames = c["chunk"] * K * world
-    value = frames / (ms_dev / 1e3)
-    e2e = frames / (ms_e2e / 1e3)
+    value = job_throughput(c["chunk"] * K, ms_dev, world)
+    e2e = job_throughput(c["chunk"] * K, ms_e2e, world)
     # roofline of the dominant kernel pair (attention forward + column sums), per call
     att_ms, att_fl = [], []
     for e0, e1, M, N in stream.attn_events:

@@ -1,0 +1,117 @@
+"""CPU-side checks: the C ABI library loads and exports every declared symbol, the product
+refuses to run without a GPU (no CPU fallback), bench helpers, and the multi-rank timing logic
+on two gloo ranks."""
+
+import os
+import re
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "stac_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(stac_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import __graft_entry__
+    __graft_entry__.build()
+    from stac_b200 import _lib
+    import ctypes
+    names = _declared_functions()
+    assert len(names) >= 15
+    handle = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(handle, n), f"{n} declared in include/stac_b200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+    lib = _lib.lib()
+    assert lib.stac_abi_version() == 1
+    assert lib.stac_status_string(1) == b"bad argument"
+    assert lib.stac_attn_workspace_bytes(1041, 16) == 1041 * 16 * 4
+    assert lib.stac_merge_scratch_bytes(4, 100, 1000) > 0
+    assert lib.stac_voxel_scratch_bytes(10) == 176
+
+
+def test_struct_layout_matches_header():
+    import ctypes
+    from stac_b200 import _lib
+    # 10 4-byte fields, 6 pointers + int (+pad), 7 pointers + int (+pad), 10 pointers, int (+pad), pointer
+    assert ctypes.sizeof(_lib.StacPool) == 40 + 6 * 8 + 8 + 7 * 8 + 8 + 10 * 8 + 8 + 8
+    assert ctypes.sizeof(_lib.StacEvicted) == 8 * 8 + 8
+
+
+def test_product_has_no_cpu_path():
+    import torch
+    from stac_b200 import _lib
+    from stac_b200.stac import STACVoxelKV
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    with pytest.raises(_lib.StacError):
+        STACVoxelKV(num_layers=1, num_heads=2, head_dim=64, token_per_frame=8, buffer_size=4,
+                    device=torch.device("cpu"), dtype=torch.bfloat16)
+    import stac_b200.stac.stac_voxel as sv
+    src = open(sv.__file__).read() + open(os.path.join(ROOT, "stac_b200", "ops.py")).read()
+    assert "oracle" not in src
+
+
+def test_manager_rejects_unsupported_config():
+    import torch
+    from stac_b200.stac.merger import VoxelKVMerger
+    with pytest.raises(ValueError):
+        VoxelKVMerger(4, 64, budget_cap=32, dtype=torch.bfloat16, device="cpu")
+    with pytest.raises(ValueError):
+        VoxelKVMerger(4, 128, budget_cap=8, dtype=torch.bfloat16, device="cpu")
+
+
+def test_bench_helpers():
+    sys.path.insert(0, ROOT)
+    import bench
+    pts = bench.synth_points(3, seed=1)
+    pts2 = bench.synth_points(3, seed=1)
+    tpf, ck = bench.CFG["tpf"], bench.CFG["chunk"]
+    assert pts[0][0].shape == (ck * tpf, 3) and pts[0][1].shape == (ck * tpf,)
+    assert all(np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]) for a, b in zip(pts, pts2))
+    assert not pts[0][1][:5].any() and not pts[0][1][tpf:tpf + 5].any()     # special tokens masked
+    z = pts[1][0][pts[1][1]]
+    assert np.isfinite(z).all()
+    due = [i for i in range(12) if bench.retrieval_due(i)]
+    assert due == [5, 7, 9, 11]
+    assert bench.attn_flops(1041, 10376) == 6 * 16 * 1041 * 10376 * 64
+    assert bench.job_throughput(32, 1000.0, 8) == 256.0
+
+
+def _rank_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    import bench
+    dist.barrier()
+    ms = bench.max_over_ranks(100.0 + 50.0 * rank)
+    q.put((rank, ms, bench.job_throughput(16, ms, world)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_timing_is_max_over_ranks():
+    """world_size 2 on gloo: each rank streams independently; the job time is the slower rank's."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 1000
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert [r[1] for r in res] == [150.0, 150.0]
+    assert all(abs(r[2] - 32 / 0.15) < 1e-9 for r in res)
