@@ -332,6 +332,101 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------ microbenchmarks
+def run_microbench_attn(args):
+    """BASELINE config 2: bf16 q [1041,16,64] against Lk keys; prints one JSON line per run with
+    TFLOP/s counted as (4+2r)*H*M*N*D.  Used for kernel profiling; not the headline line."""
+    import torch
+    from stac_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    H, D, M, Lk = CFG["heads"], CFG["head_dim"], args.m, args.lk
+    n_ret = min(args.pivots, Lk)
+    T_hot = Lk - n_ret
+    q = (torch.randn(M, H, D, device=dev) / 8).to(torch.bfloat16)
+    sets = []
+    for _ in range(3):   # rotate inputs so that K/V do not stay in L2 between iterations
+        k = (torch.randn(H, Lk, D, device=dev) / 8).to(torch.bfloat16)
+        v = (torch.randn(H, Lk, D, device=dev) / 8).to(torch.bfloat16)
+        sets.append((k, v))
+    bias = torch.log(torch.randint(1, 9, (H, max(n_ret, 1)), device=dev).float())
+    bias[torch.rand(H, max(n_ret, 1), device=dev) < 0.25] = float("-inf")
+    st = ops.DeviceStatus(dev)
+
+    def call(i):
+        k, v = sets[i % 3]
+        if n_ret:
+            return ops.attn_colsum(q, k, v, T_hot, k[:, T_hot:], v[:, T_hot:], bias, n_ret, status=st)
+        return ops.attn_colsum(q, k, v, Lk, status=st)
+
+    for i in range(max(args.warmup, 3)):
+        call(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    st.raise_if_set("attention microbench")
+    ms = e0.elapsed_time(e1) / args.steps
+    tf = attn_flops(M, Lk) / (ms / 1e3) / 1e12
+    print(json.dumps({"metric": "attn_colsum_tflops", "value": round(tf, 2), "unit": "TFLOP/s",
+                      "ms_per_call": round(ms, 4), "steps": args.steps,
+                      "config": {"workload": f"config2 attention microbench M={M} Lk={Lk} pivots={n_ret} H=16 D=64 bf16"}}))
+
+
+def run_microbench_merge(args):
+    """Merge + retrieve on config-3-like shapes (384 pool heads, bf16, T_d tokens per head per
+    step drawn around a smooth surface); prints GB/s with E*(4*D*e+12) algorithmic bytes."""
+    import torch
+    from stac_b200 import ops
+    from stac_b200.stac.merger import VoxelKVMerger
+    from stac_b200.stac.voxel import BinaryVoxel
+    dev = torch.device("cuda", 0)
+    c = CFG
+    LH, D, Td = c["layers"] * c["heads"], c["head_dim"], args.m
+    st = ops.DeviceStatus(dev)
+    vm = BinaryVoxel(c["voxel_size"], dev, status=st)
+    mg = VoxelKVMerger(LH, D, init_voxels=c["init_voxels"], pivot_cap=4, budget_cap=8, sim_thresh=0.8,
+                       replace_thresh=0.8, score_thresh=0.2, dtype=torch.bfloat16, device=dev, status=st)
+    torch.manual_seed(0)
+    n_steps = args.warmup + args.steps
+    chunks = synth_points((n_steps * Td + c["chunk"] * c["tpf"] - 1) // (c["chunk"] * c["tpf"]) + 1, seed=0)
+    allpts = np.concatenate([p for p, _ in chunks])
+    allmask = np.concatenate([m for _, m in chunks])
+    K = (torch.randn(LH, Td, D, device=dev)).to(torch.bfloat16)
+    V = (torch.randn(LH, Td, D, device=dev)).to(torch.bfloat16)
+    times_m, times_r = [], []
+    for step in range(n_steps):
+        pts = torch.from_numpy(allpts[step * Td:(step + 1) * Td]).to(dev)
+        msk = torch.from_numpy(allmask[step * Td:(step + 1) * Td]).to(dev)
+        ids = vm.upsert_points(pts, msk)
+        VX = ids.view(1, -1).expand(LH, -1).contiguous()
+        S = torch.rand(LH, Td, device=dev)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        mg.insert_evicted(K, V, S, VX, None, Td, vm.get_voxel_num())
+        e[1].record()
+        q_ids, q_cnt = vm.neighbor_ids(ids, 2)
+        mg.retrieve_device(q_ids, q_cnt, 2048)
+        e[2].record()
+        torch.cuda.synchronize()
+        if step >= args.warmup:
+            times_m.append(e[0].elapsed_time(e[1]))
+            times_r.append(e[1].elapsed_time(e[2]))
+    st.raise_if_set("merge microbench")
+    E = LH * Td
+    bytes_m = E * (4 * D * 2 + 12)
+    bytes_r = LH * 2048 * (4 * D * 2 + 5)
+    ms_m, ms_r = float(np.mean(times_m)), float(np.mean(times_r))
+    print(json.dumps({"metric": "merge_hbm_gbs", "value": round(bytes_m / ms_m / 1e6, 1), "unit": "GB/s",
+                      "ms_per_call": round(ms_m, 4), "retrieve_gbs": round(bytes_r / ms_r / 1e6, 1),
+                      "retrieve_ms": round(ms_r, 4), "steps": args.steps, "pool": mg.info(),
+                      "config": {"workload": f"merge microbench: 384 pool heads x {Td} evicted tokens/step, bf16, "
+                                             "synthetic smooth surface, retrieve top-2048"}}))
+
+
 # ------------------------------------------------------------------------------------ CPU arm
 def cpu_step_sample(n_layers, n_heads, state=None, seed=0):
     """One chunk of the same workload through the CPU oracle on a subset of (layers, heads);
@@ -431,8 +526,19 @@ if __name__ == "__main__":
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--microbench", default=None, choices=["attn", "merge"],
+                    help="kernel microbenchmarks used for profiling (not the headline line)")
+    ap.add_argument("--lk", type=int, default=10376, help="attention microbench: number of keys")
+    ap.add_argument("--m", type=int, default=None, help="microbench: query rows (attn) / evicted tokens per head (merge)")
+    ap.add_argument("--pivots", type=int, default=0, help="attention microbench: keys carrying a bias")
     a = ap.parse_args()
-    if a.impl == "reference":
+    if a.microbench == "attn":
+        a.m = a.m or 1041
+        run_microbench_attn(a)
+    elif a.microbench == "merge":
+        a.m = a.m or 8328
+        run_microbench_merge(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

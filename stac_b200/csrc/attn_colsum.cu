@@ -45,8 +45,8 @@ struct FwdSmem {
   uint64_t bar_q;
   uint64_t kv_full[kFwdStages];
   uint64_t kv_empty[kFwdStages];
-  uint64_t s_full[2];
-  uint64_t s_free[2];
+  uint64_t s_full[3];  // S tiles rotate over three TMEM buffers (tile j -> buffer j % 3)
+  uint64_t s_free[3];
   uint64_t p_full[2];
   uint64_t o_full[2];
   uint64_t o_free[2];
@@ -91,9 +91,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.kv_full[s], 1);
       mbar_init(&sm.kv_empty[s], 1);
     }
+    for (int b = 0; b < 3; ++b) {
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.s_free[b], 128);
+    }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(&sm.s_full[g], 1);
-      mbar_init(&sm.s_free[g], 128);
       mbar_init(&sm.p_full[g], 128);
       mbar_init(&sm.o_full[g], 1);
       mbar_init(&sm.o_free[g], 128);
@@ -139,15 +141,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_wait(&sm.bar_q, 0, p.err, DEV_TIMEOUT_TMA);
       const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q));
       auto issue_s = [&](int j) {
-        const int g = j & 1, it = j >> 1, s = j % kFwdStages;
+        const int b = j % 3, round = j / 3, s = j % kFwdStages;
         mbar_wait(&sm.kv_full[s], (j / kFwdStages) & 1, p.err, DEV_TIMEOUT_TMA);
-        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        if (round > 0) mbar_wait(&sm.s_free[b], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         tc_fence_after();
         const uint64_t k_desc = smem_desc_sw128(smem_u32(sm.k[s]));
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk)
-          umma_ss(tmem + g * kBN, q_desc + 2 * kk, k_desc + 2 * kk, idesc_s, kk > 0);
-        umma_commit(&sm.s_full[g]);
+          umma_ss(tmem + b * kBN, q_desc + 2 * kk, k_desc + 2 * kk, idesc_s, kk > 0);
+        umma_commit(&sm.s_full[b]);
       };
       auto issue_pv = [&](int j) {
         const int g = j & 1, it = j >> 1, s = j % kFwdStages;
@@ -158,15 +160,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int kk = 0; kk < kBN / 16; ++kk) {
           const uint64_t a = smem_desc_sw128(smem_u32(sm.p[g]) + (kk >> 2) * kTileBytes) + 2 * (kk & 3);
           const uint64_t b = smem_desc_sw128(smem_u32(sm.v[s]) + kk * 2048);
-          umma_ss(tmem + 2 * kBN + g * kD, a, b, idesc_o, kk > 0);
+          umma_ss(tmem + 3 * kBN + g * kD, a, b, idesc_o, kk > 0);
         }
         umma_commit(&sm.o_full[g]);
         umma_commit(&sm.kv_empty[s]);
       };
-      if (n_tiles > 0) issue_s(0);
+      // S tiles run up to three ahead of the softmax; P V of tile j follows its softmax
+      for (int j = 0; j < 3 && j < n_tiles; ++j) issue_s(j);
       for (int j = 0; j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) issue_s(j + 1);
         issue_pv(j);
+        if (j + 3 < n_tiles) issue_s(j + 3);
       }
     }
   } else {
@@ -181,7 +184,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float acc[kD];
 #pragma unroll
     for (int i = 0; i < kD; ++i) acc[i] = 0.f;
-    uint32_t r[32];
+    uint32_t ra[32], rb[32];
     int it = 0;
     for (int j = g; j < n_tiles; j += 2, ++it) {
       const bool is_ret = j >= n_hot;
@@ -195,36 +198,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         sm.bias2[g][t] = b;
         named_bar_sync(1 + g, 128);
       }
-      mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
+      const int sb = j % 3;
+      mbar_wait(&sm.s_full[sb], (j / 3) & 1, p.err, DEV_TIMEOUT_MMA);
       tc_fence_after();
+      // TMEM loads are double-buffered (ra / rb): the next 32 columns are in flight while the
+      // current ones are processed, and the chain runs through all three phases of a tile.
+      const uint32_t s_addr = tmem + lane_base + sb * kBN;
+      const uint32_t o_addr = tmem + lane_base + 3 * kBN + g * kD;
+      tmem_ld32(s_addr, ra);
+      tmem_ld_wait();
       // pass 1 over the S tile: row maximum in the log2 domain
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld32(tmem + lane_base + g * kBN + c * 32, r);
-        tmem_ld_wait();
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        if (c < 3) {
+          tmem_ld32(s_addr + (c + 1) * 32, nxt);
+        } else if (it > 0) {
+          mbar_wait(&sm.o_full[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
+          tc_fence_after();
+          tmem_ld32(o_addr, nxt);       // first half of the previous P V tile
+        } else {
+          tmem_ld32(s_addr, nxt);       // first columns again, for pass 2
+        }
         if (need_bias) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(r[i]), c2, sm.bias2[g][c * 32 + i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(cur[i]), c2, sm.bias2[g][c * 32 + i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * c2);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]) * c2);
         }
+        tmem_ld_wait();
       }
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2(m_run - m_use);
       // fold the previous P V tile of this warpgroup into the register accumulator
       if (it > 0) {
-        mbar_wait(&sm.o_full[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
-        tc_fence_after();
+        tmem_ld32(o_addr + 32, rb);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld32(tmem + lane_base + 2 * kBN + g * kD + c * 32, r);
-          tmem_ld_wait();
+        for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_prev, __uint_as_float(ra[i]));
+        tmem_ld_wait();
+        tmem_ld32(s_addr, ra);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(acc[32 + i], alpha_prev, __uint_as_float(rb[i]));
+        tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&sm.o_free[g]);
       }
@@ -233,34 +252,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       uint8_t* prow = sm.p[g] + row * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld32(tmem + lane_base + g * kBN + c * 32, r);
-        tmem_ld_wait();
-        float pv[32];
-        if (need_bias) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), c2, sm.bias2[g][c * 32 + i]) - m_use);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), c2, -m_use));
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) rs += pv[i];
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
         // keys c*32 .. c*32+31 -> atom c/2, 16-byte chunks (c&1)*4 .. +3 of this row
         uint8_t* atom = prow + (c >> 1) * kTileBytes;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
+          float pv[8];
+          if (need_bias) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              pv[i] = fast_exp2(fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, sm.bias2[g][c * 32 + q4 * 8 + i]) - m_use);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, -m_use));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) rs += pv[i];
           const int chunk = (c & 1) * 4 + q4;
           uint4 val;
-          val.x = pack_bf16x2(pv[q4 * 8 + 0], pv[q4 * 8 + 1]);
-          val.y = pack_bf16x2(pv[q4 * 8 + 2], pv[q4 * 8 + 3]);
-          val.z = pack_bf16x2(pv[q4 * 8 + 4], pv[q4 * 8 + 5]);
-          val.w = pack_bf16x2(pv[q4 * 8 + 6], pv[q4 * 8 + 7]);
+          val.x = pack_bf16x2(pv[0], pv[1]);
+          val.y = pack_bf16x2(pv[2], pv[3]);
+          val.z = pack_bf16x2(pv[4], pv[5]);
+          val.w = pack_bf16x2(pv[6], pv[7]);
           *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = val;
         }
+        if (c < 3) tmem_ld_wait();
       }
       tc_fence_before();
-      mbar_arrive(&sm.s_free[g]);
+      mbar_arrive(&sm.s_free[sb]);
       l_run = fmaf(l_run, alpha, rs);
       m_run = m_new;
       alpha_prev = alpha;
@@ -270,13 +291,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (it > 0) {
       mbar_wait(&sm.o_full[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
       tc_fence_after();
+      tmem_ld32(tmem + lane_base + 3 * kBN + g * kD, ra);
+      tmem_ld32(tmem + lane_base + 3 * kBN + g * kD + 32, rb);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(tmem + lane_base + 2 * kBN + g * kD + c * 32, r);
-        tmem_ld_wait();
+      for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_prev, __uint_as_float(ra[i]));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
-      }
+      for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(acc[32 + i], alpha_prev, __uint_as_float(rb[i]));
       tc_fence_before();
     }
     // merge the two warpgroups' partial softmax states (warpgroup 1 -> shared -> warpgroup 0)
@@ -325,28 +346,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
-// Column sums.  lse2 holds the row log-sum-exp in the log2 domain for the rows actually
-// used (already gathered when rows are sub-sampled); entries past M_sub are +inf so padded
-// query columns contribute exp2(-inf) = 0.
+// Column sums.  Persistent CTAs walk over work items = (pair of 128-key tiles, head).  For every
+// 128-row query tile the MMA warp computes S^T = K Q^T for both key tiles against the same
+// query tile in shared memory; warpgroup 0 owns the first key tile, warpgroup 1 the second, one
+// key (TMEM lane) per thread, so a thread's column sum never leaves its registers.
+// lse2 holds the row log-sum-exp in the log2 domain; rows past M_sub read as +inf so that
+// padded query columns contribute exp2(-inf) = 0.
 // ---------------------------------------------------------------------------------------
 struct ColSmem {
-  uint8_t k[kTileBytes];
+  uint8_t k[2][2][kTileBytes];        // [item parity][key tile of the pair]
   uint8_t q[kColStages][kTileBytes];
-  float xsum[kBN];
-  uint64_t bar_k;
+  uint64_t k_full[2];
+  uint64_t k_empty[2];
   uint64_t q_full[kColStages];
   uint64_t q_empty[kColStages];
   uint64_t s_full[2];
   uint64_t s_free[2];
   uint32_t tmem_base;
-  alignas(16) float lse2[4];  // flexible: n_q_tiles * 128 floats follow
+  alignas(16) float lse2[4];  // flexible: 2 x n_q_tiles * 128 floats follow (item parity)
 };
 
 struct ColParams {
   int M_sub, H;
   int row_stride;  // query row sub-sampling stride
   int T_hot, T_ret;
-  int n_hot_tiles;
+  int n_hot_tiles, n_tiles;
+  int n_pairs, n_items;
   int n_q_tiles;
   float scale_log2;
   float correction;
@@ -366,34 +391,24 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   ColSmem& sm = *reinterpret_cast<ColSmem*>(align1024(smem_raw));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int j = blockIdx.x;  // key tile over [hot | retrieved]
-  const int h = blockIdx.y;
-  const bool is_ret = j >= p.n_hot_tiles;
-  const int n0 = (is_ret ? j - p.n_hot_tiles : j) * kBN;
-  const int valid = min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0);
   const int nq = p.n_q_tiles;
 
   if (threadIdx.x == 0) {
-    mbar_init(&sm.bar_k, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.k_full[i], 1);
+      mbar_init(&sm.k_empty[i], 1);
+      mbar_init(&sm.s_full[i], 1);
+      mbar_init(&sm.s_free[i], 256);
+    }
     for (int s = 0; s < kColStages; ++s) {
       mbar_init(&sm.q_full[s], 1);
       mbar_init(&sm.q_empty[s], 1);
     }
-    for (int g = 0; g < 2; ++g) {
-      mbar_init(&sm.s_full[g], 1);
-      mbar_init(&sm.s_free[g], 128);
-    }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&sm.tmem_base, 256);
+    tmem_alloc(&sm.tmem_base, 512);
     tmem_relinquish();
-  }
-  // stage the row log-sum-exps of this head (all threads)
-  for (int i = threadIdx.x; i < nq * kBM; i += kColThreads) {
-    float v = INFINITY;
-    if (i < p.M_sub) v = p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(i) * p.row_stride];
-    sm.lse2[i] = v;
   }
   tc_fence_before();
   __syncthreads();
@@ -401,78 +416,123 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tmem = sm.tmem_base;
 
   if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
-      mbar_arrive_expect_tx(&sm.bar_k, kTileBytes);
-      tma_load_3d(sm.k, is_ret ? &tm_k_ret : &tm_k_hot, &sm.bar_k, 0, n0, h);
-      for (int i = 0; i < nq; ++i) {
-        const int s = i % kColStages, round = i / kColStages;
-        if (round > 0) mbar_wait(&sm.q_empty[s], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
-        tma_load_3d(sm.q[s], &tm_q, &sm.q_full[s], 0, h, i * kBM);
+      int qi = 0;
+      int n = 0;
+      for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+        const int pair = item / p.H, h = item % p.H;
+        const int kb = n & 1;
+        if (n >= 2) mbar_wait(&sm.k_empty[kb], ((n >> 1) - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_arrive_expect_tx(&sm.k_full[kb], 2 * kTileBytes);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int j = min(2 * pair + t, p.n_tiles - 1);
+          if (j < p.n_hot_tiles) tma_load_3d(sm.k[kb][t], &tm_k_hot, &sm.k_full[kb], 0, j * kBN, h);
+          else tma_load_3d(sm.k[kb][t], &tm_k_ret, &sm.k_full[kb], 0, (j - p.n_hot_tiles) * kBN, h);
+        }
+        for (int i = 0; i < nq; ++i, ++qi) {
+          const int s = qi % kColStages, round = qi / kColStages;
+          if (round > 0) mbar_wait(&sm.q_empty[s], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
+          tma_load_3d(sm.q[s], &tm_q, &sm.q_full[s], 0, h, i * kBM);
+        }
       }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(kBN, kBM, 0);
-      mbar_wait(&sm.bar_k, 0, p.err, DEV_TIMEOUT_TMA);
-      const uint64_t k_desc = smem_desc_sw128(smem_u32(sm.k));
-      for (int i = 0; i < nq; ++i) {
-        const int g = i & 1, it = i >> 1, s = i % kColStages;
-        mbar_wait(&sm.q_full[s], (i / kColStages) & 1, p.err, DEV_TIMEOUT_TMA);
-        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        tc_fence_after();
-        const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q[s]));
+      int qi = 0, gi = 0, n = 0;
+      for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+        const int kb = n & 1;
+        mbar_wait(&sm.k_full[kb], (n >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
+        const uint64_t ka_desc = smem_desc_sw128(smem_u32(sm.k[kb][0]));
+        const uint64_t kb_desc = smem_desc_sw128(smem_u32(sm.k[kb][1]));
+        for (int i = 0; i < nq; ++i, ++qi, ++gi) {
+          const int s = qi % kColStages;
+          const int g = gi & 1, it = gi >> 1;
+          mbar_wait(&sm.q_full[s], (qi / kColStages) & 1, p.err, DEV_TIMEOUT_TMA);
+          if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          tc_fence_after();
+          const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q[s]));
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk)
-          umma_ss(tmem + g * kBM, k_desc + 2 * kk, q_desc + 2 * kk, idesc, kk > 0);
-        umma_commit(&sm.s_full[g]);
-        umma_commit(&sm.q_empty[s]);
+          for (int kk = 0; kk < kD / 16; ++kk)
+            umma_ss(tmem + g * 256, ka_desc + 2 * kk, q_desc + 2 * kk, idesc, kk > 0);
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk)
+            umma_ss(tmem + g * 256 + 128, kb_desc + 2 * kk, q_desc + 2 * kk, idesc, kk > 0);
+          umma_commit(&sm.s_full[g]);
+          umma_commit(&sm.q_empty[s]);
+        }
+        umma_commit(&sm.k_empty[kb]);
       }
     }
   } else {
-    const int g = (warp - 2) >> 2;
+    // ------------------------------------------------------------------ exponent warpgroups
+    const int w = (warp - 2) >> 2;   // which key tile of the pair
     const int wq = warp & 3;
     const int key = wq * 32 + lane;  // key inside the tile = TMEM lane
+    const int tid = threadIdx.x - 64;  // 0..255
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c2 = p.scale_log2;
-    float b2 = -INFINITY;
-    if (key < valid) b2 = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e : 0.f;
-    float csum = 0.f;
-    uint32_t r[32];
-    int it = 0;
-    for (int i = g; i < nq; i += 2, ++it) {
-      mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
-      tc_fence_after();
-      const float4* l4 = reinterpret_cast<const float4*>(&sm.lse2[i * kBM]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(tmem + lane_base + g * kBM + c * 32, r);
+    uint32_t ra[32], rb[32];
+    int gi = 0, n = 0;
+    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+      const int pair = item / p.H, h = item % p.H;
+      float* lse_s = sm.lse2 + (n & 1) * nq * kBM;
+      for (int i = tid; i < nq * kBM; i += 256) {
+        float v = INFINITY;
+        if (i < p.M_sub)
+          v = p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(i) * p.row_stride];
+        lse_s[i] = v;
+      }
+      named_bar_sync(1, 256);
+      const int j = 2 * pair + w;
+      const bool exists = j < p.n_tiles;
+      const bool is_ret = j >= p.n_hot_tiles;
+      const int n0 = (is_ret ? j - p.n_hot_tiles : j) * kBN;
+      const int valid = exists ? min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0) : 0;
+      float b2 = -INFINITY;
+      if (key < valid) b2 = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e : 0.f;
+      float csum = 0.f;
+      for (int i = 0; i < nq; ++i, ++gi) {
+        const int g = gi & 1, it = gi >> 1;
+        mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+        const uint32_t s_addr = tmem + lane_base + g * 256 + w * 128;
+        const float4* l4 = reinterpret_cast<const float4*>(lse_s + i * kBM);
+        tmem_ld32(s_addr, ra);
         tmem_ld_wait();
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const float4 l = l4[c * 8 + q4];
-          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 0]), c2, b2 - l.x));
-          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 1]), c2, b2 - l.y));
-          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 2]), c2, b2 - l.z));
-          csum += fast_exp2(fmaf(__uint_as_float(r[q4 * 4 + 3]), c2, b2 - l.w));
+        for (int c = 0; c < 4; ++c) {
+          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+          if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4) {
+            const float4 l = l4[c * 8 + q4];
+            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 0]), c2, b2 - l.x));
+            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 1]), c2, b2 - l.y));
+            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 2]), c2, b2 - l.z));
+            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 3]), c2, b2 - l.w));
+          }
+          if (c < 3) tmem_ld_wait();
         }
+        tc_fence_before();
+        mbar_arrive(&sm.s_free[g]);
       }
-      tc_fence_before();
-      mbar_arrive(&sm.s_free[g]);
-    }
-    if (g == 1) sm.xsum[key] = csum;
-    named_bar_sync(3, 256);
-    if (g == 0 && key < valid) {
-      const float total = (csum + sm.xsum[key]) * p.correction;
-      p.colsum[static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key] = total;
+      if (key < valid)
+        p.colsum[static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key] =
+            csum * p.correction;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -549,7 +609,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   float corr;
   attn_subsample_plan(a.M, a.subsample_ratio, &m_sub, &stride, &corr);
   const int nq = (m_sub + kBM - 1) / kBM;
-  const int col_smem = static_cast<int>(sizeof(ColSmem)) + nq * kBM * 4 + 1024;
+  const int col_smem = static_cast<int>(sizeof(ColSmem)) + 2 * nq * kBM * 4 + 1024;
   if (col_smem > 227 * 1024) return STAC_ERR_BAD_ARG;
   if (!attr_done) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem) != cudaSuccess)
@@ -607,12 +667,22 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
     cp.M_sub = m_sub; cp.H = a.H; cp.row_stride = stride;
     cp.T_hot = a.T_hot; cp.T_ret = a.T_ret;
     cp.n_hot_tiles = fp.n_hot_tiles; cp.n_q_tiles = nq;
+    cp.n_tiles = fp.n_hot_tiles + fp.n_ret_tiles;
+    cp.n_pairs = (cp.n_tiles + 1) / 2;
+    cp.n_items = cp.n_pairs * a.H;
     cp.scale_log2 = scale_log2; cp.correction = corr;
     cp.bias_ret = a.bias_ret; cp.bias_head_stride = a.bias_head_stride;
     cp.lse2 = lse2; cp.lse2_stride = a.M;
     cp.colsum = a.colsum; cp.colsum_stride = a.colsum_head_stride;
     cp.err = err;
-    dim3 grid_c(fp.n_hot_tiles + fp.n_ret_tiles, a.H);
+    static int n_sm = 0;
+    if (n_sm == 0) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess ||
+          cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
+        return STAC_ERR_CUDA;
+    }
+    const int grid_c = cp.n_items < n_sm ? cp.n_items : n_sm;
     attn_colsum_kernel<<<grid_c, kColThreads, col_smem, stream>>>(tm_qs, tm_kh, tm_kr, cp);
     if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
   }
