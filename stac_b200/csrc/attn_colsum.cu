@@ -28,7 +28,7 @@ constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 bf16
 constexpr int kFwdStages = 4;
-constexpr int kFwdThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9 two softmax warpgroups
+constexpr int kFwdThreads = 384;       // warpgroup 0: warp 0 TMA, warp 1 MMA (2, 3 idle); warpgroups 1, 2: softmax
 constexpr int kColStages = 4;
 constexpr int kColThreads = 320;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -111,6 +111,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
+  if (warp < 4) {
+  setmaxnreg_dec<40>();   // control warpgroup hands its registers to the softmax warps
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -165,19 +167,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(&sm.o_full[g]);
         umma_commit(&sm.kv_empty[s]);
       };
-      // S tiles run up to three ahead of the softmax; P V of tile j follows its softmax
-      for (int j = 0; j < 3 && j < n_tiles; ++j) issue_s(j);
-      for (int j = 0; j < n_tiles; ++j) {
-        issue_pv(j);
-        if (j + 3 < n_tiles) issue_s(j + 3);
+      // S tiles run up to three ahead of the softmax; P V of tile j follows its softmax:
+      // S0 S1 S2 PV0 S3 PV1 S4 ...
+#pragma unroll 1
+      for (int step = 0; step < n_tiles + 3; ++step) {
+        if (step >= 3) issue_pv(step - 3);
+        if (step < n_tiles) issue_s(step);
       }
     }
+  }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    const int g = (warp - 2) >> 2;
+    setmaxnreg_inc<232>();
+    const int g = (warp - 4) >> 2;
     const int wq = warp & 3;                 // TMEM lane quarter this warp may touch
     const int row = wq * 32 + lane;          // query row inside the tile
-    const int t = ((warp - 2) & 3) * 32 + lane;
+    const int t = row;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c2 = p.scale_log2;
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
@@ -208,7 +213,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld32(s_addr, ra);
       tmem_ld_wait();
       // pass 1 over the S tile: row maximum in the log2 domain
-      float mx = -INFINITY;
+      float mx = -INFINITY, mx_raw = -INFINITY, mx_r1 = -INFINITY, mx_r2 = -INFINITY, mx_r3 = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t(&cur)[32] = (c & 1) ? rb : ra;
@@ -226,11 +231,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(cur[i]), c2, sm.bias2[g][c * 32 + i]));
         } else {
+          // raw maximum (the scale is positive, applied once after the loop)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]) * c2);
+          for (int i = 0; i < 32; i += 8) {   // four independent chains
+            mx_raw = fmax3(mx_raw, __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+            mx_r1 = fmax3(mx_r1, __uint_as_float(cur[i + 2]), __uint_as_float(cur[i + 3]));
+            mx_r2 = fmax3(mx_r2, __uint_as_float(cur[i + 4]), __uint_as_float(cur[i + 5]));
+            mx_r3 = fmax3(mx_r3, __uint_as_float(cur[i + 6]), __uint_as_float(cur[i + 7]));
+          }
         }
         tmem_ld_wait();
       }
+      if (!need_bias) mx = fmaxf(fmaxf(mx_raw, mx_r1), fmaxf(mx_r2, mx_r3)) * c2;
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2(m_run - m_use);
@@ -248,7 +260,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive(&sm.o_free[g]);
       }
       // pass 2: probabilities relative to the new maximum, bf16 into shared memory
-      float rs = 0.f;
+      float rs = 0.f, rs2 = 0.f;
       uint8_t* prow = sm.p[g] + row * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -268,8 +280,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 8; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, -m_use));
           }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) rs += pv[i];
+          rs += (pv[0] + pv[1]) + (pv[2] + pv[3]);
+          rs2 += (pv[4] + pv[5]) + (pv[6] + pv[7]);
           const int chunk = (c & 1) * 4 + q4;
           uint4 val;
           val.x = pack_bf16x2(pv[0], pv[1]);
@@ -282,7 +294,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       tc_fence_before();
       mbar_arrive(&sm.s_free[sb]);
-      l_run = fmaf(l_run, alpha, rs);
+      l_run = fmaf(l_run, alpha, rs + rs2);
       m_run = m_new;
       alpha_prev = alpha;
       fence_proxy_async_smem();
@@ -496,7 +508,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const int valid = exists ? min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0) : 0;
       float b2 = -INFINITY;
       if (key < valid) b2 = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e : 0.f;
-      float csum = 0.f;
+      float csum = 0.f, cs1 = 0.f, cs2 = 0.f, cs3 = 0.f;
       for (int i = 0; i < nq; ++i, ++gi) {
         const int g = gi & 1, it = gi >> 1;
         mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
@@ -514,9 +526,9 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           for (int q4 = 0; q4 < 8; ++q4) {
             const float4 l = l4[c * 8 + q4];
             csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 0]), c2, b2 - l.x));
-            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 1]), c2, b2 - l.y));
-            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 2]), c2, b2 - l.z));
-            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 3]), c2, b2 - l.w));
+            cs1 += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 1]), c2, b2 - l.y));
+            cs2 += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 2]), c2, b2 - l.z));
+            cs3 += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 3]), c2, b2 - l.w));
           }
           if (c < 3) tmem_ld_wait();
         }
@@ -525,7 +537,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       if (key < valid)
         p.colsum[static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key] =
-            csum * p.correction;
+            ((csum + cs1) + (cs2 + cs3)) * p.correction;
     }
   }
   tc_fence_before();
