@@ -18,15 +18,19 @@
 //   sort_tokens_kernel   one CTA per pool head: list the head's valid evicted tokens followed
 //                        by its carried overflow tokens, stable LSD radix sort by voxel id,
 //                        emit the unique rows (CSR).
-//   rows_phase_a_kernel  one warp per row: merge tokens into existing pivots (cosine >= sim),
-//                        select the rest, rank existing buffer tokens + selected tokens by
+//   rows_phase_a1_kernel one thread per row: rows without pivots need only scores (all tokens are
+//                        selected and ranked against the buffered scores); rows with pivots or
+//                        many tokens are queued for
+//   rows_phase_a2_kernel one warp per queued row: merge tokens into existing pivots (cosine >=
+//                        sim), select the rest, rank existing buffer tokens + selected tokens by
 //                        (score desc, arrival order), count new segments / overflow / full.
 //   scan_heads_kernel /  exclusive scans of those counts, allocation plan (k ids from the top
 //   scan_plan_kernel     of the free list, the rest fresh), capacity checks.
-//   rows_phase_b_kernel  one warp per row: hand out segment ids, place buffer tokens at
-//                        column = rank, emit overflow, turn full buffers into a pivot, insert
-//                        it (folding the lowest-weight pivot into its nearest neighbour when
-//                        the row is saturated), stage the freed segment ids.
+//   rows_phase_b1_kernel one warp per row: hand out segment ids, place buffer tokens at
+//                        column = rank, emit overflow, queue rows whose buffer filled up.
+//   rows_phase_b2_kernel one warp per full row: turn the buffer into a pivot, insert it (folding
+//                        the lowest-weight pivot into its nearest neighbour when the row is
+//                        saturated), stage the freed segment ids.
 //   finalize_kernel      append staged ids to the free list, publish counters.
 #include <cuda_bf16.h>
 
@@ -110,12 +114,14 @@ struct MergeParams {
   int4* head_base;     // [heads]
   int* plan;           // device ints, see kPlan*
   int* free_stage;     // [buf_cap]
+  int2* defer_list;    // [heads*ncap] rows (head, row index) that need the warp-per-row phase A
+  int2* full_list;     // [heads*ncap] rows whose buffer filled up in this call
   int passes;          // radix passes (8 bits each)
   int* err;
 };
 
 enum { kPlanK = 0, kPlanFreeLen, kPlanBufTop, kPlanPivTop, kPlanTotalAdd, kPlanTotalFull, kPlanTotalOver,
-       kPlanAnyValid, kPlanAbort, kPlanSize = 16 };
+       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanSize = 16 };
 
 // Block-wide exclusive scan, 1024 threads.
 __device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
@@ -330,12 +336,7 @@ __device__ __forceinline__ float norm_inv_denom(const float (&x)[EPL]) {
 
 // ------------------------------------------------------------------------------------ phase A
 template <typename T, int EPL>
-__global__ void __launch_bounds__(256) rows_phase_a_kernel(const MergeParams p) {
-  const int lane = threadIdx.x & 31;
-  const int h = blockIdx.y;
-  const int ri = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (p.plan[kPlanAnyValid] == 0) return;
-  if (ri >= p.n_rows[h]) return;
+__device__ __forceinline__ void phase_a_row(const MergeParams& p, const int h, const int ri, const int lane) {
   const long long hb = static_cast<long long>(h) * p.ncap;
   const int vx = p.row_vx[hb + ri];
   const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
@@ -526,6 +527,86 @@ __global__ void __launch_bounds__(256) rows_phase_a_kernel(const MergeParams p) 
   }
 }
 
+// Thread-per-row fast path of phase A: rows without pivots and with few tokens need only
+// scores (every token is selected, ranked against the buffered scores).  Rows that hold
+// pivots, or long rows, are queued for the warp-per-row path.
+__global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p) {
+  const int h = blockIdx.y;
+  const int ri = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p.plan[kPlanAnyValid] == 0) return;
+  if (ri >= p.n_rows[h]) return;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int vx = p.row_vx[hb + ri];
+  const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
+  const int s0 = rst[ri], s1 = rst[ri + 1];
+  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+  const int npiv = p.piv_row_cnt[r];
+  if (npiv > 0 || s1 - s0 > 32) {
+    const int pos = atomicAdd(&p.plan[kPlanDeferCount], 1);
+    p.defer_list[pos] = make_int2(h, ri);
+    return;
+  }
+  const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
+  const int nbuf = p.buf_row_cnt[r];
+  float* tscore = p.tok_score + hb;
+  int* tdest = p.tok_dest + hb;
+  float ex[kMaxB];
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) ex[c] = (c < nbuf) ? p.buf_S[p.buf_row_seg[r * p.B + c]] : 0.f;
+  for (int i = s0; i < s1; ++i) {
+    const int code = codes[i];
+    float sc;
+    if (code >= 0) {
+      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+      sc = p.s_src[h * p.meta_head_stride + pos];
+    } else {
+      sc = p.over_S_in[~code];
+    }
+    tscore[i] = sc;
+  }
+  const int n_sel = s1 - s0;
+  short* od = p.old_dest + (hb + ri) * kMaxB;
+#pragma unroll
+  for (int c = 0; c < kMaxB; ++c) {
+    if (c < nbuf) {
+      int rank = c;  // buffered tokens are stored in rank order
+      for (int i = s0; i < s1; ++i) rank += (tscore[i] > ex[c]) ? 1 : 0;
+      od[c] = static_cast<short>(min(rank, 32767));
+    }
+  }
+  for (int i = s0; i < s1; ++i) {
+    const float mine = tscore[i];
+    int rank = 0;
+#pragma unroll
+    for (int c = 0; c < kMaxB; ++c) rank += (c < nbuf && ex[c] >= mine) ? 1 : 0;
+    for (int i2 = s0; i2 < s1; ++i2) {
+      const float s2 = tscore[i2];
+      rank += (s2 > mine || (s2 == mine && i2 < i)) ? 1 : 0;
+    }
+    tdest[i] = rank;
+  }
+  const int n_cand = nbuf + n_sel;
+  const int newcnt = min(p.B, n_cand);
+  const int full = (newcnt == p.B) ? 1 : 0;
+  int4 info;
+  info.x = newcnt - nbuf;
+  info.y = max(0, n_cand - p.B);
+  info.z = full | (full ? 2 : 0);   // no pivots in this row: a full buffer always needs a pivot segment
+  info.w = n_sel;
+  p.row_info[hb + ri] = info;
+}
+
+template <typename T, int EPL>
+__global__ void __launch_bounds__(256) rows_phase_a2_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int n = p.plan[kPlanDeferCount];
+  for (int w = blockIdx.x * warps_per_block + (threadIdx.x >> 5); w < n; w += gridDim.x * warps_per_block) {
+    const int2 hr = p.defer_list[w];
+    phase_a_row<T, EPL>(p, hr.x, hr.y, lane);
+  }
+}
+
 // ------------------------------------------------------------------------------------ scans
 __global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p) {
   __shared__ int warp_sums[32];
@@ -625,24 +706,23 @@ __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p)
 
 // ------------------------------------------------------------------------------------ phase B
 template <typename T, int EPL>
-__global__ void __launch_bounds__(256) rows_phase_b_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(256) rows_phase_b1_kernel(const MergeParams p) {
   const int lane = threadIdx.x & 31;
   const int h = blockIdx.y;
   const int ri = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
   if (ri >= p.n_rows[h]) return;
   const long long hb = static_cast<long long>(h) * p.ncap;
+  const int4 info = p.row_info[hb + ri];
+  if (info.w == 0) return;  // nothing selected: the buffer is untouched
   const int vx = p.row_vx[hb + ri];
   const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
   const int s0 = rst[ri], s1 = rst[ri + 1];
   const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
   const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
-  const int4 info = p.row_info[hb + ri];
-  if (info.w == 0) return;  // nothing selected: the buffer is untouched
   const int4 pref = p.row_pref[hb + ri];
   const int4 hbase = p.head_base[h];
   const int add_off = hbase.x + pref.x, over_off = hbase.y + pref.y;
-  const int full_off = hbase.z + pref.z, piv_off = hbase.w + pref.w;
   const int nbuf = p.buf_row_cnt[r];
   const int newcnt = nbuf + info.x;
   const int B = p.B, D = p.D;
@@ -653,32 +733,14 @@ __global__ void __launch_bounds__(256) rows_phase_b_kernel(const MergeParams p) 
   T* oK = static_cast<T*>(p.over_K_out);
   T* oV = static_cast<T*>(p.over_V_out);
 
-  // existing tokens into registers (their column may change)
-  float exK[kMaxB][EPL], exV[kMaxB][EPL];
-  float exS = 0.f;
-  int exDest = -1;
+  // lane c holds the segment id of column c: existing columns, then the newly assigned ones
   const short* od = p.old_dest + (hb + ri) * kMaxB;
   int my_seg = -1;
+  int ex_dest = -1;
   if (lane < nbuf) {
     my_seg = p.buf_row_seg[r * B + lane];
-    exS = p.buf_S[my_seg];
-    exDest = od[lane];
+    ex_dest = od[lane];
   }
-#pragma unroll
-  for (int c = 0; c < kMaxB; ++c) {
-    const int sg = __shfl_sync(kFull, my_seg, c);
-    if (c < nbuf) {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        exK[c][e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
-        exV[c][e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) exK[c][e] = exV[c][e] = 0.f;
-    }
-  }
-  // new segment ids for columns nbuf .. newcnt-1
   const int k_take = p.plan[kPlanK], free_len = p.plan[kPlanFreeLen], buf_top = p.plan[kPlanBufTop];
   if (lane >= nbuf && lane < newcnt) {
     const int q = add_off + (lane - nbuf);
@@ -686,37 +748,43 @@ __global__ void __launch_bounds__(256) rows_phase_b_kernel(const MergeParams p) 
     p.buf_row_seg[r * B + lane] = id;
     my_seg = id;
   }
-  __syncwarp();
-  // place existing tokens
+  // Buffered tokens only ever move to a higher column (new tokens push them down the
+  // ranking), so walking them from the last column to the first moves each one into a slot
+  // whose old content has already left.
+  for (int c = nbuf - 1; c >= 0; --c) {
+    const int d = __shfl_sync(kFull, ex_dest, c);
+    if (d == c) continue;
+    const int sg = __shfl_sync(kFull, my_seg, c);
+    float k[EPL], v[EPL];
 #pragma unroll
-  for (int c = 0; c < kMaxB; ++c) {
-    const int d = __shfl_sync(kFull, exDest, c);
-    const float sc = __shfl_sync(kFull, exS, c);
-    if (c < nbuf) {
-      if (d < B) {
-        const int sg = __shfl_sync(kFull, my_seg, d);
-        if (d != c) {
+    for (int e = 0; e < EPL; ++e) {
+      k[e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
+      v[e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
+    }
+    const float sc = p.buf_S[sg];
+    __syncwarp();
+    if (d < B) {
+      const int dg = __shfl_sync(kFull, my_seg, d);
 #pragma unroll
-          for (int e = 0; e < EPL; ++e) {
-            Elem<T>::store(bK + static_cast<long long>(sg) * D + lane * EPL + e, exK[c][e]);
-            Elem<T>::store(bV + static_cast<long long>(sg) * D + lane * EPL + e, exV[c][e]);
-          }
-          if (lane == 0) p.buf_S[sg] = sc;
-        }
-      } else {
-        const long long o = over_off + (d - B);
+      for (int e = 0; e < EPL; ++e) {
+        Elem<T>::store(bK + static_cast<long long>(dg) * D + lane * EPL + e, k[e]);
+        Elem<T>::store(bV + static_cast<long long>(dg) * D + lane * EPL + e, v[e]);
+      }
+      if (lane == 0) p.buf_S[dg] = sc;
+    } else {
+      const long long o = over_off + (d - B);
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          Elem<T>::store(oK + o * D + lane * EPL + e, exK[c][e]);
-          Elem<T>::store(oV + o * D + lane * EPL + e, exV[c][e]);
-        }
-        if (lane == 0) {
-          p.over_S_out[o] = sc;
-          p.over_hv_out[2 * o] = h;
-          p.over_hv_out[2 * o + 1] = vx;
-        }
+      for (int e = 0; e < EPL; ++e) {
+        Elem<T>::store(oK + o * D + lane * EPL + e, k[e]);
+        Elem<T>::store(oV + o * D + lane * EPL + e, v[e]);
+      }
+      if (lane == 0) {
+        p.over_S_out[o] = sc;
+        p.over_hv_out[2 * o] = h;
+        p.over_hv_out[2 * o + 1] = vx;
       }
     }
+    __syncwarp();
   }
   // place selected tokens
   for (int i = s0; i < s1; ++i) {
@@ -749,24 +817,50 @@ __global__ void __launch_bounds__(256) rows_phase_b_kernel(const MergeParams p) 
       }
     }
   }
-  if (!(info.z & 1)) {
-    if (lane == 0) p.buf_row_cnt[r] = newcnt;
-    return;
+  if (lane == 0) {
+    if (info.z & 1) {
+      // full: the pivot is built by the next kernel, which also releases the row
+      const int pos = atomicAdd(&p.plan[kPlanFullCount], 1);
+      p.full_list[pos] = make_int2(h, ri);
+    } else {
+      p.buf_row_cnt[r] = newcnt;
+    }
   }
+}
+
+// Full buffers -> one pivot each, inserted into the row's pivot slots; the buffer row is released.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
+  const int n_full = p.plan[kPlanFullCount];
+  for (int wi = blockIdx.x * warps_per_block + (threadIdx.x >> 5); wi < n_full; wi += gridDim.x * warps_per_block) {
+  const int2 hr = p.full_list[wi];
+  const int h = hr.x, ri = hr.y;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int vx = p.row_vx[hb + ri];
+  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+  const int4 pref = p.row_pref[hb + ri];
+  const int4 hbase = p.head_base[h];
+  const int full_off = hbase.z + pref.z, piv_off = hbase.w + pref.w;
+  const int B = p.B, D = p.D;
+  T* bK = static_cast<T*>(p.buf_K);
+  T* bV = static_cast<T*>(p.buf_V);
+  int my_seg = -1;
+  if (lane < B) my_seg = p.buf_row_seg[r * B + lane];
   // ---- the buffer is full: B tokens -> one pivot (stac/merger.py:408-461)
-  __threadfence();
-  __syncwarp();
   float tk[kMaxB][EPL], tv[kMaxB][EPL];
   float ts = 0.f;
-  if (lane < B) ts = fmaxf(__ldcg(p.buf_S + my_seg), 1e-6f);
+  if (lane < B) ts = fmaxf(p.buf_S[my_seg], 1e-6f);
 #pragma unroll
   for (int c = 0; c < kMaxB; ++c) {
     const int sg = __shfl_sync(kFull, my_seg, c);
     if (c < B) {
 #pragma unroll
       for (int e = 0; e < EPL; ++e) {
-        tk[c][e] = Elem<T>::load_cg(bK + static_cast<long long>(sg) * D + lane * EPL + e);
-        tv[c][e] = Elem<T>::load_cg(bV + static_cast<long long>(sg) * D + lane * EPL + e);
+        tk[c][e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
+        tv[c][e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
       }
     } else {
 #pragma unroll
@@ -944,6 +1038,8 @@ __global__ void __launch_bounds__(256) rows_phase_b_kernel(const MergeParams p) 
     p.buf_row_seg[r * B + lane] = -1;
   }
   if (lane == 0) p.buf_row_cnt[r] = 0;
+  __syncwarp();
+  }
 }
 
 // Freed ids are appended after the part of the free list that was not handed out.
@@ -982,7 +1078,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct ScratchLayout {
   size_t keys_a, keys_b, vals_a, vals_b, n_tok, n_rows, row_vx, row_start, row_info, row_pref, old_dest, tok_dest,
-      tok_sim, tok_score, head_tot, head_base, plan, free_stage, total;
+      tok_sim, tok_score, head_tot, head_base, plan, free_stage, defer_list, full_list, total;
 };
 
 ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
@@ -1001,6 +1097,7 @@ ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
   L.tok_dest = take(hn * 4); L.tok_sim = take(hn * 4); L.tok_score = take(hn * 4);
   L.head_tot = take(static_cast<size_t>(heads) * 16); L.head_base = take(static_cast<size_t>(heads) * 16);
   L.plan = take(kPlanSize * 4); L.free_stage = take(static_cast<size_t>(buf_cap) * 4);
+  L.defer_list = take(hn * 8); L.full_list = take(hn * 8);
   L.total = off;
   return L;
 }
@@ -1011,10 +1108,13 @@ int launch_merge(MergeParams& mp, cudaStream_t st) {
   sort_tokens_kernel<<<mp.heads, 1024, 0, st>>>(mp);
   const int warps = 8;
   dim3 grid_rows((mp.ncap + warps - 1) / warps, mp.heads);
-  rows_phase_a_kernel<T, 2><<<grid_rows, warps * 32, 0, st>>>(mp);
+  dim3 grid_a1((mp.ncap + 255) / 256, mp.heads);
+  rows_phase_a1_kernel<<<grid_a1, 256, 0, st>>>(mp);
+  rows_phase_a2_kernel<T, 2><<<148 * 4, 256, 0, st>>>(mp);
   scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp);
   scan_plan_kernel<<<1, 1024, 0, st>>>(mp);
-  rows_phase_b_kernel<T, 2><<<grid_rows, warps * 32, 0, st>>>(mp);
+  rows_phase_b1_kernel<T, 2><<<grid_rows, warps * 32, 0, st>>>(mp);
+  rows_phase_b2_kernel<T, 2><<<148 * 8, 128, 0, st>>>(mp);
   const int fin_blocks = (mp.buf_cap + 255) / 256;
   finalize_kernel<<<fin_blocks, 256, 0, st>>>(mp);
   carry_overflow_kernel<T><<<148, 256, 0, st>>>(mp);
@@ -1082,6 +1182,8 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
   mp.head_base = reinterpret_cast<int4*>(base + L.head_base);
   mp.plan = reinterpret_cast<int*>(base + L.plan);
   mp.free_stage = reinterpret_cast<int*>(base + L.free_stage);
+  mp.defer_list = reinterpret_cast<int2*>(base + L.defer_list);
+  mp.full_list = reinterpret_cast<int2*>(base + L.full_list);
   int bits = 1;
   while ((1ll << bits) < pool->voxel_used) ++bits;
   mp.passes = (bits + 7) / 8;
