@@ -65,6 +65,7 @@ struct FwdParams {
   float* lse;                // [H, M] natural log or nullptr
   float* lse2;               // [H, lse2_stride] log2 domain
   long long lse2_stride;
+  int* fallback;             // device flag: set by the fast kernel when a row needs the exact kernel
   int* err;
 };
 
@@ -84,6 +85,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int n_hot = p.n_hot_tiles;
   const int n_tiles = p.n_hot_tiles + p.n_ret_tiles;
+  // This kernel is the exact (running-maximum) path.  When it is launched behind the fast
+  // kernel it only runs if that one flagged a row whose scores outgrew its fixed reference.
+  if (p.fallback != nullptr && *reinterpret_cast<volatile int*>(p.fallback) == 0) return;
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar_q, 1);
@@ -358,6 +362,301 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
+// Fast forward kernel.  Softmax is invariant to the reference subtracted before the exponent,
+// so instead of a running maximum every row uses ONE reference: the exact maximum of its
+// first key tile.  Nothing is ever rescaled: P V accumulates in TMEM across all key tiles of
+// the row block, three softmax warpgroups take key tiles round-robin and keep only a partial
+// row sum each.  The scheme is exact as long as no later score exceeds the reference by more
+// than 2^kFastHeadroom (probabilities then stay far inside the bf16 / fp32 range); a warp that
+// sees a larger score raises `fallback` and the exact kernel, launched right behind this one,
+// recomputes the call.
+// ---------------------------------------------------------------------------------------
+constexpr int kFastThreads = 512;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA), 1..3 softmax
+constexpr int kFastKStages = 2;
+constexpr int kFastVStages = 4;
+constexpr float kFastHeadroom = 60.f;
+
+struct FastSmem {
+  uint8_t q[kTileBytes];
+  uint8_t k[kFastKStages][kTileBytes];
+  uint8_t v[kFastVStages][kTileBytes];
+  uint8_t p[3][2 * kTileBytes];
+  float bias2[3][kBN];
+  float m_ref[kBM];
+  float lpart[3][kBM];
+  uint64_t bar_q;
+  uint64_t k_full[kFastKStages];
+  uint64_t k_empty[kFastKStages];
+  uint64_t v_full[kFastVStages];
+  uint64_t v_empty[kFastVStages];
+  uint64_t s_full[3];
+  uint64_t s_free[3];
+  uint64_t p_full[3];
+  uint64_t p_free[3];
+  uint64_t ref_ready;
+  uint64_t o_done;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(kFastThreads, 1)
+attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
+                     const __grid_constant__ CUtensorMap tm_v_hot, const __grid_constant__ CUtensorMap tm_k_ret,
+                     const __grid_constant__ CUtensorMap tm_v_ret, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  FastSmem& sm = *reinterpret_cast<FastSmem*>(align1024(smem_raw));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x;
+  const int h = blockIdx.y;
+  const int n_hot = p.n_hot_tiles;
+  const int n_tiles = p.n_hot_tiles + p.n_ret_tiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.bar_q, 1);
+    for (int s = 0; s < kFastKStages; ++s) {
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < kFastVStages; ++s) {
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
+    }
+    for (int g = 0; g < 3; ++g) {
+      mbar_init(&sm.s_full[g], 1);
+      mbar_init(&sm.s_free[g], 128);
+      mbar_init(&sm.p_full[g], 128);
+      mbar_init(&sm.p_free[g], 1);
+    }
+    mbar_init(&sm.ref_ready, 128);
+    mbar_init(&sm.o_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t o_tmem = tmem + 3 * kBN;
+
+  if (warp < 4) {
+    setmaxnreg_dec<40>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k_hot);
+      tma_prefetch_desc(&tm_v_hot);
+      mbar_arrive_expect_tx(&sm.bar_q, kTileBytes);
+      tma_load_3d(sm.q, &tm_q, &sm.bar_q, 0, h, m_tile * kBM);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int ks = j % kFastKStages, kr = j / kFastKStages;
+        const int vs = j % kFastVStages, vr = j / kFastVStages;
+        const bool hot = j < n_hot;
+        const int n0 = (hot ? j : j - n_hot) * kBN;
+        if (kr > 0) mbar_wait(&sm.k_empty[ks], (kr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_arrive_expect_tx(&sm.k_full[ks], kTileBytes);
+        tma_load_3d(sm.k[ks], hot ? &tm_k_hot : &tm_k_ret, &sm.k_full[ks], 0, n0, h);
+        if (vr > 0) mbar_wait(&sm.v_empty[vs], (vr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_arrive_expect_tx(&sm.v_full[vs], kTileBytes);
+        tma_load_3d(sm.v[vs], hot ? &tm_v_hot : &tm_v_ret, &sm.v_full[vs], 0, n0, h);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer: S = Q K^T
+      // (its own thread, so a score tile is issued the moment its TMEM buffer is released,
+      // independent of the P V stream)
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBM, kBN, 0);
+      mbar_wait(&sm.bar_q, 0, p.err, DEV_TIMEOUT_TMA);
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q));
+      const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0]));
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int g = j % 3, it = j / 3, ks = j % kFastKStages;
+        mbar_wait(&sm.k_full[ks], (j / kFastKStages) & 1, p.err, DEV_TIMEOUT_TMA);
+        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+        const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(ks * (kTileBytes >> 4));
+        const uint32_t d = tmem + g * kBN;
+        umma_ss(d, q_desc, k_desc, idesc_s, 0u);
+        umma_ss(d, q_desc + 2, k_desc + 2, idesc_s, 1u);
+        umma_ss(d, q_desc + 4, k_desc + 4, idesc_s, 1u);
+        umma_ss(d, q_desc + 6, k_desc + 6, idesc_s, 1u);
+        umma_commit(&sm.s_full[g]);
+        umma_commit(&sm.k_empty[ks]);
+      }
+    } else if (warp == 2 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer: O += P V
+      constexpr uint32_t idesc_o = umma_idesc_bf16(kBM, kD, 1);
+      const uint64_t p_desc0 = smem_desc_sw128(smem_u32(sm.p[0]));
+      const uint64_t v_desc0 = smem_desc_sw128(smem_u32(sm.v[0]));
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int g = j % 3, it = j / 3, vs = j % kFastVStages;
+        mbar_wait(&sm.v_full[vs], (j / kFastVStages) & 1, p.err, DEV_TIMEOUT_TMA);
+        mbar_wait(&sm.p_full[g], it & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+        const uint64_t pa = p_desc0 + static_cast<uint64_t>(g * ((2 * kTileBytes) >> 4));
+        const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kTileBytes >> 4));
+        // keys 0..63 live in the first 64-key atom of P, 64..127 in the second; V advances 16 rows
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk)
+          umma_ss(o_tmem, pa + static_cast<uint64_t>((kk >> 2) * (kTileBytes >> 4) + 2 * (kk & 3)),
+                  vb + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&sm.p_free[g]);
+        umma_commit(&sm.v_empty[vs]);
+        if (j == n_tiles - 1) umma_commit(&sm.o_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    setmaxnreg_inc<152>();
+    const int g = (warp - 4) >> 2;
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float c2 = p.scale_log2;
+    float m_ref = 0.f;
+    float l0 = 0.f, l1 = 0.f;
+    bool overflow = false;
+    uint32_t ra[32], rb[32];
+    int it = 0;
+    for (int j = g; j < n_tiles; j += 3, ++it) {
+      const bool is_ret = j >= n_hot;
+      const int n0 = (is_ret ? j - n_hot : j) * kBN;
+      const int valid = min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0);
+      const bool need_bias = is_ret || valid < kBN;
+      if (need_bias) {
+        named_bar_sync(1 + g, 128);
+        float b = -INFINITY;
+        if (row < valid) b = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + row] * kLog2e : 0.f;
+        sm.bias2[g][row] = b;
+        named_bar_sync(1 + g, 128);
+      }
+      mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_base + g * kBN;
+      if (j == 0) {
+        // exact row maximum of the first tile = the row's reference for the whole call
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld32(s_addr + c * 32, ra);
+          tmem_ld_wait();
+          if (need_bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(ra[i]), c2, sm.bias2[g][c * 32 + i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(ra[i]) * c2);
+          }
+        }
+        m_ref = (mx == -INFINITY) ? 0.f : mx;
+        sm.m_ref[row] = m_ref;
+        mbar_arrive(&sm.ref_ready);
+      } else if (it == 0) {
+        mbar_wait(&sm.ref_ready, 0, p.err, DEV_TIMEOUT_CONSUMER);
+        m_ref = sm.m_ref[row];
+      }
+      if (it > 0) mbar_wait(&sm.p_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
+      // single pass: probabilities relative to the fixed reference, and the tile maximum
+      float t0 = -INFINITY, t1 = -INFINITY;
+      uint8_t* prow = sm.p[g] + row * 128;
+      tmem_ld32(s_addr, ra);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
+        uint8_t* atom = prow + (c >> 1) * kTileBytes;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float pv[8];
+          if (need_bias) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float x = fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, sm.bias2[g][c * 32 + q4 * 8 + i]) - m_ref;
+              t0 = fmaxf(t0, x);
+              pv[i] = fast_exp2(x);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; i += 4) {
+              t0 = fmax3(t0, __uint_as_float(cur[q4 * 8 + i]), __uint_as_float(cur[q4 * 8 + i + 1]));
+              t1 = fmax3(t1, __uint_as_float(cur[q4 * 8 + i + 2]), __uint_as_float(cur[q4 * 8 + i + 3]));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, -m_ref));
+          }
+          l0 += (pv[0] + pv[1]) + (pv[2] + pv[3]);
+          l1 += (pv[4] + pv[5]) + (pv[6] + pv[7]);
+          const int chunk = (c & 1) * 4 + q4;
+          uint4 val;
+          val.x = pack_bf16x2(pv[0], pv[1]);
+          val.y = pack_bf16x2(pv[2], pv[3]);
+          val.z = pack_bf16x2(pv[4], pv[5]);
+          val.w = pack_bf16x2(pv[6], pv[7]);
+          *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = val;
+        }
+        if (c < 3) tmem_ld_wait();
+      }
+      // distance of the tile maximum from the reference, in the log2 domain
+      const float tmax = need_bias ? t0 : fmaf(fmaxf(t0, t1), c2, -m_ref);
+      overflow = overflow || (tmax > kFastHeadroom);
+      tc_fence_before();
+      mbar_arrive(&sm.s_free[g]);
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.p_full[g]);
+    }
+    if (__any_sync(0xffffffffu, overflow) && lane == 0) atomicOr(p.fallback, 1);
+    sm.lpart[g][row] = l0 + l1;
+    named_bar_sync(4, 384);
+    if (g == 0) {
+      mbar_wait(&sm.o_done, 0, p.err, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      tmem_ld32(o_tmem + lane_base, ra);
+      tmem_ld32(o_tmem + lane_base + 32, rb);
+      tmem_ld_wait();
+      const float l = (sm.lpart[0][row] + sm.lpart[1][row]) + sm.lpart[2][row];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int mrow = m_tile * kBM + row;
+      if (mrow < p.M) {
+        __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint4 val;
+          val.x = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 0]) * inv, __uint_as_float(ra[q8 * 8 + 1]) * inv);
+          val.y = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 2]) * inv, __uint_as_float(ra[q8 * 8 + 3]) * inv);
+          val.z = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 4]) * inv, __uint_as_float(ra[q8 * 8 + 5]) * inv);
+          val.w = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 6]) * inv, __uint_as_float(ra[q8 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
+        }
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint4 val;
+          val.x = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 0]) * inv, __uint_as_float(rb[q8 * 8 + 1]) * inv);
+          val.y = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 2]) * inv, __uint_as_float(rb[q8 * 8 + 3]) * inv);
+          val.z = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 4]) * inv, __uint_as_float(rb[q8 * 8 + 5]) * inv);
+          val.w = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 6]) * inv, __uint_as_float(rb[q8 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + 32 + q8 * 8) = val;
+        }
+        const float l2 = m_ref + log2f(l);
+        if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
+        p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
+      }
+      tc_fence_before();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Column sums.  Persistent CTAs walk over work items = (pair of 128-key tiles, head).  For every
 // 128-row query tile the MMA warp computes S^T = K Q^T for both key tiles against the same
 // query tile in shared memory; warpgroup 0 owns the first key tile, warpgroup 1 the second, one
@@ -603,7 +902,8 @@ void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* cor
   }
 }
 
-size_t attn_lse2_elems(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M); }
+// row log-sum-exps [H, M] followed by the fallback flag (64 floats of padding keep it aligned)
+size_t attn_lse2_elems(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 64; }
 
 int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t stream) {
   if (a.D != kD) return STAC_ERR_BAD_ARG;
@@ -623,8 +923,12 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   const int nq = (m_sub + kBM - 1) / kBM;
   const int col_smem = static_cast<int>(sizeof(ColSmem)) + 2 * nq * kBM * 4 + 1024;
   if (col_smem > 227 * 1024) return STAC_ERR_BAD_ARG;
+  const int fast_smem = static_cast<int>(sizeof(FastSmem)) + 1024;
   if (!attr_done) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem) != cudaSuccess)
+      return STAC_ERR_CUDA;
+    if (cudaFuncSetAttribute(attn_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fast_smem) !=
+        cudaSuccess)
       return STAC_ERR_CUDA;
     if (cudaFuncSetAttribute(attn_colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess)
@@ -670,7 +974,12 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   fp.out = static_cast<__nv_bfloat16*>(a.out); fp.out_row_stride = a.out_row_stride;
   fp.lse = a.lse; fp.lse2 = lse2; fp.lse2_stride = a.M;
   fp.err = err;
+  fp.fallback = reinterpret_cast<int*>(lse2 + static_cast<size_t>(a.H) * a.M);
   dim3 grid_f((a.M + kBM - 1) / kBM, a.H);
+  // fast kernel (fixed per-row reference) first; the exact kernel behind it returns at once
+  // unless the fast one raised the flag
+  if (cudaMemsetAsync(fp.fallback, 0, sizeof(int), stream) != cudaSuccess) return STAC_ERR_CUDA;
+  attn_fwd_fast_kernel<<<grid_f, kFastThreads, fast_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
   attn_fwd_kernel<<<grid_f, kFwdThreads, fwd_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
   if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
 
@@ -712,7 +1021,7 @@ namespace {
 
 // One float per (head, query row).  Every GPU that loads the library carries these 512 KB
 // until the process exits.
-static __device__ __align__(256) float g_static_lse2[STAC_ATTN_STATIC_MAX_ROWS];
+static __device__ __align__(256) float g_static_lse2[STAC_ATTN_STATIC_MAX_ROWS + 64];  // + fallback flag
 
 constexpr int kMaxDevices = 64;
 float* g_static_lse2_ptr[kMaxDevices] = {nullptr};
