@@ -360,7 +360,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": stream.d2h, "ms_per_step": round(ms_e2e / K, 4)},
         "gpu_launches": None,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "attn_fwd_kernel + attn_colsum_kernel (one call per layer)",
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_fast_kernel + attn_colsum_kernel (one call per layer)",
                      "achieved": round(achieved, 2) if achieved else None, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": round(achieved / peak_tf, 4) if achieved else None, "peak_source": peak_src,
                      "flops_formula": "(4+2r)*H*M*N*D, r=1", "avg_ms_per_call": round(float(np.mean(att_ms)), 4),
