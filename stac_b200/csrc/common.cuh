@@ -74,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
 }
 
 // ---------------------------------------------------------------------------------------
-// TMA tiled loads (no multicast anywhere in this library)
+// TMA tiled loads (plain per-CTA loads only)
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1, int c2) {
