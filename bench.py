@@ -36,6 +36,7 @@ sys.path.insert(0, ROOT)
 CFG = dict(layers=24, heads=16, head_dim=64, tpf=1041, special=5, patch_h=37, patch_w=28, chunk=4, window=8,
            hh=2, pinned=[0], retrieval=2, voxel_size=0.05, init_voxels=4096, buf_cap=8, piv_cap=4,
            temperature=0.9, prefill_chunks=40)
+ATTN_TRAFFIC_BYTES_PER_CALL = 130.5e6
 METRIC = "stac_hot_path_streaming_frames_per_sec"
 WORKLOAD = ("config4-hot-path: CausalVGGT+STAC stream shapes (24 layers x 16 heads x 64, 1041 tokens/frame, "
             "chunk 4, window 8, hh 2, pinned [0], retrieval 2 frames, bf16); backbone replaced by synthetic "
@@ -323,10 +324,13 @@ def run_ours(args):
 
     run_phase(c["prefill_chunks"], False, False)   # fill the hot cache, start eviction + retrieval
     run_phase(W, False, False)                     # warm-up
+    from stac_b200 import _lib as stac_lib
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.25)
+    launches0 = stac_lib.kernel_launches()
     ms_dev = run_phase(K, False, True)             # timed, device-resident inputs
+    launches = stac_lib.kernel_launches() - launches0
     clocks = sampler.stop()
     run_phase(min(W, 3), True, False)              # warm the host path
     ms_e2e = run_phase(K, True, False)             # timed, host buffers
@@ -358,22 +362,20 @@ def run_ours(args):
                    "prefill_chunks": c["prefill_chunks"], "parallelism": f"{world} independent stream(s)"},
         "e2e": {"value": round(e2e, 3), "unit": "frames/s", "h2d_bytes_per_step": stream.h2d,
                 "d2h_bytes_per_step": stream.d2h, "ms_per_step": round(ms_e2e / K, 4)},
-        "gpu_launches": None,
+        "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "attn_fwd_fast_kernel + attn_colsum_kernel (one call per layer)",
                      "achieved": round(achieved, 2) if achieved else None, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": round(achieved / peak_tf, 4) if achieved else None, "peak_source": peak_src,
                      "flops_formula": "(4+2r)*H*M*N*D, r=1", "avg_ms_per_call": round(float(np.mean(att_ms)), 4),
-                     "traffic": None},
+                     # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one call at this
+                     # shape (M=4164, N=17697), one ncu capture: profiles/attention_traffic__stream_shape.md
+                     "traffic": ATTN_TRAFFIC_BYTES_PER_CALL, "traffic_unit": "bytes per call (fwd 85.2 MB + colsum 45.2 MB)"},
         "stages_ms_per_step": {"attention_24_layers": round(sum(att_ms) / K, 3),
                                "prune_merge_compact": round(sum(mrg_ms) / K, 3)},
         "pool": {"voxels": info["used_voxels"], "pivots": info["pivot_pool_used"],
                  "buffered": info["buffer_pool_used"]},
     }
-    # kernels launched by this library per timed step: per layer fwd + colsum + scores_update,
-    # upsert 3 + neighbours 2, select 1, merge 7, compact 2, retrieval 2 when due
-    line["gpu_launches"] = K * (c["layers"] * 3 + 5 + 1 + 7 + 2) + 2 * sum(
-        1 for i in range(c["prefill_chunks"] + W, c["prefill_chunks"] + W + K) if retrieval_due(i))
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_seconds=15.0)
@@ -470,10 +472,12 @@ def run_microbench_merge(args):
     E = LH * Td
     bytes_m = E * (4 * D * 2 + 12)
     bytes_r = LH * 2048 * (4 * D * 2 + 5)
-    ms_m, ms_r = float(np.mean(times_m)), float(np.mean(times_r))
+    # median: pool growth (row arrays re-allocated at x1.5 voxel counts) lands in some steps
+    ms_m, ms_r = float(np.median(times_m)), float(np.median(times_r))
     print(json.dumps({"metric": "merge_hbm_gbs", "value": round(bytes_m / ms_m / 1e6, 1), "unit": "GB/s",
                       "ms_per_call": round(ms_m, 4), "retrieve_gbs": round(bytes_r / ms_r / 1e6, 1),
-                      "retrieve_ms": round(ms_r, 4), "steps": args.steps, "pool": mg.info(),
+                      "retrieve_ms": round(ms_r, 4), "steps": args.steps, "merge_ms_all": [round(t, 3) for t in times_m],
+                      "pool": mg.info(),
                       "config": {"workload": f"merge microbench: 384 pool heads x {Td} evicted tokens/step, bf16, "
                                              "synthetic smooth surface, retrieve top-2048"}}))
 

@@ -80,6 +80,39 @@ SIGNATURES = {
                               c_void_p, c_void_p, c_void_p, c_void_p]),
 }
 
+# kernels launched by one call of each entry point (the upper figure where it depends on arguments);
+# used to report how many of this library's kernels ran in a timed region
+KERNELS_PER_CALL = {
+    "stac_attn_colsum": 3, "stac_attn_colsum_noalloc": 3, "stac_selftest_bounded_wait": 1,
+    "stac_voxel_hash_clear": 1, "stac_voxel_rehash": 2, "stac_voxel_upsert": 3, "stac_voxel_neighbors": 2,
+    "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 12, "stac_retrieve": 2,
+}
+CALLS = {}
+
+
+class _CountingLib:
+    """Forwards to the ctypes handle and counts calls per entry point."""
+
+    def __init__(self, handle):
+        self._handle = handle
+
+    def __getattr__(self, name):
+        fn = getattr(self._handle, name)
+        if name not in KERNELS_PER_CALL:
+            return fn
+
+        def counted(*args):
+            CALLS[name] = CALLS.get(name, 0) + 1
+            return fn(*args)
+        self.__dict__[name] = counted
+        return counted
+
+
+def kernel_launches():
+    """Kernels of this library launched so far (by the entry-point calls made through lib())."""
+    return sum(KERNELS_PER_CALL[n] * c for n, c in CALLS.items())
+
+
 _lib = None
 
 
@@ -98,7 +131,7 @@ def lib():
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
-        _lib = handle
+        _lib = _CountingLib(handle)
     return _lib
 
 

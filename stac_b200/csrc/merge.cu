@@ -26,8 +26,12 @@
 //                        (score desc, arrival order), count new segments / overflow / full.
 //   scan_heads_kernel /  exclusive scans of those counts, allocation plan (k ids from the top
 //   scan_plan_kernel     of the free list, the rest fresh), capacity checks.
-//   rows_phase_b1_kernel one warp per row: hand out segment ids, place buffer tokens at
-//                        column = rank, emit overflow, queue rows whose buffer filled up.
+//   rows_phase_b1a_kernel one thread per row: hand out segment ids, publish occupancy, queue rows
+//                        whose buffered tokens change column / whose buffer filled up.
+//   rows_phase_b1m_kernel one warp per queued row: move buffered tokens to their new column
+//                        (or to the overflow list), last column first, in place.
+//   tokens_place_kernel  token-parallel 16-byte-vector copy of every selected token to its
+//                        column's segment or overflow slot.
 //   rows_phase_b2_kernel one warp per full row: turn the buffer into a pivot, insert it (folding
 //                        the lowest-weight pivot into its nearest neighbour when the row is
 //                        saturated), stage the freed segment ids.
@@ -116,12 +120,14 @@ struct MergeParams {
   int* free_stage;     // [buf_cap]
   int2* defer_list;    // [heads*ncap] rows (head, row index) that need the warp-per-row phase A
   int2* full_list;     // [heads*ncap] rows whose buffer filled up in this call
+  int2* move_list;     // [heads*ncap] rows in which buffered tokens change column
+  int* tok_row;        // [heads][ncap] row index of each sorted token
   int passes;          // radix passes (8 bits each)
   int* err;
 };
 
 enum { kPlanK = 0, kPlanFreeLen, kPlanBufTop, kPlanPivTop, kPlanTotalAdd, kPlanTotalFull, kPlanTotalOver,
-       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanSize = 16 };
+       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanMoveCount, kPlanSize = 16 };
 
 // Block-wide exclusive scan, 1024 threads.
 __device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
@@ -457,11 +463,13 @@ __device__ __forceinline__ void phase_a_row(const MergeParams& p, const int h, c
     for (int i = s0 + lane; i < s1; i += 32) {
       const bool sel = (tsim[i] < p.replace_thresh) && (fmaxf(tscore[i], 1e-6f) > gate);
       tdest[i] = sel ? 0 : -1;
+      p.tok_row[hb + i] = ri;
     }
   } else {
     for (int i = s0 + lane; i < s1; i += 32) {
       tscore[i] = rd.load_s(codes[i]);
       tdest[i] = 0;
+      p.tok_row[hb + i] = ri;
     }
   }
   __syncwarp();
@@ -521,7 +529,7 @@ __device__ __forceinline__ void phase_a_row(const MergeParams& p, const int h, c
     int4 info;
     info.x = newcnt - nbuf;
     info.y = max(0, n_cand - p.B);
-    info.z = full | ((full && npiv < p.P) ? 2 : 0);
+    info.z = full | ((full && npiv < p.P) ? 2 : 0) | (nbuf << 4);
     info.w = n_sel;
     p.row_info[hb + ri] = info;
   }
@@ -563,6 +571,7 @@ __global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p)
       sc = p.over_S_in[~code];
     }
     tscore[i] = sc;
+    p.tok_row[hb + i] = ri;
   }
   const int n_sel = s1 - s0;
   short* od = p.old_dest + (hb + ri) * kMaxB;
@@ -591,7 +600,7 @@ __global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p)
   int4 info;
   info.x = newcnt - nbuf;
   info.y = max(0, n_cand - p.B);
-  info.z = full | (full ? 2 : 0);   // no pivots in this row: a full buffer always needs a pivot segment
+  info.z = full | (full ? 2 : 0) | (nbuf << 4);   // no pivots here: a full buffer always needs a pivot segment
   info.w = n_sel;
   p.row_info[hb + ri] = info;
 }
@@ -705,125 +714,147 @@ __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p)
 }
 
 // ------------------------------------------------------------------------------------ phase B
-template <typename T, int EPL>
-__global__ void __launch_bounds__(256) rows_phase_b1_kernel(const MergeParams p) {
-  const int lane = threadIdx.x & 31;
+// Phase B, step 1 (one thread per row): hand out the segment ids of the new columns in
+// (row, column) order from the allocation plan, publish the new occupancy, and queue the rows
+// whose buffered tokens change column or whose buffer filled up.
+__global__ void __launch_bounds__(256) rows_phase_b1a_kernel(const MergeParams p) {
   const int h = blockIdx.y;
-  const int ri = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int ri = blockIdx.x * blockDim.x + threadIdx.x;
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
   if (ri >= p.n_rows[h]) return;
   const long long hb = static_cast<long long>(h) * p.ncap;
   const int4 info = p.row_info[hb + ri];
   if (info.w == 0) return;  // nothing selected: the buffer is untouched
   const int vx = p.row_vx[hb + ri];
-  const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
-  const int s0 = rst[ri], s1 = rst[ri + 1];
-  const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
   const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
-  const int4 pref = p.row_pref[hb + ri];
-  const int4 hbase = p.head_base[h];
-  const int add_off = hbase.x + pref.x, over_off = hbase.y + pref.y;
-  const int nbuf = p.buf_row_cnt[r];
+  const int add_off = p.head_base[h].x + p.row_pref[hb + ri].x;
+  const int nbuf = info.z >> 4;
   const int newcnt = nbuf + info.x;
+  const int k_take = p.plan[kPlanK], free_len = p.plan[kPlanFreeLen], buf_top = p.plan[kPlanBufTop];
+  for (int col = nbuf; col < newcnt; ++col) {
+    const int q = add_off + (col - nbuf);
+    p.buf_row_seg[r * p.B + col] = q < k_take ? p.buf_free[free_len - k_take + q] : buf_top + (q - k_take);
+  }
+  const short* od = p.old_dest + (hb + ri) * kMaxB;
+  bool moves = false;
+  for (int c = 0; c < nbuf; ++c) moves = moves || (od[c] != c);
+  if (moves) p.move_list[atomicAdd(&p.plan[kPlanMoveCount], 1)] = make_int2(h, ri);
+  if (info.z & 1) p.full_list[atomicAdd(&p.plan[kPlanFullCount], 1)] = make_int2(h, ri);
+  else p.buf_row_cnt[r] = newcnt;
+}
+
+// Phase B, step 2 (one warp per queued row): buffered tokens only ever move to a higher column
+// (new tokens push them down the ranking), so walking them from the last column to the first
+// moves each one into a slot whose old content has already left.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(256) rows_phase_b1m_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
+  const int n_move = p.plan[kPlanMoveCount];
   const int B = p.B, D = p.D;
-  const int* tdest = p.tok_dest + hb;
-  TokenReader<T, EPL> rd(p, h, lane);
   T* bK = static_cast<T*>(p.buf_K);
   T* bV = static_cast<T*>(p.buf_V);
   T* oK = static_cast<T*>(p.over_K_out);
   T* oV = static_cast<T*>(p.over_V_out);
+  for (int wi = blockIdx.x * warps_per_block + (threadIdx.x >> 5); wi < n_move; wi += gridDim.x * warps_per_block) {
+    const int2 hr = p.move_list[wi];
+    const int h = hr.x, ri = hr.y;
+    const long long hb = static_cast<long long>(h) * p.ncap;
+    const int4 info = p.row_info[hb + ri];
+    const int vx = p.row_vx[hb + ri];
+    const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+    const int over_off = p.head_base[h].y + p.row_pref[hb + ri].y;
+    const int nbuf = info.z >> 4;
+    const int newcnt = nbuf + info.x;
+    const short* od = p.old_dest + (hb + ri) * kMaxB;
+    int my_seg = -1, ex_dest = -1;
+    if (lane < newcnt) my_seg = p.buf_row_seg[r * B + lane];
+    if (lane < nbuf) ex_dest = od[lane];
+    for (int c = nbuf - 1; c >= 0; --c) {
+      const int d = __shfl_sync(kFull, ex_dest, c);
+      if (d == c) continue;
+      const int sg = __shfl_sync(kFull, my_seg, c);
+      float k[EPL], v[EPL];
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        k[e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
+        v[e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
+      }
+      const float sc = p.buf_S[sg];
+      __syncwarp();
+      if (d < B) {
+        const int dg = __shfl_sync(kFull, my_seg, d);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          Elem<T>::store(bK + static_cast<long long>(dg) * D + lane * EPL + e, k[e]);
+          Elem<T>::store(bV + static_cast<long long>(dg) * D + lane * EPL + e, v[e]);
+        }
+        if (lane == 0) p.buf_S[dg] = sc;
+      } else {
+        const long long o = over_off + (d - B);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          Elem<T>::store(oK + o * D + lane * EPL + e, k[e]);
+          Elem<T>::store(oV + o * D + lane * EPL + e, v[e]);
+        }
+        if (lane == 0) {
+          p.over_S_out[o] = sc;
+          p.over_hv_out[2 * o] = h;
+          p.over_hv_out[2 * o + 1] = vx;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
 
-  // lane c holds the segment id of column c: existing columns, then the newly assigned ones
-  const short* od = p.old_dest + (hb + ri) * kMaxB;
-  int my_seg = -1;
-  int ex_dest = -1;
-  if (lane < nbuf) {
-    my_seg = p.buf_row_seg[r * B + lane];
-    ex_dest = od[lane];
+// Phase B, step 3 (token-parallel): every selected token is copied to its column's segment or
+// to its overflow slot with 16-byte vectors; a group of 2 * vec lanes handles one token (first
+// half K, second half V).
+__global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p, const int vec, const int elem_bytes) {
+  const int h = blockIdx.y;
+  const int group = 2 * vec;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int i = static_cast<int>(gid / group);
+  const int sub = static_cast<int>(gid % group);
+  if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
+  if (i >= p.n_tok[h]) return;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int d = p.tok_dest[hb + i];
+  if (d < 0) return;
+  const int ri = p.tok_row[hb + i];
+  const int code = (((p.passes & 1) ? p.vals_b : p.vals_a) + hb)[i];
+  const int vx = p.row_vx[hb + ri];
+  const bool is_v = sub >= vec;
+  const int part = is_v ? sub - vec : sub;
+  const long long tok_bytes = static_cast<long long>(p.D) * elem_bytes;
+  const char* src;
+  float sc;
+  if (code >= 0) {
+    const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+    src = static_cast<const char*>(is_v ? p.v_src : p.k_src) +
+          (h * p.src_head_stride + pos * p.src_row_stride) * elem_bytes;
+    sc = p.s_src[h * p.meta_head_stride + pos];
+  } else {
+    src = static_cast<const char*>(is_v ? p.over_V_in : p.over_K_in) + static_cast<long long>(~code) * tok_bytes;
+    sc = p.over_S_in[~code];
   }
-  const int k_take = p.plan[kPlanK], free_len = p.plan[kPlanFreeLen], buf_top = p.plan[kPlanBufTop];
-  if (lane >= nbuf && lane < newcnt) {
-    const int q = add_off + (lane - nbuf);
-    const int id = q < k_take ? p.buf_free[free_len - k_take + q] : buf_top + (q - k_take);
-    p.buf_row_seg[r * B + lane] = id;
-    my_seg = id;
-  }
-  // Buffered tokens only ever move to a higher column (new tokens push them down the
-  // ranking), so walking them from the last column to the first moves each one into a slot
-  // whose old content has already left.
-  for (int c = nbuf - 1; c >= 0; --c) {
-    const int d = __shfl_sync(kFull, ex_dest, c);
-    if (d == c) continue;
-    const int sg = __shfl_sync(kFull, my_seg, c);
-    float k[EPL], v[EPL];
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      k[e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
-      v[e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
-    }
-    const float sc = p.buf_S[sg];
-    __syncwarp();
-    if (d < B) {
-      const int dg = __shfl_sync(kFull, my_seg, d);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        Elem<T>::store(bK + static_cast<long long>(dg) * D + lane * EPL + e, k[e]);
-        Elem<T>::store(bV + static_cast<long long>(dg) * D + lane * EPL + e, v[e]);
-      }
-      if (lane == 0) p.buf_S[dg] = sc;
-    } else {
-      const long long o = over_off + (d - B);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        Elem<T>::store(oK + o * D + lane * EPL + e, k[e]);
-        Elem<T>::store(oV + o * D + lane * EPL + e, v[e]);
-      }
-      if (lane == 0) {
-        p.over_S_out[o] = sc;
-        p.over_hv_out[2 * o] = h;
-        p.over_hv_out[2 * o + 1] = vx;
-      }
-    }
-    __syncwarp();
-  }
-  // place selected tokens
-  for (int i = s0; i < s1; ++i) {
-    const int d = tdest[i];
-    if (d < 0) continue;
-    const int code = codes[i];
-    float k[EPL], v[EPL];
-    rd.load_k(code, k);
-    rd.load_v(code, v);
-    const float sc = rd.load_s(code);
-    if (d < B) {
-      const int sg = __shfl_sync(kFull, my_seg, d);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        Elem<T>::store(bK + static_cast<long long>(sg) * D + lane * EPL + e, k[e]);
-        Elem<T>::store(bV + static_cast<long long>(sg) * D + lane * EPL + e, v[e]);
-      }
-      if (lane == 0) p.buf_S[sg] = sc;
-    } else {
-      const long long o = over_off + (d - B);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        Elem<T>::store(oK + o * D + lane * EPL + e, k[e]);
-        Elem<T>::store(oV + o * D + lane * EPL + e, v[e]);
-      }
-      if (lane == 0) {
-        p.over_S_out[o] = sc;
-        p.over_hv_out[2 * o] = h;
-        p.over_hv_out[2 * o + 1] = vx;
-      }
-    }
-  }
-  if (lane == 0) {
-    if (info.z & 1) {
-      // full: the pivot is built by the next kernel, which also releases the row
-      const int pos = atomicAdd(&p.plan[kPlanFullCount], 1);
-      p.full_list[pos] = make_int2(h, ri);
-    } else {
-      p.buf_row_cnt[r] = newcnt;
+  const uint4 val = reinterpret_cast<const uint4*>(src)[part];
+  if (d < p.B) {
+    const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+    const int sg = p.buf_row_seg[r * p.B + d];
+    char* dst = static_cast<char*>(is_v ? p.buf_V : p.buf_K) + static_cast<long long>(sg) * tok_bytes;
+    reinterpret_cast<uint4*>(dst)[part] = val;
+    if (sub == 0) p.buf_S[sg] = sc;
+  } else {
+    const long long o = p.head_base[h].y + p.row_pref[hb + ri].y + (d - p.B);
+    char* dst = static_cast<char*>(is_v ? p.over_V_out : p.over_K_out) + o * tok_bytes;
+    reinterpret_cast<uint4*>(dst)[part] = val;
+    if (sub == 0) {
+      p.over_S_out[o] = sc;
+      p.over_hv_out[2 * o] = h;
+      p.over_hv_out[2 * o + 1] = vx;
     }
   }
 }
@@ -1078,7 +1109,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct ScratchLayout {
   size_t keys_a, keys_b, vals_a, vals_b, n_tok, n_rows, row_vx, row_start, row_info, row_pref, old_dest, tok_dest,
-      tok_sim, tok_score, head_tot, head_base, plan, free_stage, defer_list, full_list, total;
+      tok_sim, tok_score, head_tot, head_base, plan, free_stage, defer_list, full_list, move_list, tok_row, total;
 };
 
 ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
@@ -1098,6 +1129,7 @@ ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
   L.head_tot = take(static_cast<size_t>(heads) * 16); L.head_base = take(static_cast<size_t>(heads) * 16);
   L.plan = take(kPlanSize * 4); L.free_stage = take(static_cast<size_t>(buf_cap) * 4);
   L.defer_list = take(hn * 8); L.full_list = take(hn * 8);
+  L.move_list = take(hn * 8); L.tok_row = take(hn * 4);
   L.total = off;
   return L;
 }
@@ -1113,7 +1145,11 @@ int launch_merge(MergeParams& mp, cudaStream_t st) {
   rows_phase_a2_kernel<T, 2><<<148 * 4, 256, 0, st>>>(mp);
   scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp);
   scan_plan_kernel<<<1, 1024, 0, st>>>(mp);
-  rows_phase_b1_kernel<T, 2><<<grid_rows, warps * 32, 0, st>>>(mp);
+  rows_phase_b1a_kernel<<<grid_a1, 256, 0, st>>>(mp);
+  rows_phase_b1m_kernel<T, 2><<<148 * 6, 256, 0, st>>>(mp);
+  const int vec = mp.D * static_cast<int>(sizeof(T)) / 16;
+  dim3 grid_tok(static_cast<unsigned>((static_cast<long long>(mp.ncap) * 2 * vec + 255) / 256), mp.heads);
+  tokens_place_kernel<<<grid_tok, 256, 0, st>>>(mp, vec, static_cast<int>(sizeof(T)));
   rows_phase_b2_kernel<T, 2><<<148 * 8, 128, 0, st>>>(mp);
   const int fin_blocks = (mp.buf_cap + 255) / 256;
   finalize_kernel<<<fin_blocks, 256, 0, st>>>(mp);
@@ -1184,6 +1220,8 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
   mp.free_stage = reinterpret_cast<int*>(base + L.free_stage);
   mp.defer_list = reinterpret_cast<int2*>(base + L.defer_list);
   mp.full_list = reinterpret_cast<int2*>(base + L.full_list);
+  mp.move_list = reinterpret_cast<int2*>(base + L.move_list);
+  mp.tok_row = reinterpret_cast<int*>(base + L.tok_row);
   int bits = 1;
   while ((1ll << bits) < pool->voxel_used) ++bits;
   mp.passes = (bits + 7) / 8;

@@ -116,6 +116,9 @@ class VoxelKVMerger:
         V_old = self._buf_row_cnt.shape[1]
         if V_new <= V_old:
             return
+        # physical rows grow geometrically (x2) so that re-allocation stays rare; the logical
+        # allocation reported by info() follows the reference's x1.5 rule
+        V_new = max(V_new, 2 * V_old)
         brs = torch.full((H, V_new, B), -1, dtype=torch.int32, device=dev)
         brc = torch.zeros((H, V_new), dtype=torch.int32, device=dev)
         prs = torch.full((H, V_new, P), -1, dtype=torch.int32, device=dev)
@@ -209,11 +212,12 @@ class VoxelKVMerger:
             self._over[1 - self._over_cur] = self._new_over(cap)
             self._over_cap = cap
         ncap = Tn + self._over_max_head
+        ncap = min(MAX_LIST, max(ncap, (ncap + 2047) // 2048 * 2048)) if ncap <= MAX_LIST else ncap
         if ncap > MAX_LIST:
             raise _lib.StacError(f"{ncap} tokens for one pool head in one call; the limit is {MAX_LIST}")
         need = _lib.lib().stac_merge_scratch_bytes(H, ncap, self._buf_cap)
         if self._scratch is None or self._scratch.numel() < need:
-            self._scratch = torch.empty(int(need * 1.25), dtype=torch.uint8, device=self.device)
+            self._scratch = torch.empty(int(need * 1.5), dtype=torch.uint8, device=self.device)
         pool = self._pool_struct()
         ev = StacEvicted()
         ev.k, ev.v = k_cache.data_ptr(), v_cache.data_ptr()
