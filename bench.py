@@ -35,7 +35,9 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(layers=24, heads=16, head_dim=64, tpf=1041, special=5, patch_h=37, patch_w=28, chunk=4, window=8,
            hh=2, pinned=[0], retrieval=2, voxel_size=0.05, init_voxels=4096, buf_cap=8, piv_cap=4,
-           temperature=0.9, prefill_chunks=40)
+           temperature=0.9, prefill_chunks=40,
+           # bounded voxel memory of BASELINE config 5: 2M slots per layer
+           max_buffer_slots=2_000_000 * 24, max_pivot_slots=2_000_000 * 24)
 ATTN_TRAFFIC_BYTES_PER_CALL = 130.5e6
 METRIC = "stac_hot_path_streaming_frames_per_sec"
 WORKLOAD = ("config4-hot-path: CausalVGGT+STAC stream shapes (24 layers x 16 heads x 64, 1041 tokens/frame, "
@@ -162,7 +164,8 @@ class Stream:
                               voxel_size=c["voxel_size"], init_voxels=c["init_voxels"], voxel_buf_cap=c["buf_cap"],
                               voxel_piv_cap=c["piv_cap"], voxel_backend="cuda", sim_threshold=0.8,
                               replace_threshold=0.8, score_threshold=0.2, slab_growth=1024, slab_cap=10000,
-                              seg_size=1, retrieval_size=c["retrieval"], allocator="segment", attn_backend="cuda")
+                              seg_size=1, retrieval_size=c["retrieval"], allocator="segment", attn_backend="cuda",
+                              max_buffer_slots=c["max_buffer_slots"], max_pivot_slots=c["max_pivot_slots"])
         self.kv.reset()
         Tq, H, D, L = c["chunk"] * c["tpf"], c["heads"], c["head_dim"], c["layers"]
         g = torch.Generator(device="cpu").manual_seed(seed)

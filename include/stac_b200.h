@@ -153,7 +153,9 @@ int stac_compact(const int* keep_idx, int n_rows, int n_keep, int T_buf, int hea
  * pivots, one token per pool segment.  Same observable state as the reference's
  * SegmentedSlabPool with seg_size = 1 (stac/allocator.py:2036-2506): row_seg[row][column] is
  * the segment id, row_cnt[row] the occupied columns, a LIFO free list plus a bump counter.
- * Rows are laid out [heads][voxel_cap].  The caller owns and grows every array.
+ * Rows are laid out [heads][voxel_cap].  The caller owns and grows every array.  If a call
+ * does not fit buf_cap / piv_cap, rows are skipped in (head, voxel) order (their selected tokens
+ * are dropped and counted in STAC_META_DROPPED): a caller that stops growing gets a bounded pool.
  * ------------------------------------------------------------------------------------- */
 enum stac_meta_index {       /* int32 counters in device memory, pool->meta[STAC_META_SIZE] */
   STAC_META_BUF_TOP = 0,     /* fresh buffer segment ids handed out so far */
@@ -162,6 +164,7 @@ enum stac_meta_index {       /* int32 counters in device memory, pool->meta[STAC
   STAC_META_OVER_COUNT = 3,  /* tokens in the carried overflow list */
   STAC_META_BUF_USED = 4,    /* tokens currently buffered */
   STAC_META_PIV_USED = 5,    /* pivots currently stored */
+  STAC_META_DROPPED = 6,     /* tokens dropped because a bounded pool was full (cumulative) */
   STAC_META_SIZE = 8
 };
 

@@ -82,13 +82,19 @@ class VoxelMerger:
     """Voxel KV memory with P pivots and a B-token buffer per (head, voxel)."""
 
     def __init__(self, heads, dim, init_voxels=1, pivot_cap=4, budget_cap=8,
-                 sim_thresh=0.8, replace_thresh=0.8, score_thresh=0.2, dtype="f32"):
+                 sim_thresh=0.8, replace_thresh=0.8, score_thresh=0.2, dtype="f32",
+                 max_buf_slots=None, max_piv_slots=None):
         self.H, self.D, self.P, self.B = heads, dim, pivot_cap, budget_cap
         self.sim_thresh = float(sim_thresh)
         self.replace_thresh = float(replace_thresh)
         self.score_thresh = float(score_thresh)
         self.dtype = dtype
         self.rnd = make_rounder(dtype)
+        # Optional pool bounds (not in the reference's Python path, which grows without limit):
+        # rows that would open buffer columns / need a pivot segment beyond the bound are skipped
+        # in (head, voxel) order and their selected tokens dropped.
+        self.max_buf_slots, self.max_piv_slots = max_buf_slots, max_piv_slots
+        self.dropped = 0
         self.V_alloc = max(1, int(init_voxels))
         self.V_used = 0
         self.token_count = 0
@@ -184,6 +190,30 @@ class VoxelMerger:
             add = len(kept) - n_old
             plans.append((key, kept, spill, n_old, add))
             total_add += add
+        if self.max_buf_slots is not None or self.max_piv_slots is not None:
+            avail_buf = (len(self.buf.free) + self.max_buf_slots - self.buf.seg_top
+                         if self.max_buf_slots is not None else None)
+            avail_piv = self.max_piv_slots - self.piv.seg_top if self.max_piv_slots is not None else None
+            short = ((avail_buf is not None and total_add > avail_buf) or
+                     (avail_piv is not None and sum(1 for (key, kept, _, _, _) in plans
+                                                    if len(kept) == self.B and self.piv.row_offset[key] < self.P)
+                      > avail_piv))
+            if short:
+                cum_add = cum_piv = 0
+                trimmed = []
+                for (key, kept, spill, n_old, add) in plans:
+                    needs_piv = len(kept) == self.B and self.piv.row_offset[key] < self.P
+                    no_buf = avail_buf is not None and add > 0 and cum_add + add > avail_buf
+                    no_piv = avail_piv is not None and needs_piv and cum_piv + 1 > avail_piv
+                    cum_add += add
+                    cum_piv += 1 if needs_piv else 0
+                    if no_buf or no_piv:
+                        self.dropped += len(selected[key])
+                        continue
+                    trimmed.append((key, kept, spill, n_old, add))
+                plans = trimmed
+                total_add = sum(pl[4] for pl in plans)
+                sel_rows = [pl[0] for pl in plans]
         ids = self.buf.alloc(total_add)
         cursor = 0
         for key, kept, spill, n_old, add in plans:

@@ -44,7 +44,7 @@ class StacEvicted(ctypes.Structure):
     ]
 
 
-META_BUF_TOP, META_BUF_FREE_LEN, META_PIV_TOP, META_OVER_COUNT, META_BUF_USED, META_PIV_USED = range(6)
+META_BUF_TOP, META_BUF_FREE_LEN, META_PIV_TOP, META_OVER_COUNT, META_BUF_USED, META_PIV_USED, META_DROPPED = range(7)
 META_SIZE = 8
 VOXEL_MAX_POINTS = 16384
 
@@ -85,7 +85,7 @@ SIGNATURES = {
 KERNELS_PER_CALL = {
     "stac_attn_colsum": 3, "stac_attn_colsum_noalloc": 3, "stac_selftest_bounded_wait": 1,
     "stac_voxel_hash_clear": 1, "stac_voxel_rehash": 2, "stac_voxel_upsert": 3, "stac_voxel_neighbors": 2,
-    "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 12, "stac_retrieve": 2,
+    "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 16, "stac_retrieve": 2,
 }
 CALLS = {}
 

@@ -127,7 +127,7 @@ struct MergeParams {
 };
 
 enum { kPlanK = 0, kPlanFreeLen, kPlanBufTop, kPlanPivTop, kPlanTotalAdd, kPlanTotalFull, kPlanTotalOver,
-       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanMoveCount, kPlanSize = 16 };
+       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanMoveCount, kPlanShort, kPlanAvailBuf, kPlanAvailPiv, kPlanSize = 16 };
 
 // Block-wide exclusive scan, 1024 threads.
 __device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
@@ -617,10 +617,12 @@ __global__ void __launch_bounds__(256) rows_phase_a2_kernel(const MergeParams p)
 }
 
 // ------------------------------------------------------------------------------------ scans
-__global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p) {
+// pass 0 always runs; pass 1 only when pass 0 found the pools too small and rows were trimmed
+__global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p, const int pass) {
   __shared__ int warp_sums[32];
   __shared__ int sh_total;
   __shared__ int carry[4];
+  if (pass == 1 && p.plan[kPlanShort] == 0) return;
   const int h = blockIdx.x;
   const long long hb = static_cast<long long>(h) * p.ncap;
   const int n = p.plan[kPlanAnyValid] ? p.n_rows[h] : 0;
@@ -650,10 +652,11 @@ __global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p
   if (threadIdx.x == 0) p.head_tot[h] = make_int4(carry[0], carry[1], carry[2], carry[3]);
 }
 
-__global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p, const int pass) {
   __shared__ int warp_sums[32];
   __shared__ int sh_total;
   __shared__ int carry[4];
+  if (pass == 1 && p.plan[kPlanShort] == 0) return;
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
   __syncthreads();
   for (int base = 0; base < p.heads; base += 1024) {
@@ -695,6 +698,16 @@ __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p)
     p.plan[kPlanTotalOver] = total_over;
     int abort = 0;
     if (any) {
+      const int avail_buf = free_len + (p.buf_cap - buf_top);
+      const int avail_piv = p.piv_cap - piv_top;
+      if (pass == 0 && (total_add > avail_buf || total_piv > avail_piv)) {
+        // The pools are bounded and this call does not fit: rows are trimmed in (head, voxel)
+        // order by trim_rows_kernel and the plan is recomputed by pass 1.
+        p.plan[kPlanShort] = 1;
+        p.plan[kPlanAvailBuf] = avail_buf;
+        p.plan[kPlanAvailPiv] = avail_piv;
+        return;
+      }
       if (buf_top + (total_add - k) > p.buf_cap || piv_top + total_piv > p.piv_cap || total_over > p.over_cap ||
           free_len - k + total_full * p.B > p.buf_cap)
         abort = 1;
@@ -714,6 +727,35 @@ __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p)
 }
 
 // ------------------------------------------------------------------------------------ phase B
+// Bounded pools: a row that would open new buffer columns, or need a new pivot segment, beyond
+// what is left is skipped as a whole (its selected tokens are dropped, the row stays as it
+// was).  The cut follows the allocation order, i.e. (head, voxel) ascending, so it is
+// deterministic; merges into existing pivots done in phase A stay.
+__global__ void __launch_bounds__(256) trim_rows_kernel(const MergeParams p) {
+  const int h = blockIdx.y;
+  const int ri = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanShort] == 0) return;
+  if (ri >= p.n_rows[h]) return;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int4 info = p.row_info[hb + ri];
+  if (info.w == 0) return;
+  const int4 pref = p.row_pref[hb + ri];
+  const int4 hbase = p.head_base[h];
+  const bool no_buf = info.x > 0 && hbase.x + pref.x + info.x > p.plan[kPlanAvailBuf];
+  const bool no_piv = (info.z & 2) && hbase.w + pref.w + 1 > p.plan[kPlanAvailPiv];
+  if (!no_buf && !no_piv) return;
+  const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
+  int dropped = 0;
+  for (int i = rst[ri]; i < rst[ri + 1]; ++i) {
+    if (p.tok_dest[hb + i] >= 0) {
+      p.tok_dest[hb + i] = -1;
+      ++dropped;
+    }
+  }
+  p.row_info[hb + ri] = make_int4(0, 0, info.z & ~3, 0);
+  atomicAdd(&p.meta[STAC_META_DROPPED], dropped);
+}
+
 // Phase B, step 1 (one thread per row): hand out the segment ids of the new columns in
 // (row, column) order from the allocation plan, publish the new occupancy, and queue the rows
 // whose buffered tokens change column or whose buffer filled up.
@@ -1143,8 +1185,11 @@ int launch_merge(MergeParams& mp, cudaStream_t st) {
   dim3 grid_a1((mp.ncap + 255) / 256, mp.heads);
   rows_phase_a1_kernel<<<grid_a1, 256, 0, st>>>(mp);
   rows_phase_a2_kernel<T, 2><<<148 * 4, 256, 0, st>>>(mp);
-  scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp);
-  scan_plan_kernel<<<1, 1024, 0, st>>>(mp);
+  scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp, 0);
+  scan_plan_kernel<<<1, 1024, 0, st>>>(mp, 0);
+  trim_rows_kernel<<<grid_a1, 256, 0, st>>>(mp);
+  scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp, 1);
+  scan_plan_kernel<<<1, 1024, 0, st>>>(mp, 1);
   rows_phase_b1a_kernel<<<grid_a1, 256, 0, st>>>(mp);
   rows_phase_b1m_kernel<T, 2><<<148 * 6, 256, 0, st>>>(mp);
   const int vec = mp.D * static_cast<int>(sizeof(T)) / 16;

@@ -50,6 +50,13 @@ class VoxelKVMerger:
         self._token_count = 0
         self._status = status
         self._slab_cap = int(kwargs.get("slab_cap", 1024))
+        # optional bounds on the two segment pools (tokens / pivots); None = grow as needed like
+        # the reference's Python path.  When a bound is hit, rows are skipped in (head, voxel)
+        # order and their tokens dropped (counted in info()["dropped_tokens"]).
+        self._max_buf = kwargs.get("max_buffer_slots", None)
+        self._max_piv = kwargs.get("max_pivot_slots", None)
+        if (self._max_buf is not None and self._max_buf < 1) or (self._max_piv is not None and self._max_piv < 1):
+            raise ValueError("pool bounds must be positive")
         dev = self.device
         H, P, B, D = self.H, self.P, self.B, self.D
         V = self._voxel_alloc
@@ -61,8 +68,8 @@ class VoxelKVMerger:
         self._piv_cap = 0
         self._buf_K = self._buf_V = self._buf_S = self._buf_free = None
         self._piv_K = self._piv_V = self._piv_W = self._piv_S = self._piv_C = None
-        self._grow_buf(max(1024, self._slab_cap * B))
-        self._grow_piv(max(1024, V))
+        self._grow_buf(min(max(1024, self._slab_cap * B), int(self._max_buf) if self._max_buf else 1 << 62))
+        self._grow_piv(min(max(1024, V), int(self._max_piv) if self._max_piv else 1 << 62))
         self._over = [self._new_over(1), self._new_over(1)]
         self._over_cur = 0
         self._over_cap = 1
@@ -116,9 +123,7 @@ class VoxelKVMerger:
         V_old = self._buf_row_cnt.shape[1]
         if V_new <= V_old:
             return
-        # physical rows grow geometrically (x2) so that re-allocation stays rare; the logical
-        # allocation reported by info() follows the reference's x1.5 rule
-        V_new = max(V_new, 2 * V_old)
+        # rows cost 56 bytes per (head, voxel): grow by the reference's x1.5 rule, not faster
         brs = torch.full((H, V_new, B), -1, dtype=torch.int32, device=dev)
         brc = torch.zeros((H, V_new), dtype=torch.int32, device=dev)
         prs = torch.full((H, V_new, P), -1, dtype=torch.int32, device=dev)
@@ -195,11 +200,17 @@ class VoxelKVMerger:
         E = H * Tn + over_in
         # worst-case needs of this call (see the capacity notes in the module docstring)
         need_buf = self._meta_host[META_BUF_TOP] + max(0, E - self._meta_host[META_BUF_FREE_LEN])
+        if self._max_buf is not None:
+            need_buf = min(need_buf, max(int(self._max_buf), self._buf_cap))
         if need_buf > self._buf_cap:
-            self._grow_buf(max(need_buf, int(self._buf_cap * 1.5)))
+            grow = max(need_buf, int(self._buf_cap * 1.5))
+            self._grow_buf(grow if self._max_buf is None else min(grow, max(int(self._max_buf), need_buf)))
         need_piv = self._meta_host[META_PIV_TOP] + (self._meta_host[META_BUF_USED] + E) // self.B + 1
+        if self._max_piv is not None:
+            need_piv = min(need_piv, max(int(self._max_piv), self._piv_cap))
         if need_piv > self._piv_cap:
-            self._grow_piv(max(need_piv, int(self._piv_cap * 1.5)))
+            grow = max(need_piv, int(self._piv_cap * 1.5))
+            self._grow_piv(grow if self._max_piv is None else min(grow, max(int(self._max_piv), need_piv)))
         if E > self._over_cap:
             cap = max(E, int(self._over_cap * 1.5))
             cur = self._over[self._over_cur]
@@ -311,7 +322,8 @@ class VoxelKVMerger:
                     best_compress_ratio=(piv_data + buf_data) / tc,
                     real_compress_ratio=(piv_alloc + buf_alloc) / tc,
                     pivot_pool_used=piv_data, pivot_pool_alloc=piv_alloc,
-                    buffer_pool_used=buf_data, buffer_pool_alloc=buf_alloc)
+                    buffer_pool_used=buf_data, buffer_pool_alloc=buf_alloc,
+                    dropped_tokens=self._meta_host[_lib.META_DROPPED])
 
     def memory(self) -> dict:
         buf_data, buf_alloc, piv_data, piv_alloc = self._pool_counts()

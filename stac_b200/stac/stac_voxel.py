@@ -48,7 +48,10 @@ class STACVoxelKV(HeavyHittersKV):
                              weight_fn=weight_fn, dtype=self.dtype, device=self.device, debug=self.debug,
                              allocator=allocator, backend=voxel_backend, slab_growth=slab_growth,
                              slab_free_policy=slab_free_policy, slab_cap=slab_cap, seg_size=seg_size,
-                             alloc_debug=alloc_debug)
+                             alloc_debug=alloc_debug,
+                             # optional bounds of the voxel memory (extension; None = unbounded)
+                             max_buffer_slots=kwargs.get("max_buffer_slots"),
+                             max_pivot_slots=kwargs.get("max_pivot_slots"))
         self._enable_alloc_cpu = False
         # the reference overwrites recent_size here after the token sizes were derived
         # (stac/stac_voxel.py:109-110); only log lines read it afterwards

@@ -213,3 +213,34 @@ def test_merge_is_deterministic():
         snaps.append(g.snapshot())
     for k in snaps[0]:
         assert np.array_equal(np.asarray(snaps[0][k]), np.asarray(snaps[1][k])), k
+
+
+@pytest.mark.parametrize("max_buf,max_piv", [(2500, None), (None, 150), (1800, 120)])
+def test_bounded_pools_match_oracle(max_buf, max_piv):
+    """With a bound on the segment pools, rows are skipped in (head, voxel) order once the pool
+    is full; state and drop counts must match the oracle's statement of the same rule."""
+    from stac_b200 import ops
+    from stac_b200.stac.merger import VoxelKVMerger
+    name = "gpu_f32"
+    c = cases.merger_config(name)
+    st = ops.DeviceStatus(torch.device(DEV))
+    g = VoxelKVMerger(c["H"], c["D"], init_voxels=c["init_voxels"], pivot_cap=c["P"], budget_cap=c["B"],
+                      sim_thresh=c["sim"], replace_thresh=c["replace"], score_thresh=c["score"], dtype=torch.float32,
+                      device=DEV, slab_cap=16, status=st, max_buffer_slots=max_buf, max_pivot_slots=max_piv)
+    m = VoxelMerger(c["H"], c["D"], c["init_voxels"], c["P"], c["B"], c["sim"], c["replace"], c["score"], "f32",
+                    max_buf_slots=max_buf, max_piv_slots=max_piv)
+    t = VoxelTable(c["voxel_size"])
+    for step, (pts, K, V, S) in enumerate(cases.merger_inputs(name)):
+        ids = t.upsert(quantize(pts, c["voxel_size"]))
+        VX = np.broadcast_to(ids, (c["H"], ids.size)).copy()
+        m.insert_and_merge(K, V, S, VX, t.num_voxels)
+        g.insert_and_merge(torch.from_numpy(K).to(DEV), torch.from_numpy(V).to(DEV), torch.from_numpy(S).to(DEV),
+                           None, torch.from_numpy(VX).to(DEV), t.num_voxels)
+        st.raise_if_set(f"bounded merge step {step}")
+        _compare_pool(g.snapshot(), m, f"bounded step {step}", 1e-3, 1e-5)
+        assert g.info()["dropped_tokens"] == m.dropped, step
+        if max_buf is not None:
+            assert g.snapshot()["buf_top"] <= max_buf
+        if max_piv is not None:
+            assert g.snapshot()["piv_top"] <= max_piv
+    assert m.dropped > 0
