@@ -63,15 +63,15 @@ def synth_points(n_chunks, seed=0):
     out = []
     frame = 0
     pos = np.zeros(3)
-    vel = np.array([0.03, 0.0, 0.01])
+    vel = np.array([0.012, 0.0, 0.004])     # a slow hand-held scan: ~1 cm per frame
     yaw = 0.0
     for _ in range(n_chunks):
         pts = np.zeros((c["chunk"] * c["tpf"], 3), np.float32)
         mask = np.zeros(c["chunk"] * c["tpf"], bool)
         for f in range(c["chunk"]):
-            vel = 0.9 * vel + 0.1 * rs.randn(3) * 0.03 + np.array([0.003, 0, 0])
+            vel = 0.9 * vel + 0.1 * rs.randn(3) * 0.01 + np.array([0.0012, 0, 0])
             pos = pos + vel
-            yaw += 0.01 * rs.randn() + 0.005
+            yaw += 0.003 * rs.randn() + 0.0015
             x = uu * 1.2
             y = vv * 0.9
             wx = x * math.cos(yaw) + pos[0]

@@ -125,6 +125,15 @@ int stac_voxel_neighbors(const int* token_voxel_ids, int n_tokens, int radius_ce
  * H2O bookkeeping on the hot cache (rows = managed layers x heads).
  * ------------------------------------------------------------------------------------- */
 
+/* KVManager.append_kv (stac/kv_manager.py:227-309) for one layer: new keys/values, token t of
+ * head h at k + h*k_head_stride + t*k_row_stride elements (64 contiguous values), go to
+ * positions [old_T, old_T + T_new) of the cache [H][cache_head_stride]; their global token
+ * ids first_token_id + t are written to token_idx i64 [H][idx_head_stride]. */
+int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t k_row_stride,
+                   int64_t v_head_stride, int64_t v_row_stride, void* k_cache, void* v_cache,
+                   int64_t cache_head_stride, int64_t* token_idx, int64_t idx_head_stride, int H, int T_new,
+                   int old_T, int64_t first_token_id, int head_dim, int elem_bytes, stac_stream_t stream);
+
 /* HeavyHittersKV._update_scores (stac/h2o.py:177-216) for one layer: s = colsum * T_live / Tq;
  * positions >= old_T take s, older ones score * temperature + s; counts += 1. */
 int stac_scores_update(const float* colsum, int64_t colsum_head_stride, float* scores, float* counts,

@@ -180,10 +180,57 @@ __global__ void compact_meta_kernel(const int* __restrict__ keep_idx, int n_keep
   }
 }
 
+// New K/V rows of one layer into the tail of the hot cache plus their global token ids, one
+// launch instead of three strided copies (stac/kv_manager.py:285-305).
+__global__ void append_kv_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, long long k_head_stride_vec,
+                                 long long k_row_stride_vec, long long v_head_stride_vec, long long v_row_stride_vec,
+                                 uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
+                                 long long cache_head_stride_vec, long long* __restrict__ token_idx,
+                                 long long idx_head_stride, int T_new, int old_T, long long first_id,
+                                 int vec_per_token) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int h = blockIdx.y;
+  const long long t = gid / vec_per_token;
+  const int part = static_cast<int>(gid % vec_per_token);
+  if (t >= T_new) return;
+  const long long dst = h * cache_head_stride_vec + (old_T + t) * vec_per_token + part;
+  k_cache[dst] = k[h * k_head_stride_vec + t * k_row_stride_vec + part];
+  v_cache[dst] = v[h * v_head_stride_vec + t * v_row_stride_vec + part];
+  if (part == 0) token_idx[h * idx_head_stride + old_T + t] = first_id + t;
+}
+
 }  // namespace
 }  // namespace stac
 
 extern "C" {
+
+int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
+                   int64_t v_row_stride, void* k_cache, void* v_cache, int64_t cache_head_stride, int64_t* token_idx,
+                   int64_t idx_head_stride, int H, int T_new, int old_T, int64_t first_token_id, int head_dim,
+                   int elem_bytes, stac_stream_t stream) {
+  if (k == nullptr || v == nullptr || k_cache == nullptr || v_cache == nullptr || token_idx == nullptr || H <= 0 ||
+      T_new < 0 || old_T < 0)
+    return STAC_ERR_BAD_ARG;
+  const int token_bytes = head_dim * elem_bytes;
+  if (token_bytes % 16 != 0) return STAC_ERR_BAD_ARG;
+  const int epv = 16 / elem_bytes;  // elements per 16-byte vector
+  if ((k_head_stride % epv) || (k_row_stride % epv) || (v_head_stride % epv) || (v_row_stride % epv) ||
+      (cache_head_stride % epv))
+    return STAC_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(k_cache) |
+       reinterpret_cast<uintptr_t>(v_cache)) & 15)
+    return STAC_ERR_BAD_ARG;
+  if (T_new == 0) return STAC_OK;
+  const int vpt = token_bytes / 16;
+  const long long total = static_cast<long long>(T_new) * vpt;
+  dim3 grid(static_cast<unsigned>((total + 255) / 256), H);
+  stac::append_kv_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(k), static_cast<const uint4*>(v), k_head_stride / epv, k_row_stride / epv,
+      v_head_stride / epv, v_row_stride / epv, static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
+      cache_head_stride / epv, reinterpret_cast<long long*>(token_idx), idx_head_stride, T_new, old_T, first_token_id,
+      vpt);
+  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+}
 
 int stac_scores_update(const float* colsum, int64_t colsum_head_stride, float* scores, float* counts,
                        int64_t row_stride, int H, int T_live, int old_T, int Tq, float temperature,

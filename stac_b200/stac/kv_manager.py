@@ -146,13 +146,20 @@ class KVManager:
         if old_T + new_T > self.reserved_buffer_token_size:
             raise RuntimeError(f"hot cache overflow ({old_T}+{new_T} > {self.reserved_buffer_token_size} tokens); "
                                "the CPU spill ring of the reference is not provided")
-        self.key_cache_hot[slot, :, old_T:old_T + new_T, :].copy_(key_states[0])
-        self.value_cache_hot[slot, :, old_T:old_T + new_T, :].copy_(value_states[0])
-        self._offset_hot[slot] = old_T + new_T
+        k, v = key_states[0], value_states[0]
+        if k.dtype != self.dtype or v.dtype != self.dtype or not k.is_cuda:
+            k, v = k.to(self.device, self.dtype), v.to(self.device, self.dtype)
+        if k.stride(2) != 1 or (k.stride(0) % 8) or (k.stride(1) % 8) or (k.data_ptr() % 16):
+            k = k.contiguous()
+        if v.stride(2) != 1 or (v.stride(0) % 8) or (v.stride(1) % 8) or (v.data_ptr() % 16):
+            v = v.contiguous()
         F_new = new_T // self.token_per_f
-        ids = torch.arange(self._processed_frames * self.token_per_f,
-                           (self._processed_frames + F_new) * self.token_per_f, device=self.device)
-        self._token_indices_hot[slot, :, old_T:old_T + new_T].copy_(ids.expand(H, -1))
+        kc, vc, ti = self.key_cache_hot[slot], self.value_cache_hot[slot], self._token_indices_hot[slot]
+        check(_lib.lib().stac_append_kv(ptr(k), ptr(v), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+                                        ptr(kc), ptr(vc), kc.stride(0), ptr(ti), ti.stride(0), H, new_T, old_T,
+                                        self._processed_frames * self.token_per_f, D, 2, stream_ptr()),
+              "stac_append_kv")
+        self._offset_hot[slot] = old_T + new_T
         if slot == self._L_eff - 1:
             self._processed_frames += F_new
 
