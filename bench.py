@@ -151,10 +151,13 @@ class ClockSampler(threading.Thread):
 class Stream:
     """One STAC stream on one GPU, driven like StreamSession.pipeline drives the manager."""
 
-    def __init__(self, device, n_input_sets=3, seed=0):
+    def __init__(self, device, n_input_sets=3, seed=0, heads=None):
         import torch
         from stac_b200.stac import STACVoxelKV
-        c = CFG
+        c = dict(CFG)
+        if heads is not None:
+            c["heads"] = heads          # head-sharded stream: this rank owns `heads` of the 16 heads
+        self.cfg = c
         self.torch, self.dev = torch, device
         buffer_size = c["chunk"] + len(c["pinned"]) + c["window"] + c["hh"]
         self.kv = STACVoxelKV(num_layers=c["layers"], num_heads=c["heads"], head_dim=c["head_dim"],
@@ -188,6 +191,8 @@ class Stream:
         self.done = [None, None]
         self.out_host = torch.empty((1, Tq, H, D), dtype=torch.bfloat16).pin_memory()
         self.chunk_idx = 0
+        self.share_counts = False
+        self.head_counts = None
         self.attn_events = []
         self.merge_events = []
         self.h2d = self.d2h = 0
@@ -212,7 +217,7 @@ class Stream:
             self.ready[slot] = ev
 
     def step(self, pts, mask, host_io=False, time_kernels=False, next_inputs=None):
-        torch, kv, c = self.torch, self.kv, CFG
+        torch, kv, c = self.torch, self.kv, self.cfg
         L = c["layers"]
         s = self.chunk_idx % len(self.host)
         h2d = d2h = 0
@@ -245,6 +250,10 @@ class Stream:
         if retrieval_due(self.chunk_idx):
             for l in range(L):
                 kv.retrieve_kv(l, return_buf=True)
+            if self.share_counts and kv._ret is not None:
+                # head-sharded stream: every rank learns the valid pivot count of every head
+                from stac_b200.sharding import gather_head_counts
+                self.head_counts = gather_head_counts(kv._ret[2].sum(dim=1), L)
         if time_kernels:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -280,8 +289,8 @@ def job_throughput(frames_per_rank, ms, world):
     return frames_per_rank * world / (ms / 1e3)
 
 
-def attn_flops(M, N, r=1.0):
-    return (4.0 + 2.0 * r) * CFG["heads"] * M * N * CFG["head_dim"]
+def attn_flops(M, N, r=1.0, heads=None):
+    return (4.0 + 2.0 * r) * (heads or CFG["heads"]) * M * N * CFG["head_dim"]
 
 
 def run_ours(args):
@@ -302,9 +311,19 @@ def run_ours(args):
     c = CFG
     K, W = args.steps, max(args.warmup, 3)
     n_chunks = c["prefill_chunks"] + 2 * (W + K)
-    points = synth_points(n_chunks, seed=rank)
+    shard_heads = args.shard == "heads" and world > 1
+    if shard_heads:
+        from stac_b200.sharding import head_slice
+        hs = head_slice(rank, world, c["heads"])
+        local_heads = hs.stop - hs.start
+        points = synth_points(n_chunks, seed=0)       # one stream: every rank sees the same points
+        stream = Stream(dev, seed=rank, heads=local_heads)
+        stream.share_counts = True
+    else:
+        local_heads = c["heads"]
+        points = synth_points(n_chunks, seed=rank)
+        stream = Stream(dev, seed=rank)
     pts_dev = [(torch.from_numpy(p).to(dev), torch.from_numpy(m).to(dev)) for p, m in points]
-    stream = Stream(dev, seed=rank)
     it = iter(range(n_chunks))
 
     def run_phase(n, host_io, timed):
@@ -339,13 +358,14 @@ def run_ours(args):
     ms_e2e = run_phase(K, True, False)             # timed, host buffers
     stream.kv.check_status()
 
-    value = job_throughput(c["chunk"] * K, ms_dev, world)
-    e2e = job_throughput(c["chunk"] * K, ms_e2e, world)
+    n_streams = 1 if shard_heads else world
+    value = job_throughput(c["chunk"] * K, ms_dev, n_streams)
+    e2e = job_throughput(c["chunk"] * K, ms_e2e, n_streams)
     # roofline of the dominant kernel pair (attention forward + column sums), per call
     att_ms, att_fl = [], []
     for e0, e1, M, N in stream.attn_events:
         att_ms.append(e0.elapsed_time(e1))
-        att_fl.append(attn_flops(M, N))
+        att_fl.append(attn_flops(M, N, heads=local_heads))
     mrg_ms = [e0.elapsed_time(e1) for e0, e1 in stream.merge_events]
     peaks = {}
     try:
@@ -358,11 +378,14 @@ def run_ours(args):
     info = stream.kv.get_merger_info()
     line = {
         "metric": METRIC, "value": round(value, 3), "unit": "frames/s", "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": round(ms_dev / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms_dev / K, 4), "higher_is_better": True,
+        "scaling": "strong" if shard_heads else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames_per_step": c["chunk"], "streams": world,
+        "config": {"workload": WORKLOAD, "frames_per_step": c["chunk"], "streams": n_streams,
                    "l2_policy": "inputs larger than L2 (hot cache 1.5 GB per stream, rotating q/k/v sets)",
-                   "prefill_chunks": c["prefill_chunks"], "parallelism": f"{world} independent stream(s)"},
+                   "prefill_chunks": c["prefill_chunks"], "parallelism": (f"1 stream, {c['heads']} heads sharded over {world} ranks (voxel memory sharded by head, "
+                                   "NCCL all-gather of per-head retrieval counts)") if shard_heads
+                   else f"{world} independent stream(s)"},
         "e2e": {"value": round(e2e, 3), "unit": "frames/s", "h2d_bytes_per_step": stream.h2d,
                 "d2h_bytes_per_step": stream.d2h, "ms_per_step": round(ms_e2e / K, 4)},
         "gpu_launches": launches,
@@ -584,6 +607,9 @@ if __name__ == "__main__":
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", default="streams", choices=["streams", "heads"],
+                    help="N > 1: one independent stream per GPU (default, weak scaling) or ONE stream whose heads "
+                         "and voxel memory are sharded over the GPUs (strong scaling)")
     ap.add_argument("--microbench", default=None, choices=["attn", "merge"],
                     help="kernel microbenchmarks used for profiling (not the headline line)")
     ap.add_argument("--lk", type=int, default=10376, help="attention microbench: number of keys")

@@ -294,10 +294,9 @@ class VoxelKVMerger:
         output, pivots ordered by W descending, bias log C, padding -inf.  With a positive
         retrieve_size the reference never returns buffer tokens, whatever return_buf says."""
         req = int(retrieve_size) if retrieve_size is not None else -1
-        if req <= 0:
-            raise NotImplementedError("unbounded retrieval (retrieve_size <= 0) is not provided by the "
-                                      "sm_100a path; pass a positive retrieve_size")
         dev = self.device
+        if req <= 0:
+            return self._retrieve_unbounded(voxel_ids, return_buf, want_idx)
         if voxel_ids is None:
             ids = torch.arange(int(self._voxel_offset), device=dev, dtype=torch.int32)
         else:
@@ -307,6 +306,70 @@ class VoxelKVMerger:
         if ids.numel() == 0:
             ids = torch.zeros(1, dtype=torch.int32, device=dev)
         return self.retrieve_device(ids, cnt, req, want_idx)
+
+    @torch.no_grad()
+    def _retrieve_unbounded(self, voxel_ids, return_buf, want_idx=False):
+        """retrieve_size <= 0 (stac/merger.py:1424-1543): output width = (#queried voxels) * P,
+        plus, with return_buf, the buffered tokens of those voxels ((voxel, column) order, bias 0)
+        padded to the longest head.  The output size depends on data, so this mode reads counts
+        back to the host; it is assembled from the pool tensors with torch indexing ops (device
+        plumbing only, no arithmetic beyond log C) and is not on the streaming path, which uses
+        a fixed retrieve_size."""
+        dev, H, P, B, D = self.device, self.H, self.P, self.B, self.D
+        if voxel_ids is None:
+            vid = torch.arange(int(self._voxel_offset), device=dev, dtype=torch.int64)
+        else:
+            vid = torch.unique(voxel_ids.to(device=dev, dtype=torch.int64))
+            vid = vid[(vid >= 0) & (vid < self._voxel_offset)]
+        Q = int(vid.numel())
+        R = Q * P
+
+        def empty(n):
+            return (torch.zeros(H, n, D, dtype=self.dtype, device=dev), torch.zeros(H, n, D, dtype=self.dtype, device=dev),
+                    torch.zeros(H, n, dtype=torch.bool, device=dev),
+                    torch.full((H, n), float("-inf"), dtype=torch.float32, device=dev),
+                    torch.full((H, n, 2), -1, dtype=torch.int32, device=dev))
+
+        def done(t):
+            return t if want_idx else t[:4]
+        if Q == 0:
+            return done(empty(R))
+        cnt = self._piv_row_cnt[:, vid]                                   # [H,Q]
+        seg = self._piv_row_seg[:, vid, :]                                # [H,Q,P]
+        slot = torch.arange(P, device=dev).view(1, 1, P)
+        mask = (slot < cnt.unsqueeze(-1)).reshape(H, R)
+        if not bool(mask.any()):
+            return done(empty(R))
+        segf = seg.reshape(H, R).clamp(min=0).long()
+        W = torch.where(mask, self._piv_W[segf], torch.zeros((), device=dev))
+        order = torch.argsort(W, dim=1, descending=True, stable=True)      # valid pivots first
+        segs = torch.gather(segf, 1, order)
+        m = torch.gather(mask, 1, order)
+        K = self._piv_K[segs] * m.unsqueeze(-1).to(self.dtype)
+        V = self._piv_V[segs] * m.unsqueeze(-1).to(self.dtype)
+        C = self._piv_C[segs]
+        bias = torch.where(m, torch.log(C.clamp_min(1e-9)), torch.full((), float("-inf"), device=dev))
+        vox = vid.view(1, Q, 1).expand(H, Q, P).reshape(H, R)
+        idx = torch.stack([torch.gather(vox, 1, order), torch.gather(slot.expand(H, Q, P).reshape(H, R), 1, order)], -1)
+        idx = torch.where(m.unsqueeze(-1), idx, torch.full((), -1, device=dev, dtype=idx.dtype)).to(torch.int32)
+        if not return_buf:
+            return done((K, V, m, bias, idx))
+        bcnt = self._buf_row_cnt[:, vid]                                   # [H,Q]
+        bseg = self._buf_row_seg[:, vid, :].reshape(H, Q * B)
+        col = torch.arange(B, device=dev).view(1, 1, B)
+        bmask = (col < bcnt.unsqueeze(-1)).reshape(H, Q * B)
+        Rb = int(bmask.sum(dim=1).max().item())
+        if Rb <= 0:
+            return done((K, V, m, bias, idx))
+        border = torch.argsort((~bmask).to(torch.int8), dim=1, stable=True)[:, :Rb]   # keeps (voxel, column) order
+        bm = torch.gather(bmask, 1, border)
+        bs = torch.gather(bseg.clamp(min=0).long(), 1, border)
+        Kb = self._buf_K[bs] * bm.unsqueeze(-1).to(self.dtype)
+        Vb = self._buf_V[bs] * bm.unsqueeze(-1).to(self.dtype)
+        bb = torch.where(bm, torch.zeros((), device=dev), torch.full((), float("-inf"), device=dev))
+        ib = torch.full((H, Rb, 2), -1, dtype=torch.int32, device=dev)
+        return done((torch.cat([K, Kb], 1), torch.cat([V, Vb], 1), torch.cat([m, bm], 1), torch.cat([bias, bb], 1),
+                     torch.cat([idx, ib], 1)))
 
     # ------------------------------------------------------------------ stats
     def _pool_counts(self):

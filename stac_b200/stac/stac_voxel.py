@@ -208,16 +208,25 @@ class STACVoxelKV(HeavyHittersKV):
                 return 0, 0
             ids, count = self._recent_voxel_ids
             if R <= 0:
-                raise NotImplementedError("retrieval_size <= 0 (unbounded retrieval) is not provided")
-            K, V, M, B = self._vstore.retrieve_device(ids, count, R)
+                # unbounded mode: the output width depends on the data (one host read of the count)
+                n = int(count.item())
+                K, V, M, B = self._vstore.retrieve(voxel_ids=ids[:n], return_buf=kwargs.get("return_buf", False),
+                                                   retrieve_size=R)
+            else:
+                K, V, M, B = self._vstore.retrieve_device(ids, count, R)
         else:
-            K, V, M, B = self._vstore.retrieve(voxel_ids=voxel_ids, retrieve_size=R)
+            K, V, M, B = self._vstore.retrieve(voxel_ids=voxel_ids, return_buf=kwargs.get("return_buf", False),
+                                               retrieve_size=R)
         self._ret = (K, V, M, B)
+        Tm = K.shape[1] if R < 0 else min(K.shape[1], R)
         for s in range(L):
-            self.key_cache_retrieval[s] = K[s * H:(s + 1) * H]
-            self.value_cache_retrieval[s] = V[s * H:(s + 1) * H]
-            self._bias_retrieval[s] = B[s * H:(s + 1) * H]
-            self._offset_retrieval[s] = R
+            self._clear_retrieval_cache(s)
+            if Tm == 0:
+                continue
+            self.key_cache_retrieval[s] = K[s * H:(s + 1) * H, :Tm]
+            self.value_cache_retrieval[s] = V[s * H:(s + 1) * H, :Tm]
+            self._bias_retrieval[s] = B[s * H:(s + 1) * H, :Tm]
+            self._offset_retrieval[s] = Tm
         return 0, 0
 
     # ------------------------------------------------------------------ public API

@@ -115,3 +115,40 @@ def test_two_rank_timing_is_max_over_ranks():
         assert p.exitcode == 0
     assert [r[1] for r in res] == [150.0, 150.0]
     assert all(abs(r[2] - 32 / 0.15) < 1e-9 for r in res)
+
+
+def _shard_rank_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    from stac_b200.sharding import gather_head_counts, head_slice
+    L, H = 3, 8
+    full = torch.arange(L * H, dtype=torch.int32).reshape(L, H) * 7 % 11
+    sl = head_slice(rank, world, H)
+    got = gather_head_counts(full[:, sl].reshape(-1), L)
+    q.put((rank, got.tolist(), full.tolist(), [sl.start, sl.stop]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_head_sharding_counts_two_ranks():
+    """Head-sharded stream: every rank ends with the per-head retrieval counts of all heads."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29600 + os.getpid() % 1000
+    procs = [ctx.Process(target=_shard_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res[0][3] == [0, 4] and res[1][3] == [4, 8]
+    for _, got, full, _ in res:
+        assert got == full
+    from stac_b200.sharding import head_slice
+    with pytest.raises(ValueError):
+        head_slice(0, 3, 16)

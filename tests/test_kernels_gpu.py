@@ -194,6 +194,18 @@ def test_merge_and_retrieve_match_oracle(name):
         fin = np.isfinite(Bo)
         assert np.array_equal(np.isfinite(Bg.cpu().numpy()), fin)
         np.testing.assert_allclose(Bg.cpu().numpy()[fin], Bo[fin], rtol=1e-5, atol=1e-6)
+    # unbounded mode (retrieve_size <= 0): width = #voxels * P, optionally followed by buffer tokens
+    q = rs.randint(0, t.num_voxels, size=min(t.num_voxels, 40)).astype(np.int64)
+    for rb in (False, True):
+        Kg, Vg, Mg, Bg, Ig = g.retrieve(torch.from_numpy(q).to(DEV), rb, -1, want_idx=True)
+        Ko, Vo, Mo, Bo, Io = m.retrieve(q, -1, rb)
+        assert Kg.shape == Ko.shape, (name, rb)
+        assert np.array_equal(Mg.cpu().numpy(), Mo) and np.array_equal(Ig.cpu().numpy(), Io), (name, rb)
+        np.testing.assert_allclose(Kg.float().cpu().numpy(), Ko, rtol=rtol, atol=atol)
+        np.testing.assert_allclose(Vg.float().cpu().numpy(), Vo, rtol=rtol, atol=atol)
+        fin = np.isfinite(Bo)
+        assert np.array_equal(np.isfinite(Bg.cpu().numpy()), fin)
+        np.testing.assert_allclose(Bg.cpu().numpy()[fin], Bo[fin], rtol=1e-5, atol=1e-6)
 
 
 def test_merge_is_deterministic():
