@@ -367,20 +367,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // first key tile.  Nothing is ever rescaled: P V accumulates in TMEM across all key tiles of
 // the row block, three softmax warpgroups take key tiles round-robin and keep only a partial
 // row sum each.  The scheme is exact as long as no later score exceeds the reference by more
-// than 2^kFastHeadroom (probabilities then stay far inside the bf16 / fp32 range); a warp that
-// sees a larger score raises `fallback` and the exact kernel, launched right behind this one,
-// recomputes the call.
+// than 2^60 (probabilities then stay far inside the bf16 / fp32 range); a row whose sum of
+// probabilities leaves that range raises `fallback` and the exact kernel, launched right
+// behind this one, recomputes the call.
+//
+// Shared memory carries only the operands TMA brings in.  Each warpgroup owns one 128-column
+// TMEM buffer: the scores of its tile arrive there, the probabilities go back into the same
+// columns (bf16, two per column) and feed the P V MMA as its A operand straight from tensor
+// memory.  The tensor pipe has a floor of about 48 clocks per MMA instruction whatever its
+// width and stalls while its issuing thread does anything else, so scores use one N = 128
+// instruction per K step, the two MMA streams (scores, P V) have a warp each, and the
+// instructions of a group are issued back to back with operands prepared beforehand.
 // ---------------------------------------------------------------------------------------
-constexpr int kFastThreads = 512;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA), 1..3 softmax
-constexpr int kFastKStages = 2;
-constexpr int kFastVStages = 4;
-constexpr float kFastHeadroom = 60.f;
+constexpr int kFastThreads = 512;   // warpgroup 0 control (warp 0 TMA, warps 1-2 MMA issue), 1..3 softmax
+constexpr int kFastKStages = 4;
+constexpr int kFastVStages = 5;
+constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 
 struct FastSmem {
   uint8_t q[kTileBytes];
   uint8_t k[kFastKStages][kTileBytes];
   uint8_t v[kFastVStages][kTileBytes];
-  uint8_t p[3][2 * kTileBytes];
   float bias2[3][kBN];
   float m_ref[kBM];
   float lpart[3][kBM];
@@ -389,14 +396,38 @@ struct FastSmem {
   uint64_t k_empty[kFastKStages];
   uint64_t v_full[kFastVStages];
   uint64_t v_empty[kFastVStages];
-  uint64_t s_full[3];
-  uint64_t s_free[3];
-  uint64_t p_full[3];
-  uint64_t p_free[3];
+  uint64_t s_full[3];    // scores of a tile are in TMEM
+  uint64_t p_full[3];    // its probabilities are in TMEM
+  uint64_t buf_free[3];  // the P V MMAs that read them are done
   uint64_t ref_ready;
   uint64_t o_done;
   uint32_t tmem_base;
 };
+
+// 32 scores -> 32 probabilities relative to the row reference, packed as 16 bf16 pairs.
+template <bool kBias>
+__device__ __forceinline__ void fast_exp_chunk(const uint32_t (&s)[32], uint32_t (&pk)[16], const float* bias2,
+                                               float c2, float m_ref, float& l0, float& l1) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    float e0, e1, e2, e3;
+    if (kBias) {
+      e0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), c2, bias2[i + 0]) - m_ref);
+      e1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c2, bias2[i + 1]) - m_ref);
+      e2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c2, bias2[i + 2]) - m_ref);
+      e3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c2, bias2[i + 3]) - m_ref);
+    } else {
+      e0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), c2, -m_ref));
+      e1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c2, -m_ref));
+      e2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c2, -m_ref));
+      e3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c2, -m_ref));
+    }
+    l0 += e0 + e1;
+    l1 += e2 + e3;
+    pk[i / 2] = pack_bf16x2(e0, e1);
+    pk[i / 2 + 1] = pack_bf16x2(e2, e3);
+  }
+}
 
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
@@ -421,11 +452,10 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
-    for (int g = 0; g < 3; ++g) {
-      mbar_init(&sm.s_full[g], 1);
-      mbar_init(&sm.s_free[g], 128);
-      mbar_init(&sm.p_full[g], 128);
-      mbar_init(&sm.p_free[g], 1);
+    for (int b = 0; b < 3; ++b) {
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.p_full[b], 128);
+      mbar_init(&sm.buf_free[b], 1);
     }
     mbar_init(&sm.ref_ready, 128);
     mbar_init(&sm.o_done, 1);
@@ -439,7 +469,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t o_tmem = tmem + 3 * kBN;
+  const uint32_t o_tmem = tmem + 3 * kBN;   // columns 384..447
 
   if (warp < 4) {
     setmaxnreg_dec<40>();
@@ -450,9 +480,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tma_prefetch_desc(&tm_v_hot);
       mbar_arrive_expect_tx(&sm.bar_q, kTileBytes);
       tma_load_3d(sm.q, &tm_q, &sm.bar_q, 0, h, m_tile * kBM);
+      int ks = 0, kr = 0, vs = 0, vr = 0;   // stage and round of the K and V rings
       for (int j = 0; j < n_tiles; ++j) {
-        const int ks = j % kFastKStages, kr = j / kFastKStages;
-        const int vs = j % kFastVStages, vr = j / kFastVStages;
         const bool hot = j < n_hot;
         const int n0 = (hot ? j : j - n_hot) * kBN;
         if (kr > 0) mbar_wait(&sm.k_empty[ks], (kr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
@@ -461,51 +490,62 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (vr > 0) mbar_wait(&sm.v_empty[vs], (vr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         mbar_arrive_expect_tx(&sm.v_full[vs], kTileBytes);
         tma_load_3d(sm.v[vs], hot ? &tm_v_hot : &tm_v_ret, &sm.v_full[vs], 0, n0, h);
+        if (++ks == kFastKStages) { ks = 0; ++kr; }
+        if (++vs == kFastVStages) { vs = 0; ++vr; }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
       // ---------------------------------------------------------------- MMA issuer: S = Q K^T
-      // (its own thread, so a score tile is issued the moment its TMEM buffer is released,
-      // independent of the P V stream)
+      // (all lanes run the loop, one elected lane issues)
       constexpr uint32_t idesc_s = umma_idesc_bf16(kBM, kBN, 0);
       mbar_wait(&sm.bar_q, 0, p.err, DEV_TIMEOUT_TMA);
       const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q));
       const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0]));
+      int g = 0, it = 0, ks = 0, kr = 0;
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
-        const int g = j % 3, it = j / 3, ks = j % kFastKStages;
-        mbar_wait(&sm.k_full[ks], (j / kFastKStages) & 1, p.err, DEV_TIMEOUT_TMA);
-        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        tc_fence_after();
         const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(ks * (kTileBytes >> 4));
         const uint32_t d = tmem + g * kBN;
-        umma_ss(d, q_desc, k_desc, idesc_s, 0u);
-        umma_ss(d, q_desc + 2, k_desc + 2, idesc_s, 1u);
-        umma_ss(d, q_desc + 4, k_desc + 4, idesc_s, 1u);
-        umma_ss(d, q_desc + 6, k_desc + 6, idesc_s, 1u);
-        umma_commit(&sm.s_full[g]);
-        umma_commit(&sm.k_empty[ks]);
+        mbar_wait(&sm.k_full[ks], kr & 1, p.err, DEV_TIMEOUT_TMA);
+        if (it > 0) mbar_wait(&sm.buf_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+        if (elect_one()) {
+          umma_ss(d, q_desc, k_desc, idesc_s, 0u);
+          umma_ss(d, q_desc + 2, k_desc + 2, idesc_s, 1u);
+          umma_ss(d, q_desc + 4, k_desc + 4, idesc_s, 1u);
+          umma_ss(d, q_desc + 6, k_desc + 6, idesc_s, 1u);
+          umma_commit(&sm.s_full[g]);
+          umma_commit(&sm.k_empty[ks]);
+        }
+        __syncwarp();
+        if (++ks == kFastKStages) { ks = 0; ++kr; }
+        if (++g == 3) { g = 0; ++it; }
       }
-    } else if (warp == 2 && lane == 0) {
+    } else if (warp == 2) {
       // ---------------------------------------------------------------- MMA issuer: O += P V
       constexpr uint32_t idesc_o = umma_idesc_bf16(kBM, kD, 1);
-      const uint64_t p_desc0 = smem_desc_sw128(smem_u32(sm.p[0]));
       const uint64_t v_desc0 = smem_desc_sw128(smem_u32(sm.v[0]));
+      int g = 0, it = 0, vs = 0, vr = 0;
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
-        const int g = j % 3, it = j / 3, vs = j % kFastVStages;
-        mbar_wait(&sm.v_full[vs], (j / kFastVStages) & 1, p.err, DEV_TIMEOUT_TMA);
+        // A: 16 keys = 8 columns of packed probabilities; B: V advances 16 rows = 2048 bytes
+        const uint32_t pa = tmem + g * kBN;
+        const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kTileBytes >> 4));
+        const uint32_t acc0 = j > 0 ? 1u : 0u;
+        mbar_wait(&sm.v_full[vs], vr & 1, p.err, DEV_TIMEOUT_TMA);
         mbar_wait(&sm.p_full[g], it & 1, p.err, DEV_TIMEOUT_CONSUMER);
         tc_fence_after();
-        const uint64_t pa = p_desc0 + static_cast<uint64_t>(g * ((2 * kTileBytes) >> 4));
-        const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kTileBytes >> 4));
-        // keys 0..63 live in the first 64-key atom of P, 64..127 in the second; V advances 16 rows
+        if (elect_one()) {
+          umma_ts(o_tmem, pa, vb, idesc_o, acc0);
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk)
-          umma_ss(o_tmem, pa + static_cast<uint64_t>((kk >> 2) * (kTileBytes >> 4) + 2 * (kk & 3)),
-                  vb + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&sm.p_free[g]);
-        umma_commit(&sm.v_empty[vs]);
-        if (j == n_tiles - 1) umma_commit(&sm.o_done);
+          for (int kk = 1; kk < kBN / 16; ++kk)
+            umma_ts(o_tmem, pa + kk * 8, vb + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, 1u);
+          umma_commit(&sm.buf_free[g]);
+          umma_commit(&sm.v_empty[vs]);
+          if (j == n_tiles - 1) umma_commit(&sm.o_done);
+        }
+        __syncwarp();
+        if (++vs == kFastVStages) { vs = 0; ++vr; }
+        if (++g == 3) { g = 0; ++it; }
       }
     }
   } else {
@@ -515,11 +555,12 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + g * kBN;
     const float c2 = p.scale_log2;
+    const float* bias2 = sm.bias2[g];
     float m_ref = 0.f;
     float l0 = 0.f, l1 = 0.f;
-    bool overflow = false;
-    uint32_t ra[32], rb[32];
+    uint32_t ra[32], rb[32], pk[16];
     int it = 0;
     for (int j = g; j < n_tiles; j += 3, ++it) {
       const bool is_ret = j >= n_hot;
@@ -535,21 +576,25 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
       tc_fence_after();
-      const uint32_t s_addr = tmem + lane_base + g * kBN;
+      tmem_ld32(s_addr, ra);
       if (j == 0) {
         // exact row maximum of the first tile = the row's reference for the whole call
         float mx = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          tmem_ld32(s_addr + c * 32, ra);
           tmem_ld_wait();
+          tmem_ld32(s_addr + ((c + 1) & 3) * 32, rb);   // last turn re-fetches the first 32 keys
           if (need_bias) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(ra[i]), c2, sm.bias2[g][c * 32 + i]));
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(ra[i]), c2, bias2[c * 32 + i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(ra[i]) * c2);
+            for (int i = 0; i < 32; i += 2)
+              mx = fmax3(mx, __uint_as_float(ra[i]) * c2, __uint_as_float(ra[i + 1]) * c2);
           }
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ra[i] = rb[i];
         }
         m_ref = (mx == -INFINITY) ? 0.f : mx;
         sm.m_ref[row] = m_ref;
@@ -558,59 +603,34 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_wait(&sm.ref_ready, 0, p.err, DEV_TIMEOUT_CONSUMER);
         m_ref = sm.m_ref[row];
       }
-      if (it > 0) mbar_wait(&sm.p_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_MMA);
-      // single pass: probabilities relative to the fixed reference, and the tile maximum
-      float t0 = -INFINITY, t1 = -INFINITY;
-      uint8_t* prow = sm.p[g] + row * 128;
-      tmem_ld32(s_addr, ra);
+      // keys 0..31 are on their way into ra
       tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
-        if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
-        uint8_t* atom = prow + (c >> 1) * kTileBytes;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          float pv[8];
-          if (need_bias) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float x = fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, sm.bias2[g][c * 32 + q4 * 8 + i]) - m_ref;
-              t0 = fmaxf(t0, x);
-              pv[i] = fast_exp2(x);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; i += 4) {
-              t0 = fmax3(t0, __uint_as_float(cur[q4 * 8 + i]), __uint_as_float(cur[q4 * 8 + i + 1]));
-              t1 = fmax3(t1, __uint_as_float(cur[q4 * 8 + i + 2]), __uint_as_float(cur[q4 * 8 + i + 3]));
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(cur[q4 * 8 + i]), c2, -m_ref));
-          }
-          l0 += (pv[0] + pv[1]) + (pv[2] + pv[3]);
-          l1 += (pv[4] + pv[5]) + (pv[6] + pv[7]);
-          const int chunk = (c & 1) * 4 + q4;
-          uint4 val;
-          val.x = pack_bf16x2(pv[0], pv[1]);
-          val.y = pack_bf16x2(pv[2], pv[3]);
-          val.z = pack_bf16x2(pv[4], pv[5]);
-          val.w = pack_bf16x2(pv[6], pv[7]);
-          *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = val;
-        }
-        if (c < 3) tmem_ld_wait();
-      }
-      // distance of the tile maximum from the reference, in the log2 domain
-      const float tmax = need_bias ? t0 : fmaf(fmaxf(t0, t1), c2, -m_ref);
-      overflow = overflow || (tmax > kFastHeadroom);
+      tmem_ld32(s_addr + 32, rb);
+      if (need_bias) fast_exp_chunk<true>(ra, pk, bias2, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false>(ra, pk, bias2, c2, m_ref, l0, l1);
+      tmem_st16(s_addr, pk);
+      tmem_ld_wait();
+      tmem_ld32(s_addr + 64, ra);
+      if (need_bias) fast_exp_chunk<true>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+      tmem_st16(s_addr + 16, pk);
+      tmem_ld_wait();
+      tmem_ld32(s_addr + 96, rb);
+      if (need_bias) fast_exp_chunk<true>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+      tmem_st16(s_addr + 32, pk);
+      tmem_ld_wait();
+      if (need_bias) fast_exp_chunk<true>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+      tmem_st16(s_addr + 48, pk);
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&sm.s_free[g]);
-      fence_proxy_async_smem();
       mbar_arrive(&sm.p_full[g]);
     }
+    const float lsum = l0 + l1;
+    const bool overflow = !(lsum <= kFastRowSumLimit);   // also true for NaN
     if (__any_sync(0xffffffffu, overflow) && lane == 0) atomicOr(p.fallback, 1);
-    sm.lpart[g][row] = l0 + l1;
+    sm.lpart[g][row] = lsum;
     named_bar_sync(4, 384);
     if (g == 0) {
       mbar_wait(&sm.o_done, 0, p.err, DEV_TIMEOUT_MMA);
@@ -657,8 +677,12 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------
-// Column sums.  Persistent CTAs walk over work items = (pair of 128-key tiles, head).  For every
-// 128-row query tile the MMA warp computes S^T = K Q^T for both key tiles against the same
+// Column sums.  An item = (pair of 128-key tiles, head); its units are the 128-row query
+// tiles.  All units of the launch form one sequence that is cut into equal contiguous ranges,
+// one per persistent CTA, so every SM gets the same amount of work; an item that straddles a
+// cut is finished by two CTAs, each adding its partial sums to the zeroed output with one
+// atomic add per key (two addends onto zero give the same bits in either order).
+// For every query tile the MMA warp computes S^T = K Q^T for both key tiles against the same
 // query tile in shared memory; warpgroup 0 owns the first key tile, warpgroup 1 the second, one
 // key (TMEM lane) per thread, so a thread's column sum never leaves its registers.
 // lse2 holds the row log-sum-exp in the log2 domain; rows past M_sub read as +inf so that
@@ -674,7 +698,7 @@ struct ColSmem {
   uint64_t s_full[2];
   uint64_t s_free[2];
   uint32_t tmem_base;
-  alignas(16) float lse2[4];  // flexible: 2 x n_q_tiles * 128 floats follow (item parity)
+  alignas(16) float lse2[4];  // flexible: 2 x n_q_tiles * 128 floats follow (item parity), negated
 };
 
 struct ColParams {
@@ -684,6 +708,7 @@ struct ColParams {
   int n_hot_tiles, n_tiles;
   int n_pairs, n_items;
   int n_q_tiles;
+  int split;       // 1: units are cut evenly over the grid (items may be shared by two CTAs)
   float scale_log2;
   float correction;
   const float* bias_ret;
@@ -694,6 +719,45 @@ struct ColParams {
   long long colsum_stride;
   int* err;
 };
+
+// The range of units of one CTA, walked item by item (same sequence in every role).
+struct ColWalk {
+  long long u, u_end;
+  int nq;
+  __device__ ColWalk(const ColParams& p) {
+    nq = p.n_q_tiles;
+    if (p.split) {
+      const long long total = static_cast<long long>(p.n_items) * nq;
+      u = total * blockIdx.x / gridDim.x;
+      u_end = total * (blockIdx.x + 1) / gridDim.x;
+    } else {
+      u = static_cast<long long>(blockIdx.x) * nq;
+      u_end = u + nq;
+    }
+  }
+  __device__ bool next(int& item, int& i0, int& i1) {
+    if (u >= u_end) return false;
+    item = static_cast<int>(u / nq);
+    i0 = static_cast<int>(u - static_cast<long long>(item) * nq);
+    const long long e = static_cast<long long>(item + 1) * nq;
+    i1 = static_cast<int>((e < u_end ? e : u_end) - static_cast<long long>(item) * nq);
+    u = static_cast<long long>(item) * nq + i1;
+    return true;
+  }
+};
+
+// 32 scores of one key against 32 query rows: sum of exp2(score * c2 - lse2[row]).
+__device__ __forceinline__ void col_exp_chunk(const uint32_t (&s)[32], const float4* nl4, float c2, float& a0,
+                                              float& a1, float& a2, float& a3) {
+#pragma unroll
+  for (int q4 = 0; q4 < 8; ++q4) {
+    const float4 nl = nl4[q4];
+    a0 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 0]), c2, nl.x));
+    a1 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 1]), c2, nl.y));
+    a2 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 2]), c2, nl.z));
+    a3 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 3]), c2, nl.w));
+  }
+}
 
 __global__ void __launch_bounds__(kColThreads, 1)
 attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
@@ -730,9 +794,9 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
-      int qi = 0;
-      int n = 0;
-      for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+      ColWalk walk(p);
+      int qi = 0, n = 0, item, i0, i1;
+      for (; walk.next(item, i0, i1); ++n) {
         const int pair = item / p.H, h = item % p.H;
         const int kb = n & 1;
         if (n >= 2) mbar_wait(&sm.k_empty[kb], ((n >> 1) - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
@@ -743,7 +807,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (j < p.n_hot_tiles) tma_load_3d(sm.k[kb][t], &tm_k_hot, &sm.k_full[kb], 0, j * kBN, h);
           else tma_load_3d(sm.k[kb][t], &tm_k_ret, &sm.k_full[kb], 0, (j - p.n_hot_tiles) * kBN, h);
         }
-        for (int i = 0; i < nq; ++i, ++qi) {
+        for (int i = i0; i < i1; ++i, ++qi) {
           const int s = qi % kColStages, round = qi / kColStages;
           if (round > 0) mbar_wait(&sm.q_empty[s], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
           mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
@@ -755,15 +819,16 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(kBN, kBM, 0);
-      int qi = 0, gi = 0, n = 0;
-      for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+      ColWalk walk(p);
+      int qi = 0, n = 0, item, i0, i1;
+      for (; walk.next(item, i0, i1); ++n) {
         const int kb = n & 1;
         mbar_wait(&sm.k_full[kb], (n >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
         const uint64_t ka_desc = smem_desc_sw128(smem_u32(sm.k[kb][0]));
         const uint64_t kb_desc = smem_desc_sw128(smem_u32(sm.k[kb][1]));
-        for (int i = 0; i < nq; ++i, ++qi, ++gi) {
+        for (int i = i0; i < i1; ++i, ++qi) {
           const int s = qi % kColStages;
-          const int g = gi & 1, it = gi >> 1;
+          const int g = qi & 1, it = qi >> 1;
           mbar_wait(&sm.q_full[s], (qi / kColStages) & 1, p.err, DEV_TIMEOUT_TMA);
           if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
           tc_fence_after();
@@ -789,15 +854,18 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c2 = p.scale_log2;
     uint32_t ra[32], rb[32];
-    int gi = 0, n = 0;
-    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++n) {
+    ColWalk walk(p);
+    int qi = 0, n = 0, item, i0, i1;
+    for (; walk.next(item, i0, i1); ++n) {
       const int pair = item / p.H, h = item % p.H;
-      float* lse_s = sm.lse2 + (n & 1) * nq * kBM;
-      for (int i = tid; i < nq * kBM; i += 256) {
-        float v = INFINITY;
-        if (i < p.M_sub)
-          v = p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(i) * p.row_stride];
-        lse_s[i] = v;
+      // negated row log-sum-exps of this item's query tiles (tile i0 at offset 0)
+      float* nl_s = sm.lse2 + (n & 1) * nq * kBM;
+      for (int r = tid; r < (i1 - i0) * kBM; r += 256) {
+        const int row = i0 * kBM + r;
+        float v = -INFINITY;
+        if (row < p.M_sub)
+          v = -p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(row) * p.row_stride];
+        nl_s[r] = v;
       }
       named_bar_sync(1, 256);
       const int j = 2 * pair + w;
@@ -805,38 +873,68 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool is_ret = j >= p.n_hot_tiles;
       const int n0 = (is_ret ? j - p.n_hot_tiles : j) * kBN;
       const int valid = exists ? min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0) : 0;
-      float b2 = -INFINITY;
-      if (key < valid) b2 = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e : 0.f;
-      float csum = 0.f, cs1 = 0.f, cs2 = 0.f, cs3 = 0.f;
-      for (int i = 0; i < nq; ++i, ++gi) {
-        const int g = gi & 1, it = gi >> 1;
+      // the key's bias multiplies its whole column: exp2(s c2 + b2 - lse2) = 2^b2 exp2(s c2 - lse2);
+      // taken out of the exponent while it is small, else folded into the score scale below
+      float b2 = 0.f;
+      if (key < valid && is_ret) b2 = p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e;
+      const bool b2_small = fabsf(b2) <= 32.f;
+      const float b2_in = b2_small ? 0.f : b2;   // rare: stays inside the exponent
+      const bool warp_fast = __all_sync(0xffffffffu, b2_small);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      // first tile of the item: nothing is in flight yet
+      {
+        const int g = qi & 1, it = qi >> 1;
         mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
         tc_fence_after();
+        tmem_ld32(tmem + lane_base + g * 256 + w * 128, ra);
+      }
+      for (int i = i0; i < i1; ++i, ++qi) {
+        const int g = qi & 1;
         const uint32_t s_addr = tmem + lane_base + g * 256 + w * 128;
-        const float4* l4 = reinterpret_cast<const float4*>(lse_s + i * kBM);
-        tmem_ld32(s_addr, ra);
-        tmem_ld_wait();
+        const float4* nl4 = reinterpret_cast<const float4*>(nl_s + (i - i0) * kBM);
+        if (__builtin_expect(!warp_fast, 0)) {
+          // general path: the bias stays in the exponent
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
-          if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
-#pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
-            const float4 l = l4[c * 8 + q4];
-            csum += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 0]), c2, b2 - l.x));
-            cs1 += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 1]), c2, b2 - l.y));
-            cs2 += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 2]), c2, b2 - l.z));
-            cs3 += fast_exp2(fmaf(__uint_as_float(cur[q4 * 4 + 3]), c2, b2 - l.w));
+            for (int q = 0; q < 32; ++q)
+              a0 += fast_exp2(fmaf(__uint_as_float(ra[q]), c2, b2_in + nl_s[(i - i0) * kBM + c * 32 + q]));
+            if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, ra);
           }
-          if (c < 3) tmem_ld_wait();
+          tmem_ld_wait();
+        } else {
+          tmem_ld_wait();
+          tmem_ld32(s_addr + 32, rb);
+          col_exp_chunk(ra, nl4, c2, a0, a1, a2, a3);
+          tmem_ld_wait();
+          tmem_ld32(s_addr + 64, ra);
+          col_exp_chunk(rb, nl4 + 8, c2, a0, a1, a2, a3);
+          tmem_ld_wait();
+          tmem_ld32(s_addr + 96, rb);
+          col_exp_chunk(ra, nl4 + 16, c2, a0, a1, a2, a3);
+          tmem_ld_wait();
         }
+        // the next query tile of this item was scored while this one was summed: fetch its
+        // first 32 rows before the last chunk of this tile is worked on
+        const bool more = i + 1 < i1;
+        if (more) {
+          const int g2 = (qi + 1) & 1, it2 = (qi + 1) >> 1;
+          mbar_wait(&sm.s_full[g2], it2 & 1, p.err, DEV_TIMEOUT_MMA);
+          tc_fence_after();
+          tmem_ld32(tmem + lane_base + g2 * 256 + w * 128, ra);
+        }
+        if (warp_fast) col_exp_chunk(rb, nl4 + 24, c2, a0, a1, a2, a3);
         tc_fence_before();
         mbar_arrive(&sm.s_free[g]);
       }
-      if (key < valid)
-        p.colsum[static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key] =
-            ((csum + cs1) + (cs2 + cs3)) * p.correction;
+      if (key < valid) {
+        float sum = ((a0 + a1) + (a2 + a3)) * p.correction;
+        if (b2_small) sum *= exp2f(b2);
+        float* dst = p.colsum + static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key;
+        if (i0 == 0 && i1 == nq) *dst = sum;
+        else atomicAdd(dst, sum);
+      }
     }
   }
   tc_fence_before();
@@ -1003,7 +1101,14 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
           cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
         return STAC_ERR_CUDA;
     }
-    const int grid_c = cp.n_items < n_sm ? cp.n_items : n_sm;
+    // enough items: cut the units evenly over one CTA per SM (an item is then shared by at most
+    // two CTAs, which add their partial sums onto zeros); else one item per CTA
+    cp.split = cp.n_items >= n_sm ? 1 : 0;
+    const int grid_c = cp.split ? n_sm : cp.n_items;
+    if (cp.split && cudaMemset2DAsync(a.colsum, static_cast<size_t>(a.colsum_head_stride) * sizeof(float), 0,
+                                      static_cast<size_t>(a.T_hot + a.T_ret) * sizeof(float), a.H, stream) !=
+                        cudaSuccess)
+      return STAC_ERR_CUDA;
     attn_colsum_kernel<<<grid_c, kColThreads, col_smem, stream>>>(tm_qs, tm_kh, tm_kr, cp);
     if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
   }

@@ -15,7 +15,7 @@ def _bf16(x):
     return torch.from_numpy(x).to(torch.bfloat16)
 
 
-def _run_two_segment(M, H, T_hot, T_ret, seed, T_buf=None, subsample=1.0, spread=1.0):
+def _run_two_segment(M, H, T_hot, T_ret, seed, T_buf=None, subsample=1.0, spread=1.0, bias_shift=0.0):
     from stac_b200 import ops
     rs = np.random.RandomState(seed)
     D = 64
@@ -27,6 +27,8 @@ def _run_two_segment(M, H, T_hot, T_ret, seed, T_buf=None, subsample=1.0, spread
     vr = _bf16(rs.randn(H, max(T_ret, 1), D).astype(np.float32))
     bias = np.log(rs.randint(1, 9, size=(H, max(T_ret, 1))).astype(np.float32))
     bias[rs.rand(H, max(T_ret, 1)) < 0.25] = -np.inf
+    if bias_shift:
+        bias[:, ::3] += bias_shift       # some keys far outside the usual log-count range
     dev = torch.device("cuda:0")
     status = ops.DeviceStatus(dev)
     out, lse, cs = ops.attn_colsum(q.to(dev), kh.to(dev), vh.to(dev), T_hot,
@@ -68,6 +70,21 @@ def test_two_segment(M, H, T_hot, T_ret):
 def test_peaked_scores():
     """Large logits exercise the running-max rescale of the online softmax."""
     got, ref = _run_two_segment(300, 2, 700, 130, seed=5, spread=3.0)
+    _assert_close(got, ref)
+
+
+def test_units_split_over_all_sms():
+    """More (key pair, head) items than SMs: the column-sum kernel cuts its units evenly over
+    the SMs and items that straddle a cut are summed by two CTAs."""
+    got, ref = _run_two_segment(300, 16, 2500, 140, seed=21)
+    _assert_close(got, ref)
+    again, _ = _run_two_segment(300, 16, 2500, 140, seed=21)
+    assert np.array_equal(got[2], again[2])          # shared items sum to the same bits every run
+
+
+@pytest.mark.parametrize("shift", [-40.0, 30.0])
+def test_large_bias(shift):
+    got, ref = _run_two_segment(200, 2, 300, 260, seed=13, bias_shift=shift)
     _assert_close(got, ref)
 
 
