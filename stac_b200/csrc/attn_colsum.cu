@@ -371,23 +371,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // probabilities leaves that range raises `fallback` and the exact kernel, launched right
 // behind this one, recomputes the call.
 //
-// Shared memory carries only the operands TMA brings in.  Each warpgroup owns one 128-column
-// TMEM buffer: the scores of its tile arrive there, the probabilities go back into the same
-// columns (bf16, two per column) and feed the P V MMA as its A operand straight from tensor
-// memory.  The tensor pipe has a floor of about 48 clocks per MMA instruction whatever its
-// width and stalls while its issuing thread does anything else, so scores use one N = 128
-// instruction per K step, the two MMA streams (scores, P V) have a warp each, and the
-// instructions of a group are issued back to back with operands prepared beforehand.
+// Shared memory carries only the operands TMA brings in.  Key tiles are 112 keys wide so that
+// FOUR score buffers fit beside the output accumulator in the 512 TMEM columns (4 x 112 + 64):
+// three are being exponentiated while the fourth goes through P V and the next Q K^T, so a
+// warpgroup finds its next tile scored when it gets there.  The probabilities go back into
+// the columns their scores came from (bf16, two per column) and feed the P V MMA as its A
+// operand straight from tensor memory.  The tensor pipe has a floor of about 48 clocks per
+// MMA instruction whatever its width and idles while its issuing thread does anything else,
+// so scores use one wide instruction per K step, the two MMA streams (scores, P V) have a
+// warp each, and the instructions of a group are issued back to back with operands prepared
+// beforehand.
 // ---------------------------------------------------------------------------------------
 constexpr int kFastThreads = 512;   // warpgroup 0 control (warp 0 TMA, warps 1-2 MMA issue), 1..3 softmax
 constexpr int kFastKStages = 4;
 constexpr int kFastVStages = 5;
+constexpr int kFT = 112;                        // keys per tile
+constexpr int kFastTileBytes = kFT * 128;       // 112 rows x 64 bf16
+constexpr int kFastRing = 4;
 constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 
 struct FastSmem {
   uint8_t q[kTileBytes];
-  uint8_t k[kFastKStages][kTileBytes];
-  uint8_t v[kFastVStages][kTileBytes];
+  uint8_t k[kFastKStages][kFastTileBytes];
+  uint8_t v[kFastVStages][kFastTileBytes];
   float bias2[3][kBN];
   float m_ref[kBM];
   float lpart[3][kBM];
@@ -396,20 +402,20 @@ struct FastSmem {
   uint64_t k_empty[kFastKStages];
   uint64_t v_full[kFastVStages];
   uint64_t v_empty[kFastVStages];
-  uint64_t s_full[3];    // scores of a tile are in TMEM
-  uint64_t p_full[3];    // its probabilities are in TMEM
-  uint64_t buf_free[3];  // the P V MMAs that read them are done
+  uint64_t s_full[kFastRing];    // scores of a tile are in TMEM
+  uint64_t p_full[kFastRing];    // its probabilities are in TMEM
+  uint64_t buf_free[kFastRing];  // the P V MMAs that read them are done
   uint64_t ref_ready;
   uint64_t o_done;
   uint32_t tmem_base;
 };
 
-// 32 scores -> 32 probabilities relative to the row reference, packed as 16 bf16 pairs.
-template <bool kBias>
+// kN scores -> kN probabilities relative to the row reference, packed as bf16 pairs.
+template <bool kBias, int kN>
 __device__ __forceinline__ void fast_exp_chunk(const uint32_t (&s)[32], uint32_t (&pk)[16], const float* bias2,
                                                float c2, float m_ref, float& l0, float& l1) {
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
+  for (int i = 0; i < kN; i += 4) {
     float e0, e1, e2, e3;
     if (kBias) {
       e0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), c2, bias2[i + 0]) - m_ref);
@@ -429,6 +435,19 @@ __device__ __forceinline__ void fast_exp_chunk(const uint32_t (&s)[32], uint32_t
   }
 }
 
+template <int kN>
+__device__ __forceinline__ float fast_max_chunk(const uint32_t (&s)[32], const float* bias2, bool need_bias, float c2,
+                                                float mx) {
+  if (need_bias) {
+#pragma unroll
+    for (int i = 0; i < kN; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(s[i]), c2, bias2[i]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < kN; i += 2) mx = fmax3(mx, __uint_as_float(s[i]) * c2, __uint_as_float(s[i + 1]) * c2);
+  }
+  return mx;
+}
+
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
                      const __grid_constant__ CUtensorMap tm_v_hot, const __grid_constant__ CUtensorMap tm_k_ret,
@@ -439,8 +458,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int lane = threadIdx.x & 31;
   const int m_tile = blockIdx.x;
   const int h = blockIdx.y;
-  const int n_hot = p.n_hot_tiles;
-  const int n_tiles = p.n_hot_tiles + p.n_ret_tiles;
+  const int n_hot = (p.T_hot + kFT - 1) / kFT;
+  const int n_tiles = n_hot + (p.T_ret + kFT - 1) / kFT;
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar_q, 1);
@@ -452,7 +471,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
-    for (int b = 0; b < 3; ++b) {
+    for (int b = 0; b < kFastRing; ++b) {
       mbar_init(&sm.s_full[b], 1);
       mbar_init(&sm.p_full[b], 128);
       mbar_init(&sm.buf_free[b], 1);
@@ -469,7 +488,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t o_tmem = tmem + 3 * kBN;   // columns 384..447
+  const uint32_t o_tmem = tmem + kFastRing * kFT;   // columns 448..511
 
   if (warp < 4) {
     setmaxnreg_dec<40>();
@@ -483,12 +502,12 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       int ks = 0, kr = 0, vs = 0, vr = 0;   // stage and round of the K and V rings
       for (int j = 0; j < n_tiles; ++j) {
         const bool hot = j < n_hot;
-        const int n0 = (hot ? j : j - n_hot) * kBN;
+        const int n0 = (hot ? j : j - n_hot) * kFT;
         if (kr > 0) mbar_wait(&sm.k_empty[ks], (kr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        mbar_arrive_expect_tx(&sm.k_full[ks], kTileBytes);
+        mbar_arrive_expect_tx(&sm.k_full[ks], kFastTileBytes);
         tma_load_3d(sm.k[ks], hot ? &tm_k_hot : &tm_k_ret, &sm.k_full[ks], 0, n0, h);
         if (vr > 0) mbar_wait(&sm.v_empty[vs], (vr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        mbar_arrive_expect_tx(&sm.v_full[vs], kTileBytes);
+        mbar_arrive_expect_tx(&sm.v_full[vs], kFastTileBytes);
         tma_load_3d(sm.v[vs], hot ? &tm_v_hot : &tm_v_ret, &sm.v_full[vs], 0, n0, h);
         if (++ks == kFastKStages) { ks = 0; ++kr; }
         if (++vs == kFastVStages) { vs = 0; ++vr; }
@@ -496,56 +515,56 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     } else if (warp == 1) {
       // ---------------------------------------------------------------- MMA issuer: S = Q K^T
       // (all lanes run the loop, one elected lane issues)
-      constexpr uint32_t idesc_s = umma_idesc_bf16(kBM, kBN, 0);
+      constexpr uint32_t idesc_s = umma_idesc_bf16(kBM, kFT, 0);
       mbar_wait(&sm.bar_q, 0, p.err, DEV_TIMEOUT_TMA);
       const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q));
       const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0]));
-      int g = 0, it = 0, ks = 0, kr = 0;
+      int b = 0, round = 0, ks = 0, kr = 0;
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
-        const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(ks * (kTileBytes >> 4));
-        const uint32_t d = tmem + g * kBN;
+        const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(ks * (kFastTileBytes >> 4));
+        const uint32_t d = tmem + b * kFT;
         mbar_wait(&sm.k_full[ks], kr & 1, p.err, DEV_TIMEOUT_TMA);
-        if (it > 0) mbar_wait(&sm.buf_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        if (round > 0) mbar_wait(&sm.buf_free[b], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         tc_fence_after();
         if (elect_one()) {
           umma_ss(d, q_desc, k_desc, idesc_s, 0u);
           umma_ss(d, q_desc + 2, k_desc + 2, idesc_s, 1u);
           umma_ss(d, q_desc + 4, k_desc + 4, idesc_s, 1u);
           umma_ss(d, q_desc + 6, k_desc + 6, idesc_s, 1u);
-          umma_commit(&sm.s_full[g]);
+          umma_commit(&sm.s_full[b]);
           umma_commit(&sm.k_empty[ks]);
         }
         __syncwarp();
         if (++ks == kFastKStages) { ks = 0; ++kr; }
-        if (++g == 3) { g = 0; ++it; }
+        if (++b == kFastRing) { b = 0; ++round; }
       }
     } else if (warp == 2) {
       // ---------------------------------------------------------------- MMA issuer: O += P V
       constexpr uint32_t idesc_o = umma_idesc_bf16(kBM, kD, 1);
       const uint64_t v_desc0 = smem_desc_sw128(smem_u32(sm.v[0]));
-      int g = 0, it = 0, vs = 0, vr = 0;
+      int b = 0, round = 0, vs = 0, vr = 0;
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         // A: 16 keys = 8 columns of packed probabilities; B: V advances 16 rows = 2048 bytes
-        const uint32_t pa = tmem + g * kBN;
-        const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kTileBytes >> 4));
+        const uint32_t pa = tmem + b * kFT;
+        const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kFastTileBytes >> 4));
         const uint32_t acc0 = j > 0 ? 1u : 0u;
         mbar_wait(&sm.v_full[vs], vr & 1, p.err, DEV_TIMEOUT_TMA);
-        mbar_wait(&sm.p_full[g], it & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_wait(&sm.p_full[b], round & 1, p.err, DEV_TIMEOUT_CONSUMER);
         tc_fence_after();
         if (elect_one()) {
           umma_ts(o_tmem, pa, vb, idesc_o, acc0);
 #pragma unroll
-          for (int kk = 1; kk < kBN / 16; ++kk)
+          for (int kk = 1; kk < kFT / 16; ++kk)
             umma_ts(o_tmem, pa + kk * 8, vb + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, 1u);
-          umma_commit(&sm.buf_free[g]);
+          umma_commit(&sm.buf_free[b]);
           umma_commit(&sm.v_empty[vs]);
           if (j == n_tiles - 1) umma_commit(&sm.o_done);
         }
         __syncwarp();
         if (++vs == kFastVStages) { vs = 0; ++vr; }
-        if (++g == 3) { g = 0; ++it; }
+        if (++b == kFastRing) { b = 0; ++round; }
       }
     }
   } else {
@@ -555,77 +574,91 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t s_addr = tmem + lane_base + g * kBN;
     const float c2 = p.scale_log2;
     const float* bias2 = sm.bias2[g];
     float m_ref = 0.f;
     float l0 = 0.f, l1 = 0.f;
     uint32_t ra[32], rb[32], pk[16];
-    int it = 0;
-    for (int j = g; j < n_tiles; j += 3, ++it) {
+    int b = g, round = 0;   // ring buffer and round of tile j (j = g, g + 3, ...)
+    bool fetching = false;  // the first 32 scores of tile j are already on their way into ra
+    for (int j = g; j < n_tiles; j += 3) {
       const bool is_ret = j >= n_hot;
-      const int n0 = (is_ret ? j - n_hot : j) * kBN;
-      const int valid = min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0);
-      const bool need_bias = is_ret || valid < kBN;
+      const int n0 = (is_ret ? j - n_hot : j) * kFT;
+      const int valid = min(kFT, (is_ret ? p.T_ret : p.T_hot) - n0);
+      const bool need_bias = is_ret || valid < kFT;
       if (need_bias) {
         named_bar_sync(1 + g, 128);
-        float b = -INFINITY;
-        if (row < valid) b = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + row] * kLog2e : 0.f;
-        sm.bias2[g][row] = b;
+        if (row < kFT) {
+          float bv = -INFINITY;
+          if (row < valid) bv = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + row] * kLog2e : 0.f;
+          sm.bias2[g][row] = bv;
+        }
         named_bar_sync(1 + g, 128);
       }
-      mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
-      tc_fence_after();
-      tmem_ld32(s_addr, ra);
-      if (j == 0) {
-        // exact row maximum of the first tile = the row's reference for the whole call
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
+      const uint32_t s_addr = tmem + lane_base + b * kFT;
+      if (!fetching) {
+        mbar_wait(&sm.s_full[b], round & 1, p.err, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+        tmem_ld32(s_addr, ra);
+      }
+      if (j < 3) {
+        if (j == 0) {
+          // exact row maximum of the first tile = the row's reference for the whole call
+          float mx = -INFINITY;
           tmem_ld_wait();
-          tmem_ld32(s_addr + ((c + 1) & 3) * 32, rb);   // last turn re-fetches the first 32 keys
-          if (need_bias) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(ra[i]), c2, bias2[c * 32 + i]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              mx = fmax3(mx, __uint_as_float(ra[i]) * c2, __uint_as_float(ra[i + 1]) * c2);
-          }
+          mx = fast_max_chunk<32>(ra, bias2, need_bias, c2, mx);
+          tmem_ld32(s_addr + 32, ra);
           tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ra[i] = rb[i];
+          mx = fast_max_chunk<32>(ra, bias2 + 32, need_bias, c2, mx);
+          tmem_ld32(s_addr + 64, ra);
+          tmem_ld_wait();
+          mx = fast_max_chunk<32>(ra, bias2 + 64, need_bias, c2, mx);
+          tmem_ld16(s_addr + 96, ra);
+          tmem_ld_wait();
+          mx = fast_max_chunk<16>(ra, bias2 + 96, need_bias, c2, mx);
+          m_ref = (mx == -INFINITY) ? 0.f : mx;
+          sm.m_ref[row] = m_ref;
+          mbar_arrive(&sm.ref_ready);
+          tmem_ld32(s_addr, ra);
+        } else {
+          mbar_wait(&sm.ref_ready, 0, p.err, DEV_TIMEOUT_CONSUMER);
+          m_ref = sm.m_ref[row];
         }
-        m_ref = (mx == -INFINITY) ? 0.f : mx;
-        sm.m_ref[row] = m_ref;
-        mbar_arrive(&sm.ref_ready);
-      } else if (it == 0) {
-        mbar_wait(&sm.ref_ready, 0, p.err, DEV_TIMEOUT_CONSUMER);
-        m_ref = sm.m_ref[row];
       }
       // keys 0..31 are on their way into ra
       tmem_ld_wait();
       tmem_ld32(s_addr + 32, rb);
-      if (need_bias) fast_exp_chunk<true>(ra, pk, bias2, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false>(ra, pk, bias2, c2, m_ref, l0, l1);
+      if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
       tmem_st16(s_addr, pk);
       tmem_ld_wait();
       tmem_ld32(s_addr + 64, ra);
-      if (need_bias) fast_exp_chunk<true>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+      if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
       tmem_st16(s_addr + 16, pk);
       tmem_ld_wait();
-      tmem_ld32(s_addr + 96, rb);
-      if (need_bias) fast_exp_chunk<true>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+      tmem_ld16(s_addr + 96, rb);
+      if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
       tmem_st16(s_addr + 32, pk);
       tmem_ld_wait();
-      if (need_bias) fast_exp_chunk<true>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
-      tmem_st16(s_addr + 48, pk);
+      // this warpgroup's next tile is normally scored by now: start fetching it (never wait for
+      // it here: its buffer is released by another warpgroup's P V, which may be behind this one)
+      int b2 = b + 3, round2 = round;
+      if (b2 >= kFastRing) { b2 -= kFastRing; ++round2; }
+      fetching = false;
+      if (j + 3 < n_tiles && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+        tc_fence_after();
+        tmem_ld32(tmem + lane_base + b2 * kFT, ra);
+        fetching = true;
+      }
+      if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+      else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+      tmem_st8(s_addr + 48, pk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&sm.p_full[g]);
+      mbar_arrive(&sm.p_full[b]);
+      b = b2; round = round2;
     }
     const float lsum = l0 + l1;
     const bool overflow = !(lsum <= kFastRowSumLimit);   // also true for NaN
@@ -677,8 +710,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------
-// Column sums.  An item = (pair of 128-key tiles, head); its units are the 128-row query
-// tiles.  All units of the launch form one sequence that is cut into equal contiguous ranges,
+// Column sums.  An item = (head, pair of 128-key tiles), head-major; its units are the 128-row
+// query tiles.  All units of the launch form one sequence that is cut into equal contiguous ranges,
 // one per persistent CTA, so every SM gets the same amount of work; an item that straddles a
 // cut is finished by two CTAs, each adding its partial sums to the zeroed output with one
 // atomic add per key (two addends onto zero give the same bits in either order).
@@ -698,7 +731,7 @@ struct ColSmem {
   uint64_t s_full[2];
   uint64_t s_free[2];
   uint32_t tmem_base;
-  alignas(16) float lse2[4];  // flexible: 2 x n_q_tiles * 128 floats follow (item parity), negated
+  alignas(16) float lse2[4];  // flexible: n_q_tiles * 128 floats follow (negated, one head)
 };
 
 struct ColParams {
@@ -797,7 +830,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       ColWalk walk(p);
       int qi = 0, n = 0, item, i0, i1;
       for (; walk.next(item, i0, i1); ++n) {
-        const int pair = item / p.H, h = item % p.H;
+        const int h = item / p.n_pairs, pair = item - h * p.n_pairs;   // head-major item order
         const int kb = n & 1;
         if (n >= 2) mbar_wait(&sm.k_empty[kb], ((n >> 1) - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         mbar_arrive_expect_tx(&sm.k_full[kb], 2 * kTileBytes);
@@ -817,32 +850,40 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(kBN, kBM, 0);
-      ColWalk walk(p);
-      int qi = 0, n = 0, item, i0, i1;
-      for (; walk.next(item, i0, i1); ++n) {
-        const int kb = n & 1;
-        mbar_wait(&sm.k_full[kb], (n >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
-        const uint64_t ka_desc = smem_desc_sw128(smem_u32(sm.k[kb][0]));
-        const uint64_t kb_desc = smem_desc_sw128(smem_u32(sm.k[kb][1]));
-        for (int i = i0; i < i1; ++i, ++qi) {
-          const int s = qi % kColStages;
-          const int g = qi & 1, it = qi >> 1;
-          mbar_wait(&sm.q_full[s], (qi / kColStages) & 1, p.err, DEV_TIMEOUT_TMA);
-          if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-          tc_fence_after();
-          const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q[s]));
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            umma_ss(tmem + g * 256, ka_desc + 2 * kk, q_desc + 2 * kk, idesc, kk > 0);
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            umma_ss(tmem + g * 256 + 128, kb_desc + 2 * kk, q_desc + 2 * kk, idesc, kk > 0);
+    // (all lanes run the loop so that descriptors are warp-uniform; one elected lane issues)
+    constexpr uint32_t idesc = umma_idesc_bf16(kBN, kBM, 0);
+    ColWalk walk(p);
+    const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0][0]));
+    const uint64_t q_desc0 = smem_desc_sw128(smem_u32(sm.q[0]));
+    int qi = 0, n = 0, item, i0, i1;
+    int s = 0, s_round = 0;   // stage and round of the query ring
+    for (; walk.next(item, i0, i1); ++n) {
+      const int kb = n & 1;
+      mbar_wait(&sm.k_full[kb], (n >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
+      const uint64_t ka_desc = k_desc0 + static_cast<uint64_t>(kb * 2 * (kTileBytes >> 4));
+      const uint64_t kb_desc = ka_desc + static_cast<uint64_t>(kTileBytes >> 4);
+      for (int i = i0; i < i1; ++i, ++qi) {
+        const int g = qi & 1, it = qi >> 1;
+        const uint64_t q_desc = q_desc0 + static_cast<uint64_t>(s * (kTileBytes >> 4));
+        const uint32_t d = tmem + g * 256;
+        mbar_wait(&sm.q_full[s], s_round & 1, p.err, DEV_TIMEOUT_TMA);
+        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        tc_fence_after();
+        if (elect_one()) {
+          umma_ss(d, ka_desc, q_desc, idesc, 0u);
+          umma_ss(d, ka_desc + 2, q_desc + 2, idesc, 1u);
+          umma_ss(d, ka_desc + 4, q_desc + 4, idesc, 1u);
+          umma_ss(d, ka_desc + 6, q_desc + 6, idesc, 1u);
+          umma_ss(d + 128, kb_desc, q_desc, idesc, 0u);
+          umma_ss(d + 128, kb_desc + 2, q_desc + 2, idesc, 1u);
+          umma_ss(d + 128, kb_desc + 4, q_desc + 4, idesc, 1u);
+          umma_ss(d + 128, kb_desc + 6, q_desc + 6, idesc, 1u);
           umma_commit(&sm.s_full[g]);
           umma_commit(&sm.q_empty[s]);
+          if (i == i1 - 1) umma_commit(&sm.k_empty[kb]);
         }
-        umma_commit(&sm.k_empty[kb]);
+        __syncwarp();
+        if (++s == kColStages) { s = 0; ++s_round; }
       }
     }
   } else {
@@ -856,18 +897,23 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint32_t ra[32], rb[32];
     ColWalk walk(p);
     int qi = 0, n = 0, item, i0, i1;
+    int cur_h = -1;
     for (; walk.next(item, i0, i1); ++n) {
-      const int pair = item / p.H, h = item % p.H;
-      // negated row log-sum-exps of this item's query tiles (tile i0 at offset 0)
-      float* nl_s = sm.lse2 + (n & 1) * nq * kBM;
-      for (int r = tid; r < (i1 - i0) * kBM; r += 256) {
-        const int row = i0 * kBM + r;
-        float v = -INFINITY;
-        if (row < p.M_sub)
-          v = -p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(row) * p.row_stride];
-        nl_s[r] = v;
+      const int h = item / p.n_pairs, pair = item - h * p.n_pairs;   // head-major item order
+      // negated row log-sum-exps of the head's query rows, reloaded only when the head changes
+      // (a CTA's items are consecutive, so that is once or twice per launch)
+      float* nl_s = sm.lse2;
+      if (h != cur_h) {
+        cur_h = h;
+        named_bar_sync(1, 256);   // everyone is done with the previous head's values
+        for (int r = tid; r < nq * kBM; r += 256) {
+          float v = -INFINITY;
+          if (r < p.M_sub)
+            v = -p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(r) * p.row_stride];
+          nl_s[r] = v;
+        }
+        named_bar_sync(1, 256);
       }
-      named_bar_sync(1, 256);
       const int j = 2 * pair + w;
       const bool exists = j < p.n_tiles;
       const bool is_ret = j >= p.n_hot_tiles;
@@ -891,7 +937,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int i = i0; i < i1; ++i, ++qi) {
         const int g = qi & 1;
         const uint32_t s_addr = tmem + lane_base + g * 256 + w * 128;
-        const float4* nl4 = reinterpret_cast<const float4*>(nl_s + (i - i0) * kBM);
+        const float4* nl4 = reinterpret_cast<const float4*>(nl_s + i * kBM);
         if (__builtin_expect(!warp_fast, 0)) {
           // general path: the bias stays in the exponent
 #pragma unroll 1
@@ -899,7 +945,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 32; ++q)
-              a0 += fast_exp2(fmaf(__uint_as_float(ra[q]), c2, b2_in + nl_s[(i - i0) * kBM + c * 32 + q]));
+              a0 += fast_exp2(fmaf(__uint_as_float(ra[q]), c2, b2_in + nl_s[i * kBM + c * 32 + q]));
             if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, ra);
           }
           tmem_ld_wait();
@@ -1019,7 +1065,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   float corr;
   attn_subsample_plan(a.M, a.subsample_ratio, &m_sub, &stride, &corr);
   const int nq = (m_sub + kBM - 1) / kBM;
-  const int col_smem = static_cast<int>(sizeof(ColSmem)) + 2 * nq * kBM * 4 + 1024;
+  const int col_smem = static_cast<int>(sizeof(ColSmem)) + nq * kBM * 4 + 1024;
   if (col_smem > 227 * 1024) return STAC_ERR_BAD_ARG;
   const int fast_smem = static_cast<int>(sizeof(FastSmem)) + 1024;
   if (!attr_done) {
@@ -1036,6 +1082,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
 
   const uint64_t eb = 2;  // bytes per element
   CUtensorMap tm_q, tm_qs, tm_kh, tm_vh, tm_kr, tm_vr;
+  CUtensorMap tf_kh, tf_vh, tf_kr, tf_vr;   // the same tensors in 112-key boxes (fast kernel)
   int rc;
   // q[m, h, :]: dims {64, H, M}
   rc = make_map(&tm_q, a.q, a.H, a.M, kD * eb, a.q_row_stride * eb, 1, kBM);
@@ -1061,6 +1108,14 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   if (rc) return rc;
   rc = make_map(&tm_vr, vr, tr, a.H, rr * eb, sr * eb, kBN, 1);
   if (rc) return rc;
+  rc = make_map(&tf_kh, kh, th, a.H, rh * eb, sh * eb, kFT, 1);
+  if (rc) return rc;
+  rc = make_map(&tf_vh, vh, th, a.H, rh * eb, sh * eb, kFT, 1);
+  if (rc) return rc;
+  rc = make_map(&tf_kr, kr, tr, a.H, rr * eb, sr * eb, kFT, 1);
+  if (rc) return rc;
+  rc = make_map(&tf_vr, vr, tr, a.H, rr * eb, sr * eb, kFT, 1);
+  if (rc) return rc;
 
   const float scale_log2 = a.scale * kLog2e;
   FwdParams fp;
@@ -1077,7 +1132,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   // fast kernel (fixed per-row reference) first; the exact kernel behind it returns at once
   // unless the fast one raised the flag
   if (cudaMemsetAsync(fp.fallback, 0, sizeof(int), stream) != cudaSuccess) return STAC_ERR_CUDA;
-  attn_fwd_fast_kernel<<<grid_f, kFastThreads, fast_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
+  attn_fwd_fast_kernel<<<grid_f, kFastThreads, fast_smem, stream>>>(tm_q, tf_kh, tf_vh, tf_kr, tf_vr, fp);
   attn_fwd_kernel<<<grid_f, kFwdThreads, fwd_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
   if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
 
