@@ -382,8 +382,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // warp each, and the instructions of a group are issued back to back with operands prepared
 // beforehand.
 // ---------------------------------------------------------------------------------------
-constexpr int kFastThreads = 512;   // warpgroup 0 control (warp 0 TMA, warps 1-2 MMA issue), 1..3 softmax
-constexpr int kFastKStages = 4;
+constexpr int kFastThreads = 512;   // warpgroup 0 control (warps 0, 3 TMA, warps 1-2 MMA issue), 1..3 softmax
+constexpr int kFastKStages = 5;
 constexpr int kFastVStages = 5;
 constexpr int kFT = 112;                        // keys per tile
 constexpr int kFastTileBytes = kFT * 128;       // 112 rows x 64 bf16
@@ -496,20 +496,29 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // ---------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k_hot);
-      tma_prefetch_desc(&tm_v_hot);
       mbar_arrive_expect_tx(&sm.bar_q, kTileBytes);
       tma_load_3d(sm.q, &tm_q, &sm.bar_q, 0, h, m_tile * kBM);
-      int ks = 0, kr = 0, vs = 0, vr = 0;   // stage and round of the K and V rings
+      int ks = 0, kr = 0;   // stage and round of the K ring
       for (int j = 0; j < n_tiles; ++j) {
         const bool hot = j < n_hot;
         const int n0 = (hot ? j : j - n_hot) * kFT;
         if (kr > 0) mbar_wait(&sm.k_empty[ks], (kr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         mbar_arrive_expect_tx(&sm.k_full[ks], kFastTileBytes);
         tma_load_3d(sm.k[ks], hot ? &tm_k_hot : &tm_k_ret, &sm.k_full[ks], 0, n0, h);
+        if (++ks == kFastKStages) { ks = 0; ++kr; }
+      }
+    } else if (warp == 3 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer for V
+      // (its own thread: V tiles are released several tiles later than K tiles, and one
+      // thread serving both rings in order would hold K back whenever the V ring is full)
+      tma_prefetch_desc(&tm_v_hot);
+      int vs = 0, vr = 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const bool hot = j < n_hot;
+        const int n0 = (hot ? j : j - n_hot) * kFT;
         if (vr > 0) mbar_wait(&sm.v_empty[vs], (vr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         mbar_arrive_expect_tx(&sm.v_full[vs], kFastTileBytes);
         tma_load_3d(sm.v[vs], hot ? &tm_v_hot : &tm_v_ret, &sm.v_full[vs], 0, n0, h);
-        if (++ks == kFastKStages) { ks = 0; ++kr; }
         if (++vs == kFastVStages) { vs = 0; ++vr; }
       }
     } else if (warp == 1) {
@@ -655,6 +664,11 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
       else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
       tmem_st8(s_addr + 48, pk);
+      if (!fetching && j + 3 < n_tiles && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+        tc_fence_after();                  // second chance, a chunk later
+        tmem_ld32(tmem + lane_base + b2 * kFT, ra);
+        fetching = true;
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&sm.p_full[b]);
