@@ -30,7 +30,7 @@ constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 bf16
 constexpr int kFwdStages = 4;
 constexpr int kFwdThreads = 384;       // warpgroup 0: warp 0 TMA, warp 1 MMA (2, 3 idle); warpgroups 1, 2: softmax
 constexpr int kColStages = 4;
-constexpr int kColThreads = 320;
+constexpr int kColThreads = 512;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA issue), 1..3 exponent
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -491,7 +491,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t o_tmem = tmem + kFastRing * kFT;   // columns 448..511
 
   if (warp < 4) {
-    setmaxnreg_dec<40>();
+    setmaxnreg_dec<56>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&tm_q);
@@ -724,19 +724,25 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------
-// Column sums.  An item = (head, pair of 128-key tiles), head-major; its units are the 128-row
-// query tiles.  All units of the launch form one sequence that is cut into equal contiguous ranges,
-// one per persistent CTA, so every SM gets the same amount of work; an item that straddles a
-// cut is finished by two CTAs, each adding its partial sums to the zeroed output with one
-// atomic add per key (two addends onto zero give the same bits in either order).
-// For every query tile the MMA warp computes S^T = K Q^T for both key tiles against the same
-// query tile in shared memory; warpgroup 0 owns the first key tile, warpgroup 1 the second, one
-// key (TMEM lane) per thread, so a thread's column sum never leaves its registers.
+// Column sums.  An item = (head, group of three 128-key tiles), head-major; its units are the
+// 128-row query tiles.  All units of the launch form one sequence that is cut into equal
+// contiguous ranges, one per persistent CTA, so every SM gets the same amount of work; an item
+// that straddles a cut is finished by two CTAs, each adding its partial sums to the zeroed
+// output with one atomic add per key (two addends onto zero give the same bits in either
+// order).  A query tile is scored in two halves of 64 rows: for each half the MMA warp
+// computes S^T = K Q^T for the three key tiles against the same query rows in shared memory
+// (N = 64, two 64-column TMEM buffers per key tile); warpgroup w owns key tile w, one key
+// (TMEM lane) per thread, so a thread's column sum never leaves its registers.  Three
+// exponent warps per scheduler keep the exp2 unit busier than two did.
 // lse2 holds the row log-sum-exp in the log2 domain; rows past M_sub read as +inf so that
 // padded query columns contribute exp2(-inf) = 0.
 // ---------------------------------------------------------------------------------------
+constexpr int kColGroup = 3;           // key tiles per item = exponent warpgroups
+constexpr int kColExpThreads = kColGroup * 128;
+constexpr int kColHalf = 64;           // query rows per score buffer
+
 struct ColSmem {
-  uint8_t k[2][2][kTileBytes];        // [item parity][key tile of the pair]
+  uint8_t k[2][kColGroup][kTileBytes];  // [item parity][key tile of the group]
   uint8_t q[kColStages][kTileBytes];
   uint64_t k_full[2];
   uint64_t k_empty[2];
@@ -753,7 +759,7 @@ struct ColParams {
   int row_stride;  // query row sub-sampling stride
   int T_hot, T_ret;
   int n_hot_tiles, n_tiles;
-  int n_pairs, n_items;
+  int n_groups, n_items;
   int n_q_tiles;
   int split;       // 1: units are cut evenly over the grid (items may be shared by two CTAs)
   float scale_log2;
@@ -806,6 +812,54 @@ __device__ __forceinline__ void col_exp_chunk(const uint32_t (&s)[32], const flo
   }
 }
 
+// All half tiles of one item for one key (thread): returns the sum over the item's query rows.
+// kFast: the key's bias was taken out of the exponent (every lane of the warp agrees).
+template <bool kFast>
+__device__ __forceinline__ float col_item_sum(ColSmem& sm, const ColParams& p, uint32_t t_base, const float* nl_item,
+                                              int n_half, int& ui, float c2, float b2_in) {
+  uint32_t ra[32], rb[32];
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  // first half tile of the item: nothing is in flight yet
+  {
+    const int g = ui & 1, it = ui >> 1;
+    mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
+    tc_fence_after();
+    tmem_ld32(t_base + g * kColHalf, ra);
+  }
+  for (int hu = 0; hu < n_half; ++hu, ++ui) {
+    const int g = ui & 1;
+    const uint32_t s_addr = t_base + g * kColHalf;
+    const float* nl = nl_item + hu * kColHalf;
+    const float4* nl4 = reinterpret_cast<const float4*>(nl);
+    tmem_ld_wait();                 // rows 0..31 of the half are in ra
+    tmem_ld32(s_addr + 32, rb);
+    if (kFast) {
+      col_exp_chunk(ra, nl4, c2, a0, a1, a2, a3);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 32; ++q) a0 += fast_exp2(fmaf(__uint_as_float(ra[q]), c2, b2_in + nl[q]));
+    }
+    tmem_ld_wait();                 // rows 32..63 are in rb
+    // the next half tile was scored while this one was summed: fetch its first 32 rows
+    // (its buffer does not depend on this warpgroup finishing the current one)
+    if (hu + 1 < n_half) {
+      const int g2 = (ui + 1) & 1, it2 = (ui + 1) >> 1;
+      mbar_wait(&sm.s_full[g2], it2 & 1, p.err, DEV_TIMEOUT_MMA);
+      tc_fence_after();
+      tmem_ld32(t_base + g2 * kColHalf, ra);
+    }
+    if (kFast) {
+      col_exp_chunk(rb, nl4 + 8, c2, a0, a1, a2, a3);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 32; ++q) a0 += fast_exp2(fmaf(__uint_as_float(rb[q]), c2, b2_in + nl[32 + q]));
+    }
+    tc_fence_before();
+    mbar_arrive(&sm.s_free[g]);
+  }
+  return (a0 + a1) + (a2 + a3);
+}
+
 __global__ void __launch_bounds__(kColThreads, 1)
 attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
                    const __grid_constant__ CUtensorMap tm_k_ret, const ColParams p) {
@@ -820,7 +874,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(&sm.k_full[i], 1);
       mbar_init(&sm.k_empty[i], 1);
       mbar_init(&sm.s_full[i], 1);
-      mbar_init(&sm.s_free[i], 256);
+      mbar_init(&sm.s_free[i], kColExpThreads);
     }
     for (int s = 0; s < kColStages; ++s) {
       mbar_init(&sm.q_full[s], 1);
@@ -837,159 +891,122 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+  if (warp < 4) {
+    setmaxnreg_dec<56>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
       tma_prefetch_desc(&tm_q);
       ColWalk walk(p);
-      int qi = 0, n = 0, item, i0, i1;
+      int n = 0, item, i0, i1;
+      int s = 0, s_round = 0;   // stage and round of the query ring
       for (; walk.next(item, i0, i1); ++n) {
-        const int h = item / p.n_pairs, pair = item - h * p.n_pairs;   // head-major item order
+        const int h = item / p.n_groups, grp = item - h * p.n_groups;   // head-major item order
         const int kb = n & 1;
         if (n >= 2) mbar_wait(&sm.k_empty[kb], ((n >> 1) - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        mbar_arrive_expect_tx(&sm.k_full[kb], 2 * kTileBytes);
+        mbar_arrive_expect_tx(&sm.k_full[kb], kColGroup * kTileBytes);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int j = min(2 * pair + t, p.n_tiles - 1);
+        for (int t = 0; t < kColGroup; ++t) {
+          const int j = min(kColGroup * grp + t, p.n_tiles - 1);
           if (j < p.n_hot_tiles) tma_load_3d(sm.k[kb][t], &tm_k_hot, &sm.k_full[kb], 0, j * kBN, h);
           else tma_load_3d(sm.k[kb][t], &tm_k_ret, &sm.k_full[kb], 0, (j - p.n_hot_tiles) * kBN, h);
         }
-        for (int i = i0; i < i1; ++i, ++qi) {
-          const int s = qi % kColStages, round = qi / kColStages;
-          if (round > 0) mbar_wait(&sm.q_empty[s], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        for (int i = i0; i < i1; ++i) {
+          if (s_round > 0) mbar_wait(&sm.q_empty[s], (s_round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
           mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
           tma_load_3d(sm.q[s], &tm_q, &sm.q_full[s], 0, h, i * kBM);
+          if (++s == kColStages) { s = 0; ++s_round; }
         }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    // (all lanes run the loop so that descriptors are warp-uniform; one elected lane issues)
-    constexpr uint32_t idesc = umma_idesc_bf16(kBN, kBM, 0);
-    ColWalk walk(p);
-    const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0][0]));
-    const uint64_t q_desc0 = smem_desc_sw128(smem_u32(sm.q[0]));
-    int qi = 0, n = 0, item, i0, i1;
-    int s = 0, s_round = 0;   // stage and round of the query ring
-    for (; walk.next(item, i0, i1); ++n) {
-      const int kb = n & 1;
-      mbar_wait(&sm.k_full[kb], (n >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
-      const uint64_t ka_desc = k_desc0 + static_cast<uint64_t>(kb * 2 * (kTileBytes >> 4));
-      const uint64_t kb_desc = ka_desc + static_cast<uint64_t>(kTileBytes >> 4);
-      for (int i = i0; i < i1; ++i, ++qi) {
-        const int g = qi & 1, it = qi >> 1;
-        const uint64_t q_desc = q_desc0 + static_cast<uint64_t>(s * (kTileBytes >> 4));
-        const uint32_t d = tmem + g * 256;
-        mbar_wait(&sm.q_full[s], s_round & 1, p.err, DEV_TIMEOUT_TMA);
-        if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        tc_fence_after();
-        if (elect_one()) {
-          umma_ss(d, ka_desc, q_desc, idesc, 0u);
-          umma_ss(d, ka_desc + 2, q_desc + 2, idesc, 1u);
-          umma_ss(d, ka_desc + 4, q_desc + 4, idesc, 1u);
-          umma_ss(d, ka_desc + 6, q_desc + 6, idesc, 1u);
-          umma_ss(d + 128, kb_desc, q_desc, idesc, 0u);
-          umma_ss(d + 128, kb_desc + 2, q_desc + 2, idesc, 1u);
-          umma_ss(d + 128, kb_desc + 4, q_desc + 4, idesc, 1u);
-          umma_ss(d + 128, kb_desc + 6, q_desc + 6, idesc, 1u);
-          umma_commit(&sm.s_full[g]);
-          umma_commit(&sm.q_empty[s]);
-          if (i == i1 - 1) umma_commit(&sm.k_empty[kb]);
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      // (all lanes run the loop so that descriptors are warp-uniform; one elected lane issues)
+      constexpr uint32_t idesc = umma_idesc_bf16(kBN, kColHalf, 0);
+      ColWalk walk(p);
+      const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0][0]));
+      const uint64_t q_desc0 = smem_desc_sw128(smem_u32(sm.q[0]));
+      int ui = 0, n = 0, item, i0, i1;   // ui: running count of half tiles
+      int s = 0, s_round = 0;
+      for (; walk.next(item, i0, i1); ++n) {
+        const int kb = n & 1;
+        mbar_wait(&sm.k_full[kb], (n >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
+        const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(kb * kColGroup * (kTileBytes >> 4));
+        for (int i = i0; i < i1; ++i) {
+          mbar_wait(&sm.q_full[s], s_round & 1, p.err, DEV_TIMEOUT_TMA);
+#pragma unroll
+          for (int half = 0; half < 2; ++half, ++ui) {
+            const int g = ui & 1, it = ui >> 1;
+            // query rows 64*half.. of the tile: 8192 bytes further in the K-major tile
+            const uint64_t q_desc = q_desc0 + static_cast<uint64_t>(s * (kTileBytes >> 4) + half * (8192 >> 4));
+            const uint32_t d = tmem + g * kColHalf;
+            if (it > 0) mbar_wait(&sm.s_free[g], (it - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+            tc_fence_after();
+            if (elect_one()) {
+#pragma unroll
+              for (int t = 0; t < kColGroup; ++t) {
+                const uint64_t kd = k_desc + static_cast<uint64_t>(t * (kTileBytes >> 4));
+                umma_ss(d + t * 128, kd, q_desc, idesc, 0u);
+                umma_ss(d + t * 128, kd + 2, q_desc + 2, idesc, 1u);
+                umma_ss(d + t * 128, kd + 4, q_desc + 4, idesc, 1u);
+                umma_ss(d + t * 128, kd + 6, q_desc + 6, idesc, 1u);
+              }
+              umma_commit(&sm.s_full[g]);
+              if (half == 1) {
+                umma_commit(&sm.q_empty[s]);
+                if (i == i1 - 1) umma_commit(&sm.k_empty[kb]);
+              }
+            }
+            __syncwarp();
+          }
+          if (++s == kColStages) { s = 0; ++s_round; }
         }
-        __syncwarp();
-        if (++s == kColStages) { s = 0; ++s_round; }
       }
     }
   } else {
     // ------------------------------------------------------------------ exponent warpgroups
-    const int w = (warp - 2) >> 2;   // which key tile of the pair
+    setmaxnreg_inc<152>();
+    const int w = (warp - 4) >> 2;   // which key tile of the group
     const int wq = warp & 3;
     const int key = wq * 32 + lane;  // key inside the tile = TMEM lane
-    const int tid = threadIdx.x - 64;  // 0..255
-    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const int tid = threadIdx.x - 128;  // 0..383
+    const uint32_t t_base = tmem + (static_cast<uint32_t>(wq * 32) << 16) + w * 128;
     const float c2 = p.scale_log2;
-    uint32_t ra[32], rb[32];
     ColWalk walk(p);
-    int qi = 0, n = 0, item, i0, i1;
+    int ui = 0, n = 0, item, i0, i1;
     int cur_h = -1;
     for (; walk.next(item, i0, i1); ++n) {
-      const int h = item / p.n_pairs, pair = item - h * p.n_pairs;   // head-major item order
+      const int h = item / p.n_groups, grp = item - h * p.n_groups;   // head-major item order
       // negated row log-sum-exps of the head's query rows, reloaded only when the head changes
       // (a CTA's items are consecutive, so that is once or twice per launch)
       float* nl_s = sm.lse2;
       if (h != cur_h) {
         cur_h = h;
-        named_bar_sync(1, 256);   // everyone is done with the previous head's values
-        for (int r = tid; r < nq * kBM; r += 256) {
+        named_bar_sync(1, kColExpThreads);   // everyone is done with the previous head's values
+        for (int r = tid; r < nq * kBM; r += kColExpThreads) {
           float v = -INFINITY;
           if (r < p.M_sub)
             v = -p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(r) * p.row_stride];
           nl_s[r] = v;
         }
-        named_bar_sync(1, 256);
+        named_bar_sync(1, kColExpThreads);
       }
-      const int j = 2 * pair + w;
+      const int j = kColGroup * grp + w;
       const bool exists = j < p.n_tiles;
       const bool is_ret = j >= p.n_hot_tiles;
       const int n0 = (is_ret ? j - p.n_hot_tiles : j) * kBN;
       const int valid = exists ? min(kBN, (is_ret ? p.T_ret : p.T_hot) - n0) : 0;
       // the key's bias multiplies its whole column: exp2(s c2 + b2 - lse2) = 2^b2 exp2(s c2 - lse2);
-      // taken out of the exponent while it is small, else folded into the score scale below
+      // taken out of the exponent while it is small, else kept inside (rare, slower path)
       float b2 = 0.f;
       if (key < valid && is_ret) b2 = p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e;
       const bool b2_small = fabsf(b2) <= 32.f;
-      const float b2_in = b2_small ? 0.f : b2;   // rare: stays inside the exponent
+      const float b2_in = b2_small ? 0.f : b2;
       const bool warp_fast = __all_sync(0xffffffffu, b2_small);
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      // first tile of the item: nothing is in flight yet
-      {
-        const int g = qi & 1, it = qi >> 1;
-        mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
-        tc_fence_after();
-        tmem_ld32(tmem + lane_base + g * 256 + w * 128, ra);
-      }
-      for (int i = i0; i < i1; ++i, ++qi) {
-        const int g = qi & 1;
-        const uint32_t s_addr = tmem + lane_base + g * 256 + w * 128;
-        const float4* nl4 = reinterpret_cast<const float4*>(nl_s + i * kBM);
-        if (__builtin_expect(!warp_fast, 0)) {
-          // general path: the bias stays in the exponent
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld_wait();
-#pragma unroll
-            for (int q = 0; q < 32; ++q)
-              a0 += fast_exp2(fmaf(__uint_as_float(ra[q]), c2, b2_in + nl_s[i * kBM + c * 32 + q]));
-            if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, ra);
-          }
-          tmem_ld_wait();
-        } else {
-          tmem_ld_wait();
-          tmem_ld32(s_addr + 32, rb);
-          col_exp_chunk(ra, nl4, c2, a0, a1, a2, a3);
-          tmem_ld_wait();
-          tmem_ld32(s_addr + 64, ra);
-          col_exp_chunk(rb, nl4 + 8, c2, a0, a1, a2, a3);
-          tmem_ld_wait();
-          tmem_ld32(s_addr + 96, rb);
-          col_exp_chunk(ra, nl4 + 16, c2, a0, a1, a2, a3);
-          tmem_ld_wait();
-        }
-        // the next query tile of this item was scored while this one was summed: fetch its
-        // first 32 rows before the last chunk of this tile is worked on
-        const bool more = i + 1 < i1;
-        if (more) {
-          const int g2 = (qi + 1) & 1, it2 = (qi + 1) >> 1;
-          mbar_wait(&sm.s_full[g2], it2 & 1, p.err, DEV_TIMEOUT_MMA);
-          tc_fence_after();
-          tmem_ld32(tmem + lane_base + g2 * 256 + w * 128, ra);
-        }
-        if (warp_fast) col_exp_chunk(rb, nl4 + 24, c2, a0, a1, a2, a3);
-        tc_fence_before();
-        mbar_arrive(&sm.s_free[g]);
-      }
+      const int n_half = 2 * (i1 - i0);
+      const float* nl_item = nl_s + i0 * kBM;
+      float sum = warp_fast ? col_item_sum<true>(sm, p, t_base, nl_item, n_half, ui, c2, 0.f)
+                            : col_item_sum<false>(sm, p, t_base, nl_item, n_half, ui, c2, b2_in);
       if (key < valid) {
-        float sum = ((a0 + a1) + (a2 + a3)) * p.correction;
+        sum *= p.correction;
         if (b2_small) sum *= exp2f(b2);
         float* dst = p.colsum + static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key;
         if (i0 == 0 && i1 == nq) *dst = sum;
@@ -1156,8 +1173,8 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
     cp.T_hot = a.T_hot; cp.T_ret = a.T_ret;
     cp.n_hot_tiles = fp.n_hot_tiles; cp.n_q_tiles = nq;
     cp.n_tiles = fp.n_hot_tiles + fp.n_ret_tiles;
-    cp.n_pairs = (cp.n_tiles + 1) / 2;
-    cp.n_items = cp.n_pairs * a.H;
+    cp.n_groups = (cp.n_tiles + kColGroup - 1) / kColGroup;
+    cp.n_items = cp.n_groups * a.H;
     cp.scale_log2 = scale_log2; cp.correction = corr;
     cp.bias_ret = a.bias_ret; cp.bias_head_stride = a.bias_head_stride;
     cp.lse2 = lse2; cp.lse2_stride = a.M;
