@@ -67,6 +67,10 @@ struct FwdParams {
   long long lse2_stride;
   int* fallback;             // device flag: set by the fast kernel when a row needs the exact kernel
   int* err;
+  // fast kernel only: items = (head, 128-row query tile), head-major
+  int n_q_tiles, n_items;
+  int split;                 // 1: the (item, key tile) units are cut evenly over the grid
+  float* part;               // split == 1: two partial-result slots per CTA
 };
 
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
@@ -381,6 +385,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // so scores use one wide instruction per K step, the two MMA streams (scores, P V) have a
 // warp each, and the instructions of a group are issued back to back with operands prepared
 // beforehand.
+//
+// Work = items (head, 128-row query tile) x key tiles.  With enough items the kernel runs one
+// CTA per SM and cuts that unit sequence into equal contiguous ranges (no partly filled last
+// wave); a CTA walks its range segment by segment, a segment being a run of key tiles of one
+// item.  An item on a cut is computed in two parts by two CTAs, each with its own row
+// references; the parts (unnormalised accumulator, row sums, references) go to a workspace and
+// attn_fwd_combine_kernel joins them.  Barrier phases, the score ring and the K/V rings run on
+// across segments; the query tile, the row references and the partial row sums are double
+// buffered by segment parity, and so are the barriers that several warpgroups arrive on per
+// segment: a warpgroup without a tile in a short first or last segment runs one segment ahead,
+// never two (a CTA's middle segments are whole items of at least kFastMinSplitTiles tiles, far
+// longer than the few tiles the score ring lets the warpgroups be apart).
 // ---------------------------------------------------------------------------------------
 constexpr int kFastThreads = 512;   // warpgroup 0 control (warps 0, 3 TMA, warps 1-2 MMA issue), 1..3 softmax
 constexpr int kFastKStages = 5;
@@ -389,15 +405,19 @@ constexpr int kFT = 112;                        // keys per tile
 constexpr int kFastTileBytes = kFT * 128;       // 112 rows x 64 bf16
 constexpr int kFastRing = 4;
 constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
+constexpr int kPartFloats = kBM * kD + 2 * kBM; // one partial result: O[128][64], row sums, row references
+constexpr int kFastMaxCtas = 160;               // partial-result slots are provided for this many CTAs
+constexpr int kFastMinSplitTiles = 8;           // shorter key ranges run one CTA per item
 
 struct FastSmem {
-  uint8_t q[kTileBytes];
+  uint8_t q[2][kTileBytes];                     // query tile of the segment (parity)
   uint8_t k[kFastKStages][kFastTileBytes];
   uint8_t v[kFastVStages][kFastTileBytes];
   float bias2[3][kBN];
-  float m_ref[kBM];
-  float lpart[3][kBM];
-  uint64_t bar_q;
+  float m_ref[2][kBM];                          // row references of the segment (parity)
+  float lpart[2][2][kBM];                       // row sums of warpgroups 1 and 2 (segment parity)
+  uint64_t q_full[2];
+  uint64_t q_empty[2];
   uint64_t k_full[kFastKStages];
   uint64_t k_empty[kFastKStages];
   uint64_t v_full[kFastVStages];
@@ -405,9 +425,40 @@ struct FastSmem {
   uint64_t s_full[kFastRing];    // scores of a tile are in TMEM
   uint64_t p_full[kFastRing];    // its probabilities are in TMEM
   uint64_t buf_free[kFastRing];  // the P V MMAs that read them are done
-  uint64_t ref_ready;
-  uint64_t o_done;
+  uint64_t ref_ready[2];
+  uint64_t l_ready[2];           // warpgroups 1 and 2 have published their row sums of the segment (parity)
+  uint64_t o_done;               // all P V MMAs of the segment are complete
+  uint64_t o_free;               // the segment's accumulator has been read out of TMEM
   uint32_t tmem_base;
+};
+
+// The (item, key tile) units of one CTA, walked segment by segment: a segment is a run of key
+// tiles [t0, t1) of one item.  With `split` the units of the whole launch are cut into equal
+// contiguous ranges, one per CTA (an item on a cut is then finished by two CTAs); without it
+// CTA i owns item i.  Every role of the CTA walks the same sequence.
+struct FwdWalk {
+  long long u, u_end;
+  int nt;
+  __device__ FwdWalk(const FwdParams& p, int n_tiles) {
+    nt = n_tiles;
+    if (p.split) {
+      const long long total = static_cast<long long>(p.n_items) * nt;
+      u = total * blockIdx.x / gridDim.x;
+      u_end = total * (blockIdx.x + 1) / gridDim.x;
+    } else {
+      u = static_cast<long long>(blockIdx.x) * nt;
+      u_end = u + nt;
+    }
+  }
+  __device__ bool next(int& item, int& t0, int& t1) {
+    if (u >= u_end) return false;
+    item = static_cast<int>(u / nt);
+    t0 = static_cast<int>(u - static_cast<long long>(item) * nt);
+    const long long e = static_cast<long long>(item + 1) * nt;
+    t1 = static_cast<int>((e < u_end ? e : u_end) - static_cast<long long>(item) * nt);
+    u = static_cast<long long>(item) * nt + t1;
+    return true;
+  }
 };
 
 // kN scores -> kN probabilities relative to the row reference, packed as bf16 pairs.
@@ -456,13 +507,16 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   FastSmem& sm = *reinterpret_cast<FastSmem*>(align1024(smem_raw));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_tile = blockIdx.x;
-  const int h = blockIdx.y;
   const int n_hot = (p.T_hot + kFT - 1) / kFT;
   const int n_tiles = n_hot + (p.T_ret + kFT - 1) / kFT;
 
   if (threadIdx.x == 0) {
-    mbar_init(&sm.bar_q, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.q_full[i], 1);
+      mbar_init(&sm.q_empty[i], 1);
+      mbar_init(&sm.ref_ready[i], 128);
+      mbar_init(&sm.l_ready[i], 256);
+    }
     for (int s = 0; s < kFastKStages; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
@@ -476,8 +530,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&sm.p_full[b], 128);
       mbar_init(&sm.buf_free[b], 1);
     }
-    mbar_init(&sm.ref_ready, 128);
     mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.o_free, 128);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -493,87 +547,112 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (warp < 4) {
     setmaxnreg_dec<56>();
     if (warp == 0 && lane == 0) {
-      // ---------------------------------------------------------------- TMA producer
+      // ---------------------------------------------------------------- TMA producer: Q and K
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k_hot);
-      mbar_arrive_expect_tx(&sm.bar_q, kTileBytes);
-      tma_load_3d(sm.q, &tm_q, &sm.bar_q, 0, h, m_tile * kBM);
+      FwdWalk walk(p, n_tiles);
+      int seg = 0, item, t0, t1;
       int ks = 0, kr = 0;   // stage and round of the K ring
-      for (int j = 0; j < n_tiles; ++j) {
-        const bool hot = j < n_hot;
-        const int n0 = (hot ? j : j - n_hot) * kFT;
-        if (kr > 0) mbar_wait(&sm.k_empty[ks], (kr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        mbar_arrive_expect_tx(&sm.k_full[ks], kFastTileBytes);
-        tma_load_3d(sm.k[ks], hot ? &tm_k_hot : &tm_k_ret, &sm.k_full[ks], 0, n0, h);
-        if (++ks == kFastKStages) { ks = 0; ++kr; }
+      for (; walk.next(item, t0, t1); ++seg) {
+        const int h = item / p.n_q_tiles, m_tile = item - h * p.n_q_tiles;
+        const int qb = seg & 1;
+        if (seg >= 2) mbar_wait(&sm.q_empty[qb], ((seg >> 1) - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        mbar_arrive_expect_tx(&sm.q_full[qb], kTileBytes);
+        tma_load_3d(sm.q[qb], &tm_q, &sm.q_full[qb], 0, h, m_tile * kBM);
+        for (int j = t0; j < t1; ++j) {
+          const bool hot = j < n_hot;
+          const int n0 = (hot ? j : j - n_hot) * kFT;
+          if (kr > 0) mbar_wait(&sm.k_empty[ks], (kr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          mbar_arrive_expect_tx(&sm.k_full[ks], kFastTileBytes);
+          tma_load_3d(sm.k[ks], hot ? &tm_k_hot : &tm_k_ret, &sm.k_full[ks], 0, n0, h);
+          if (++ks == kFastKStages) { ks = 0; ++kr; }
+        }
       }
     } else if (warp == 3 && lane == 0) {
-      // ---------------------------------------------------------------- TMA producer for V
+      // ---------------------------------------------------------------- TMA producer: V
       // (its own thread: V tiles are released several tiles later than K tiles, and one
       // thread serving both rings in order would hold K back whenever the V ring is full)
       tma_prefetch_desc(&tm_v_hot);
+      FwdWalk walk(p, n_tiles);
+      int item, t0, t1;
       int vs = 0, vr = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const bool hot = j < n_hot;
-        const int n0 = (hot ? j : j - n_hot) * kFT;
-        if (vr > 0) mbar_wait(&sm.v_empty[vs], (vr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        mbar_arrive_expect_tx(&sm.v_full[vs], kFastTileBytes);
-        tma_load_3d(sm.v[vs], hot ? &tm_v_hot : &tm_v_ret, &sm.v_full[vs], 0, n0, h);
-        if (++vs == kFastVStages) { vs = 0; ++vr; }
+      while (walk.next(item, t0, t1)) {
+        const int h = item / p.n_q_tiles;
+        for (int j = t0; j < t1; ++j) {
+          const bool hot = j < n_hot;
+          const int n0 = (hot ? j : j - n_hot) * kFT;
+          if (vr > 0) mbar_wait(&sm.v_empty[vs], (vr - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          mbar_arrive_expect_tx(&sm.v_full[vs], kFastTileBytes);
+          tma_load_3d(sm.v[vs], hot ? &tm_v_hot : &tm_v_ret, &sm.v_full[vs], 0, n0, h);
+          if (++vs == kFastVStages) { vs = 0; ++vr; }
+        }
       }
     } else if (warp == 1) {
       // ---------------------------------------------------------------- MMA issuer: S = Q K^T
       // (all lanes run the loop, one elected lane issues)
       constexpr uint32_t idesc_s = umma_idesc_bf16(kBM, kFT, 0);
-      mbar_wait(&sm.bar_q, 0, p.err, DEV_TIMEOUT_TMA);
-      const uint64_t q_desc = smem_desc_sw128(smem_u32(sm.q));
+      const uint64_t q_desc0 = smem_desc_sw128(smem_u32(sm.q[0]));
       const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0]));
+      FwdWalk walk(p, n_tiles);
+      int seg = 0, item, t0, t1;
       int b = 0, round = 0, ks = 0, kr = 0;
+      for (; walk.next(item, t0, t1); ++seg) {
+        const int qb = seg & 1;
+        const uint64_t q_desc = q_desc0 + static_cast<uint64_t>(qb * (kTileBytes >> 4));
+        mbar_wait(&sm.q_full[qb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_TMA);
 #pragma unroll 1
-      for (int j = 0; j < n_tiles; ++j) {
-        const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(ks * (kFastTileBytes >> 4));
-        const uint32_t d = tmem + b * kFT;
-        mbar_wait(&sm.k_full[ks], kr & 1, p.err, DEV_TIMEOUT_TMA);
-        if (round > 0) mbar_wait(&sm.buf_free[b], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        tc_fence_after();
-        if (elect_one()) {
-          umma_ss(d, q_desc, k_desc, idesc_s, 0u);
-          umma_ss(d, q_desc + 2, k_desc + 2, idesc_s, 1u);
-          umma_ss(d, q_desc + 4, k_desc + 4, idesc_s, 1u);
-          umma_ss(d, q_desc + 6, k_desc + 6, idesc_s, 1u);
-          umma_commit(&sm.s_full[b]);
-          umma_commit(&sm.k_empty[ks]);
+        for (int j = t0; j < t1; ++j) {
+          const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(ks * (kFastTileBytes >> 4));
+          const uint32_t d = tmem + b * kFT;
+          mbar_wait(&sm.k_full[ks], kr & 1, p.err, DEV_TIMEOUT_TMA);
+          if (round > 0) mbar_wait(&sm.buf_free[b], (round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          tc_fence_after();
+          if (elect_one()) {
+            umma_ss(d, q_desc, k_desc, idesc_s, 0u);
+            umma_ss(d, q_desc + 2, k_desc + 2, idesc_s, 1u);
+            umma_ss(d, q_desc + 4, k_desc + 4, idesc_s, 1u);
+            umma_ss(d, q_desc + 6, k_desc + 6, idesc_s, 1u);
+            umma_commit(&sm.s_full[b]);
+            umma_commit(&sm.k_empty[ks]);
+            if (j == t1 - 1) umma_commit(&sm.q_empty[qb]);
+          }
+          __syncwarp();
+          if (++ks == kFastKStages) { ks = 0; ++kr; }
+          if (++b == kFastRing) { b = 0; ++round; }
         }
-        __syncwarp();
-        if (++ks == kFastKStages) { ks = 0; ++kr; }
-        if (++b == kFastRing) { b = 0; ++round; }
       }
     } else if (warp == 2) {
       // ---------------------------------------------------------------- MMA issuer: O += P V
       constexpr uint32_t idesc_o = umma_idesc_bf16(kBM, kD, 1);
       const uint64_t v_desc0 = smem_desc_sw128(smem_u32(sm.v[0]));
+      FwdWalk walk(p, n_tiles);
+      int seg = 0, item, t0, t1;
       int b = 0, round = 0, vs = 0, vr = 0;
+      for (; walk.next(item, t0, t1); ++seg) {
 #pragma unroll 1
-      for (int j = 0; j < n_tiles; ++j) {
-        // A: 16 keys = 8 columns of packed probabilities; B: V advances 16 rows = 2048 bytes
-        const uint32_t pa = tmem + b * kFT;
-        const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kFastTileBytes >> 4));
-        const uint32_t acc0 = j > 0 ? 1u : 0u;
-        mbar_wait(&sm.v_full[vs], vr & 1, p.err, DEV_TIMEOUT_TMA);
-        mbar_wait(&sm.p_full[b], round & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        tc_fence_after();
-        if (elect_one()) {
-          umma_ts(o_tmem, pa, vb, idesc_o, acc0);
+        for (int j = t0; j < t1; ++j) {
+          // A: 16 keys = 8 columns of packed probabilities; B: V advances 16 rows = 2048 bytes
+          const uint32_t pa = tmem + b * kFT;
+          const uint64_t vb = v_desc0 + static_cast<uint64_t>(vs * (kFastTileBytes >> 4));
+          const uint32_t acc0 = j > t0 ? 1u : 0u;
+          mbar_wait(&sm.v_full[vs], vr & 1, p.err, DEV_TIMEOUT_TMA);
+          mbar_wait(&sm.p_full[b], round & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          // a new segment overwrites the accumulator: the previous one must have been read out
+          if (j == t0 && seg > 0) mbar_wait(&sm.o_free, (seg - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          tc_fence_after();
+          if (elect_one()) {
+            umma_ts(o_tmem, pa, vb, idesc_o, acc0);
 #pragma unroll
-          for (int kk = 1; kk < kFT / 16; ++kk)
-            umma_ts(o_tmem, pa + kk * 8, vb + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, 1u);
-          umma_commit(&sm.buf_free[b]);
-          umma_commit(&sm.v_empty[vs]);
-          if (j == n_tiles - 1) umma_commit(&sm.o_done);
+            for (int kk = 1; kk < kFT / 16; ++kk)
+              umma_ts(o_tmem, pa + kk * 8, vb + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, 1u);
+            umma_commit(&sm.buf_free[b]);
+            umma_commit(&sm.v_empty[vs]);
+            if (j == t1 - 1) umma_commit(&sm.o_done);
+          }
+          __syncwarp();
+          if (++vs == kFastVStages) { vs = 0; ++vr; }
+          if (++b == kFastRing) { b = 0; ++round; }
         }
-        __syncwarp();
-        if (++vs == kFastVStages) { vs = 0; ++vr; }
-        if (++b == kFastRing) { b = 0; ++round; }
       }
     }
   } else {
@@ -585,135 +664,176 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c2 = p.scale_log2;
     const float* bias2 = sm.bias2[g];
-    float m_ref = 0.f;
-    float l0 = 0.f, l1 = 0.f;
     uint32_t ra[32], rb[32], pk[16];
-    int b = g, round = 0;   // ring buffer and round of tile j (j = g, g + 3, ...)
-    bool fetching = false;  // the first 32 scores of tile j are already on their way into ra
-    for (int j = g; j < n_tiles; j += 3) {
-      const bool is_ret = j >= n_hot;
-      const int n0 = (is_ret ? j - n_hot : j) * kFT;
-      const int valid = min(kFT, (is_ret ? p.T_ret : p.T_hot) - n0);
-      const bool need_bias = is_ret || valid < kFT;
-      if (need_bias) {
-        named_bar_sync(1 + g, 128);
-        if (row < kFT) {
-          float bv = -INFINITY;
-          if (row < valid) bv = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + row] * kLog2e : 0.f;
-          sm.bias2[g][row] = bv;
+    bool overflow = false;
+    FwdWalk walk(p, n_tiles);
+    int seg = 0, item, t0, t1;
+    int c_base = 0;   // key tiles of earlier segments: tile c of the CTA uses ring buffer c % 4, warpgroup c % 3
+    for (; walk.next(item, t0, t1); ++seg) {
+      const int h = item / p.n_q_tiles, m_tile = item - h * p.n_q_tiles;
+      const int len = t1 - t0;
+      const int sb = seg & 1;
+      float m_ref = 0.f;
+      float l0 = 0.f, l1 = 0.f;
+      bool have_ref = false;
+      bool fetching = false;  // the first 32 scores of the next tile are already on their way into ra
+      for (int x = (g + 3 - c_base % 3) % 3; x < len; x += 3) {
+        const int c = c_base + x;
+        const int b = c & (kFastRing - 1), round = c >> 2;
+        const int j = t0 + x;
+        const bool is_ret = j >= n_hot;
+        const int n0 = (is_ret ? j - n_hot : j) * kFT;
+        const int valid = min(kFT, (is_ret ? p.T_ret : p.T_hot) - n0);
+        const bool need_bias = is_ret || valid < kFT;
+        if (need_bias) {
+          named_bar_sync(1 + g, 128);
+          if (row < kFT) {
+            float bv = -INFINITY;
+            if (row < valid) bv = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + row] * kLog2e : 0.f;
+            sm.bias2[g][row] = bv;
+          }
+          named_bar_sync(1 + g, 128);
         }
-        named_bar_sync(1 + g, 128);
-      }
-      const uint32_t s_addr = tmem + lane_base + b * kFT;
-      if (!fetching) {
-        mbar_wait(&sm.s_full[b], round & 1, p.err, DEV_TIMEOUT_MMA);
-        tc_fence_after();
-        tmem_ld32(s_addr, ra);
-      }
-      if (j < 3) {
-        if (j == 0) {
-          // exact row maximum of the first tile = the row's reference for the whole call
-          float mx = -INFINITY;
-          tmem_ld_wait();
-          mx = fast_max_chunk<32>(ra, bias2, need_bias, c2, mx);
-          tmem_ld32(s_addr + 32, ra);
-          tmem_ld_wait();
-          mx = fast_max_chunk<32>(ra, bias2 + 32, need_bias, c2, mx);
-          tmem_ld32(s_addr + 64, ra);
-          tmem_ld_wait();
-          mx = fast_max_chunk<32>(ra, bias2 + 64, need_bias, c2, mx);
-          tmem_ld16(s_addr + 96, ra);
-          tmem_ld_wait();
-          mx = fast_max_chunk<16>(ra, bias2 + 96, need_bias, c2, mx);
-          m_ref = (mx == -INFINITY) ? 0.f : mx;
-          sm.m_ref[row] = m_ref;
-          mbar_arrive(&sm.ref_ready);
+        const uint32_t s_addr = tmem + lane_base + b * kFT;
+        if (!fetching) {
+          mbar_wait(&sm.s_full[b], round & 1, p.err, DEV_TIMEOUT_MMA);
+          tc_fence_after();
           tmem_ld32(s_addr, ra);
-        } else {
-          mbar_wait(&sm.ref_ready, 0, p.err, DEV_TIMEOUT_CONSUMER);
-          m_ref = sm.m_ref[row];
         }
+        if (!have_ref) {
+          have_ref = true;
+          if (x == 0) {
+            // exact row maximum of the segment's first tile = the row's reference for the segment
+            float mx = -INFINITY;
+            tmem_ld_wait();
+            mx = fast_max_chunk<32>(ra, bias2, need_bias, c2, mx);
+            tmem_ld32(s_addr + 32, ra);
+            tmem_ld_wait();
+            mx = fast_max_chunk<32>(ra, bias2 + 32, need_bias, c2, mx);
+            tmem_ld32(s_addr + 64, ra);
+            tmem_ld_wait();
+            mx = fast_max_chunk<32>(ra, bias2 + 64, need_bias, c2, mx);
+            tmem_ld16(s_addr + 96, ra);
+            tmem_ld_wait();
+            mx = fast_max_chunk<16>(ra, bias2 + 96, need_bias, c2, mx);
+            m_ref = (mx == -INFINITY) ? 0.f : mx;
+            sm.m_ref[sb][row] = m_ref;
+            mbar_arrive(&sm.ref_ready[sb]);
+            tmem_ld32(s_addr, ra);
+          } else {
+            mbar_wait(&sm.ref_ready[sb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+            m_ref = sm.m_ref[sb][row];
+          }
+        }
+        // keys 0..31 are on their way into ra
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 32, rb);
+        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
+        else fast_exp_chunk<false, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
+        tmem_st16(s_addr, pk);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 64, ra);
+        if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+        else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+        tmem_st16(s_addr + 16, pk);
+        tmem_ld_wait();
+        tmem_ld16(s_addr + 96, rb);
+        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+        else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+        tmem_st16(s_addr + 32, pk);
+        tmem_ld_wait();
+        // this warpgroup's next tile of the segment is normally scored by now: start fetching it
+        // (never wait for it here: its buffer is released by another warpgroup's P V, which may
+        // be behind this one)
+        const int b2 = (c + 3) & (kFastRing - 1), round2 = (c + 3) >> 2;
+        const bool more = x + 3 < len;
+        fetching = false;
+        if (more && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+          tc_fence_after();
+          tmem_ld32(tmem + lane_base + b2 * kFT, ra);
+          fetching = true;
+        }
+        if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+        else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+        tmem_st8(s_addr + 48, pk);
+        if (more && !fetching && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+          tc_fence_after();                  // second chance, a chunk later
+          tmem_ld32(tmem + lane_base + b2 * kFT, ra);
+          fetching = true;
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full[b]);
       }
-      // keys 0..31 are on their way into ra
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 32, rb);
-      if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
-      tmem_st16(s_addr, pk);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 64, ra);
-      if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
-      tmem_st16(s_addr + 16, pk);
-      tmem_ld_wait();
-      tmem_ld16(s_addr + 96, rb);
-      if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
-      tmem_st16(s_addr + 32, pk);
-      tmem_ld_wait();
-      // this warpgroup's next tile is normally scored by now: start fetching it (never wait for
-      // it here: its buffer is released by another warpgroup's P V, which may be behind this one)
-      int b2 = b + 3, round2 = round;
-      if (b2 >= kFastRing) { b2 -= kFastRing; ++round2; }
-      fetching = false;
-      if (j + 3 < n_tiles && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+      // ---- end of the segment
+      const float lsum = l0 + l1;
+      overflow = overflow || !(lsum <= kFastRowSumLimit);   // also true for NaN
+      if (g != 0) {
+        sm.lpart[sb][g - 1][row] = lsum;
+        mbar_arrive(&sm.l_ready[sb]);
+      } else {
+        if (!have_ref) {
+          mbar_wait(&sm.ref_ready[sb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+          m_ref = sm.m_ref[sb][row];
+        }
+        mbar_wait(&sm.l_ready[sb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+        const float l = (lsum + sm.lpart[sb][0][row]) + sm.lpart[sb][1][row];
+        mbar_wait(&sm.o_done, seg & 1, p.err, DEV_TIMEOUT_MMA);
         tc_fence_after();
-        tmem_ld32(tmem + lane_base + b2 * kFT, ra);
-        fetching = true;
+        tmem_ld32(o_tmem + lane_base, ra);
+        tmem_ld32(o_tmem + lane_base + 32, rb);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&sm.o_free);
+        const int mrow = m_tile * kBM + row;
+        if (t0 == 0 && t1 == n_tiles) {
+          // the whole item was done here: normalise and write the output rows
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          if (mrow < p.M) {
+            __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              uint4 val;
+              val.x = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 0]) * inv, __uint_as_float(ra[q8 * 8 + 1]) * inv);
+              val.y = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 2]) * inv, __uint_as_float(ra[q8 * 8 + 3]) * inv);
+              val.z = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 4]) * inv, __uint_as_float(ra[q8 * 8 + 5]) * inv);
+              val.w = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 6]) * inv, __uint_as_float(ra[q8 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
+            }
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              uint4 val;
+              val.x = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 0]) * inv, __uint_as_float(rb[q8 * 8 + 1]) * inv);
+              val.y = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 2]) * inv, __uint_as_float(rb[q8 * 8 + 3]) * inv);
+              val.z = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 4]) * inv, __uint_as_float(rb[q8 * 8 + 5]) * inv);
+              val.w = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 6]) * inv, __uint_as_float(rb[q8 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + 32 + q8 * 8) = val;
+            }
+            const float l2 = m_ref + log2f(l);
+            if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
+            p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
+          }
+        } else {
+          // part of an item: unnormalised accumulator, row sum and row reference go to this
+          // CTA's slot (slot 1: the item starts here and ends in the next CTA; slot 0: it began
+          // in the previous CTA); attn_fwd_combine_kernel joins the two parts
+          float* slot = p.part + static_cast<size_t>(2 * blockIdx.x + (t0 == 0 ? 1 : 0)) * kPartFloats;
+          float4* orow = reinterpret_cast<float4*>(slot + row * kD);
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            orow[q4] = make_float4(__uint_as_float(ra[q4 * 4 + 0]), __uint_as_float(ra[q4 * 4 + 1]),
+                                   __uint_as_float(ra[q4 * 4 + 2]), __uint_as_float(ra[q4 * 4 + 3]));
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            orow[8 + q4] = make_float4(__uint_as_float(rb[q4 * 4 + 0]), __uint_as_float(rb[q4 * 4 + 1]),
+                                       __uint_as_float(rb[q4 * 4 + 2]), __uint_as_float(rb[q4 * 4 + 3]));
+          slot[kBM * kD + row] = l;
+          slot[kBM * kD + kBM + row] = m_ref;
+        }
       }
-      if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
-      else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
-      tmem_st8(s_addr + 48, pk);
-      if (!fetching && j + 3 < n_tiles && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
-        tc_fence_after();                  // second chance, a chunk later
-        tmem_ld32(tmem + lane_base + b2 * kFT, ra);
-        fetching = true;
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&sm.p_full[b]);
-      b = b2; round = round2;
+      c_base += len;
     }
-    const float lsum = l0 + l1;
-    const bool overflow = !(lsum <= kFastRowSumLimit);   // also true for NaN
     if (__any_sync(0xffffffffu, overflow) && lane == 0) atomicOr(p.fallback, 1);
-    sm.lpart[g][row] = lsum;
-    named_bar_sync(4, 384);
-    if (g == 0) {
-      mbar_wait(&sm.o_done, 0, p.err, DEV_TIMEOUT_MMA);
-      tc_fence_after();
-      tmem_ld32(o_tmem + lane_base, ra);
-      tmem_ld32(o_tmem + lane_base + 32, rb);
-      tmem_ld_wait();
-      const float l = (sm.lpart[0][row] + sm.lpart[1][row]) + sm.lpart[2][row];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int mrow = m_tile * kBM + row;
-      if (mrow < p.M) {
-        __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
-#pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
-          uint4 val;
-          val.x = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 0]) * inv, __uint_as_float(ra[q8 * 8 + 1]) * inv);
-          val.y = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 2]) * inv, __uint_as_float(ra[q8 * 8 + 3]) * inv);
-          val.z = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 4]) * inv, __uint_as_float(ra[q8 * 8 + 5]) * inv);
-          val.w = pack_bf16x2(__uint_as_float(ra[q8 * 8 + 6]) * inv, __uint_as_float(ra[q8 * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
-        }
-#pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
-          uint4 val;
-          val.x = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 0]) * inv, __uint_as_float(rb[q8 * 8 + 1]) * inv);
-          val.y = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 2]) * inv, __uint_as_float(rb[q8 * 8 + 3]) * inv);
-          val.z = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 4]) * inv, __uint_as_float(rb[q8 * 8 + 5]) * inv);
-          val.w = pack_bf16x2(__uint_as_float(rb[q8 * 8 + 6]) * inv, __uint_as_float(rb[q8 * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + 32 + q8 * 8) = val;
-        }
-        const float l2 = m_ref + log2f(l);
-        if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
-        p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
-      }
-      tc_fence_before();
-    }
   }
   tc_fence_before();
   __syncthreads();
@@ -721,6 +841,46 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+}
+
+// Joins the two parts of every item that straddles a cut between CTA c and CTA c + 1 of the
+// split fast kernel: block c, one thread per query row.  Plain split-softmax algebra in a fixed
+// order, so the result does not depend on timing.
+__global__ void __launch_bounds__(kBM)
+attn_fwd_combine_kernel(const FwdParams p, int n_tiles, int grid) {
+  const int c = blockIdx.x;
+  const long long total = static_cast<long long>(p.n_items) * n_tiles;
+  const long long cut = total * (c + 1) / grid;      // first unit of CTA c + 1
+  if (cut % n_tiles == 0) return;                    // the cut falls between two items
+  const int item = static_cast<int>(cut / n_tiles);
+  const int h = item / p.n_q_tiles, m_tile = item - h * p.n_q_tiles;
+  const int row = threadIdx.x;
+  const int mrow = m_tile * kBM + row;
+  if (mrow >= p.M) return;
+  const float* a = p.part + static_cast<size_t>(2 * c + 1) * kPartFloats;
+  const float* b = p.part + static_cast<size_t>(2 * (c + 1)) * kPartFloats;
+  const float la = a[kBM * kD + row], ma = a[kBM * kD + kBM + row];
+  const float lb = b[kBM * kD + row], mb = b[kBM * kD + kBM + row];
+  const float m = fmaxf(ma, mb);
+  const float wa = exp2f(ma - m), wb = exp2f(mb - m);
+  const float l = la * wa + lb * wb;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const float4* oa = reinterpret_cast<const float4*>(a + row * kD);
+  const float4* ob = reinterpret_cast<const float4*>(b + row * kD);
+  __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
+#pragma unroll
+  for (int q8 = 0; q8 < 8; ++q8) {
+    const float4 a0 = oa[2 * q8], a1 = oa[2 * q8 + 1], b0 = ob[2 * q8], b1 = ob[2 * q8 + 1];
+    uint4 val;
+    val.x = pack_bf16x2((a0.x * wa + b0.x * wb) * inv, (a0.y * wa + b0.y * wb) * inv);
+    val.y = pack_bf16x2((a0.z * wa + b0.z * wb) * inv, (a0.w * wa + b0.w * wb) * inv);
+    val.z = pack_bf16x2((a1.x * wa + b1.x * wb) * inv, (a1.y * wa + b1.y * wb) * inv);
+    val.w = pack_bf16x2((a1.z * wa + b1.z * wb) * inv, (a1.w * wa + b1.w * wb) * inv);
+    *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
+  }
+  const float l2 = m + log2f(l);
+  if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
+  p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1080,7 +1240,10 @@ void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* cor
 // row log-sum-exps [H, M] followed by the fallback flag (64 floats of padding keep it aligned)
 size_t attn_lse2_elems(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 64; }
 
-int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t stream) {
+// partial results of the split forward kernel: two slots per CTA
+size_t attn_part_elems() { return static_cast<size_t>(2) * kFastMaxCtas * kPartFloats; }
+
+int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cudaStream_t stream) {
   if (a.D != kD) return STAC_ERR_BAD_ARG;
   if (a.M <= 0 || a.H <= 0 || a.T_hot < 0 || a.T_ret < 0 || a.T_hot + a.T_ret <= 0) return STAC_ERR_BAD_ARG;
   if (a.T_ret > 0 && (a.k_ret == nullptr || a.v_ret == nullptr || a.bias_ret == nullptr)) return STAC_ERR_BAD_ARG;
@@ -1160,10 +1323,27 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
   fp.err = err;
   fp.fallback = reinterpret_cast<int*>(lse2 + static_cast<size_t>(a.H) * a.M);
   dim3 grid_f((a.M + kBM - 1) / kBM, a.H);
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
+      return STAC_ERR_CUDA;
+  }
   // fast kernel (fixed per-row reference) first; the exact kernel behind it returns at once
-  // unless the fast one raised the flag
+  // unless the fast one raised the flag.  With at least one item per SM (and a workspace for
+  // the parts) the units are cut evenly over one CTA per SM, else every CTA takes one item.
+  fp.n_q_tiles = static_cast<int>(grid_f.x);
+  fp.n_items = fp.n_q_tiles * a.H;
+  const int n_tiles_f = (a.T_hot + kFT - 1) / kFT + (a.T_ret + kFT - 1) / kFT;
+  fp.split = (part != nullptr && fp.n_items >= n_sm && n_sm <= kFastMaxCtas && n_tiles_f >= kFastMinSplitTiles) ? 1 : 0;
+  fp.part = part;
+  const int grid_fast = fp.split ? n_sm : fp.n_items;
   if (cudaMemsetAsync(fp.fallback, 0, sizeof(int), stream) != cudaSuccess) return STAC_ERR_CUDA;
-  attn_fwd_fast_kernel<<<grid_f, kFastThreads, fast_smem, stream>>>(tm_q, tf_kh, tf_vh, tf_kr, tf_vr, fp);
+  attn_fwd_fast_kernel<<<grid_fast, kFastThreads, fast_smem, stream>>>(tm_q, tf_kh, tf_vh, tf_kr, tf_vr, fp);
+  if (fp.split) {
+    attn_fwd_combine_kernel<<<grid_fast - 1, kBM, 0, stream>>>(fp, n_tiles_f, grid_fast);
+  }
   attn_fwd_kernel<<<grid_f, kFwdThreads, fwd_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
   if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
 
@@ -1180,13 +1360,6 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, int* err, cudaStream_t st
     cp.lse2 = lse2; cp.lse2_stride = a.M;
     cp.colsum = a.colsum; cp.colsum_stride = a.colsum_head_stride;
     cp.err = err;
-    static int n_sm = 0;
-    if (n_sm == 0) {
-      int dev = 0;
-      if (cudaGetDevice(&dev) != cudaSuccess ||
-          cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
-        return STAC_ERR_CUDA;
-    }
     // enough items: cut the units evenly over one CTA per SM (an item is then shared by at most
     // two CTAs, which add their partial sums onto zeros); else one item per CTA
     cp.split = cp.n_items >= n_sm ? 1 : 0;
@@ -1264,5 +1437,5 @@ extern "C" int stac_attn_colsum_noalloc(const void* q, int64_t q_row_stride, con
   a.M = M; a.H = H; a.D = D; a.scale = scale; a.subsample_ratio = subsample_ratio;
   // Every entry of the scratch that the column-sum pass reads (rows < M of each head) is
   // written by the forward pass of this same call, so nothing has to be cleared first.
-  return stac::attn_colsum_launch(a, scratch, dev_status, reinterpret_cast<cudaStream_t>(stream));
+  return stac::attn_colsum_launch(a, scratch, nullptr, dev_status, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -15,13 +15,16 @@ def _bf16(x):
     return torch.from_numpy(x).to(torch.bfloat16)
 
 
-def _run_two_segment(M, H, T_hot, T_ret, seed, T_buf=None, subsample=1.0, spread=1.0, bias_shift=0.0):
+def _run_two_segment(M, H, T_hot, T_ret, seed, T_buf=None, subsample=1.0, spread=1.0, bias_shift=0.0,
+                     first_keys_scale=1.0):
     from stac_b200 import ops
     rs = np.random.RandomState(seed)
     D = 64
     T_buf = T_buf or (T_hot + 37)
     q = _bf16(rs.randn(M, H, D).astype(np.float32) * spread)
-    kh = _bf16(rs.randn(H, T_buf, D).astype(np.float32) * spread)
+    kh_f = rs.randn(H, T_buf, D).astype(np.float32) * spread
+    kh_f[:, :128] *= first_keys_scale          # the forward kernel takes its row reference from the first keys
+    kh = _bf16(kh_f)
     vh = _bf16(rs.randn(H, T_buf, D).astype(np.float32))
     kr = _bf16(rs.randn(H, max(T_ret, 1), D).astype(np.float32) * spread)
     vr = _bf16(rs.randn(H, max(T_ret, 1), D).astype(np.float32))
@@ -80,6 +83,33 @@ def test_units_split_over_all_sms():
     _assert_close(got, ref)
     again, _ = _run_two_segment(300, 16, 2500, 140, seed=21)
     assert np.array_equal(got[2], again[2])          # shared items sum to the same bits every run
+
+
+def test_forward_units_split_over_all_sms():
+    """More (head, query tile) items than SMs: the forward kernel runs one CTA per SM over equal
+    ranges of (item, key tile) units; items on a cut are computed in two parts and joined."""
+    got, ref = _run_two_segment(1200, 16, 700, 150, seed=33)
+    _assert_close(got, ref)
+    again, _ = _run_two_segment(1200, 16, 700, 150, seed=33)
+    assert np.array_equal(got[0], again[0]) and np.array_equal(got[1], again[1])   # same bits every run
+
+
+def test_forward_split_with_peaked_scores():
+    got, ref = _run_two_segment(1100, 16, 1000, 0, seed=34, spread=2.0)
+    _assert_close(got, ref)
+
+
+@pytest.mark.parametrize("M,H,T_hot", [(300, 2, 700), (1100, 16, 1000)])
+def test_scores_far_above_the_first_keys(M, H, T_hot):
+    """Tiny first keys give every row a reference near zero while later scores reach 2^60 and
+    more above it: the fixed-reference kernel must notice and the exact kernel must redo the call
+    (one CTA per item, and the split grid)."""
+    got, ref = _run_two_segment(M, H, T_hot, 0, seed=35, spread=4.0, first_keys_scale=1e-3)
+    (o, lse, cs), (o_ref, lse_ref, cs_ref) = got, ref
+    assert np.isfinite(o).all() and np.isfinite(cs).all()
+    assert np.abs(o - o_ref).max() <= 2e-2 * max(1.0, float(np.abs(o_ref).max()))
+    np.testing.assert_allclose(lse, lse_ref, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(cs, cs_ref, rtol=1e-3, atol=1e-6)
 
 
 @pytest.mark.parametrize("shift", [-40.0, 30.0])
