@@ -53,6 +53,7 @@ int stac_attn_colsum(const void* q, int64_t q_row_stride, const void* k_hot, con
   if (q == nullptr || out == nullptr || workspace == nullptr) return STAC_ERR_BAD_ARG;
   if (!(subsample_ratio > 0.f && subsample_ratio <= 1.f)) return STAC_ERR_BAD_ARG;
   if (workspace_bytes < stac_attn_workspace_bytes(M, H)) return STAC_ERR_CAPACITY;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return STAC_ERR_BAD_ARG;
   if ((q_row_stride % 8) || (out_row_stride % 8) || (hot_head_stride % 8) || (ret_head_stride % 8) ||
       (hot_row_stride % 8) || (ret_row_stride % 8))
     return STAC_ERR_BAD_ARG;
