@@ -4,9 +4,11 @@ recent + pinned pruning with gather-compaction.
 
 Differences that do not change results: the cache is double-buffered so compaction is a pure
 gather into the second buffer (the attributes ``key_cache_hot`` / ``value_cache_hot`` always
-name the live one); attention reads the [H, T, D] cache in place.  The reference's CPU spill
-ring for buffers longer than ``gpu_limit`` frames (stac/kv_manager.py:244-283) is not provided:
-appending beyond the GPU buffer raises.
+name the live one); attention reads the [H, T, D] cache in place.  The CPU spill of buffers
+longer than ``gpu_limit`` frames (stac/kv_manager.py:244-283) keeps the reference's rule (the
+oldest tokens of an append that does not fit go to the host buffer, which only ever grows and
+raises when full) with pinned host memory and stream-ordered copies; plain attention then reads
+the spilled tokens as a second key segment from a device staging buffer.
 """
 
 import gc
@@ -123,6 +125,14 @@ class KVManager:
         self._alloc_cache()
         self._offset_hot = [0] * self._L_eff
         self._offset_hot_cpu = [0] * self._L_eff
+        self.use_cpu = False
+        T_cpu = self.reserved_buffer_token_size_cpu
+        self.key_cache_hot_cpu = self.value_cache_hot_cpu = None
+        self._cpu_stage = None
+        if T_cpu > 0:
+            shape = (self._L_eff, self.num_heads, T_cpu, self.head_dim)
+            self.key_cache_hot_cpu = torch.empty(shape, dtype=self.dtype).pin_memory()
+            self.value_cache_hot_cpu = torch.empty(shape, dtype=self.dtype).pin_memory()
 
     def free(self):
         self._processed_frames = 0
@@ -130,6 +140,8 @@ class KVManager:
         self._kv = self._ti = None
         self._offset_hot = None
         self._offset_hot_cpu = None
+        self.key_cache_hot_cpu = self.value_cache_hot_cpu = None
+        self._cpu_stage = None
         gc.collect()
         torch.cuda.synchronize(self.device)
         torch.cuda.empty_cache()
@@ -143,12 +155,32 @@ class KVManager:
         assert new_T % self.token_per_f == 0, "T_new must be a multiple of token_per_frame in append_kv()."
         slot = self._to_slot(layer_idx, strict=True)
         old_T = self._offset_hot[slot]
-        if old_T + new_T > self.reserved_buffer_token_size:
-            raise RuntimeError(f"hot cache overflow ({old_T}+{new_T} > {self.reserved_buffer_token_size} tokens); "
-                               "the CPU spill ring of the reference is not provided")
         k, v = key_states[0], value_states[0]
         if k.dtype != self.dtype or v.dtype != self.dtype or not k.is_cuda:
             k, v = k.to(self.device, self.dtype), v.to(self.device, self.dtype)
+        # the GPU buffer takes the LAST tokens that fit, the host buffer the first ones
+        # (stac/kv_manager.py:244-283); token ids are kept for the GPU part only
+        to_gpu = min(new_T, max(self.reserved_buffer_token_size - old_T, 0))
+        to_cpu = new_T - to_gpu
+        if to_cpu > 0:
+            warnings.warn(f"Exceeding GPU buffer token size {self.reserved_buffer_token_size} in append_kv(). "
+                          f"{to_cpu} tokens will be stored on CPU.")
+            self.use_cpu = True
+            if self.reserved_buffer_token_size_cpu > 0:
+                old_c = self._offset_hot_cpu[slot]
+                if old_c + to_cpu > self.reserved_buffer_token_size_cpu:
+                    raise RuntimeError("CPU buffer overflow in append_kv(). Increase gpu_limit or buffer_size.")
+                self.key_cache_hot_cpu[slot, :, old_c:old_c + to_cpu].copy_(k[:, :to_cpu], non_blocking=True)
+                self.value_cache_hot_cpu[slot, :, old_c:old_c + to_cpu].copy_(v[:, :to_cpu], non_blocking=True)
+                self._offset_hot_cpu[slot] = old_c + to_cpu
+        F_new = new_T // self.token_per_f
+        first_id = self._processed_frames * self.token_per_f + to_cpu
+        if slot == self._L_eff - 1:
+            self._processed_frames += F_new
+        if to_gpu == 0:
+            return
+        k, v = k[:, to_cpu:], v[:, to_cpu:]
+        new_T = to_gpu
         if k.stride(2) != 1 or (k.stride(0) % 8) or (k.stride(1) % 8) or (k.data_ptr() % 16):
             k = k.contiguous()
         if v.stride(2) != 1 or (v.stride(0) % 8) or (v.stride(1) % 8) or (v.data_ptr() % 16):
@@ -157,11 +189,9 @@ class KVManager:
         kc, vc, ti = self.key_cache_hot[slot], self.value_cache_hot[slot], self._token_indices_hot[slot]
         check(_lib.lib().stac_append_kv(ptr(k), ptr(v), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
                                         ptr(kc), ptr(vc), kc.stride(0), ptr(ti), ti.stride(0), H, new_T, old_T,
-                                        self._processed_frames * self.token_per_f, D, 2, stream_ptr()),
+                                        first_id, D, 2, stream_ptr()),
               "stac_append_kv")
         self._offset_hot[slot] = old_T + new_T
-        if slot == self._L_eff - 1:
-            self._processed_frames += F_new
 
     @torch.no_grad()
     def prefill(self, query_states, key_states, value_states, layer_idx: int):
@@ -199,9 +229,24 @@ class KVManager:
 
     @torch.no_grad()
     def decode_sparse_attn(self, query_states: torch.Tensor, layer_idx: int) -> torch.Tensor:
-        """Plain attention over the hot cache; query_states [B, Tq, H, D] -> [B, Tq, H, D]."""
+        """Plain attention over the hot cache and, once tokens were spilled, the host part as well
+        (stac/kv_manager.py:311-360); query_states [B, Tq, H, D] -> [B, Tq, H, D]."""
         slot = self._to_slot(layer_idx, strict=True)
-        out, _ = self._attend(query_states, slot)
+        T_cpu = self._offset_hot_cpu[slot] if self.use_cpu and self.key_cache_hot_cpu is not None else 0
+        if T_cpu == 0:
+            out, _ = self._attend(query_states, slot)
+            return out
+        # bring the spilled tokens back into a device staging buffer (stream-ordered copies from
+        # pinned memory) and attend over them as a second key segment with zero bias
+        if self._cpu_stage is None:
+            shape = (self.num_heads, self.reserved_buffer_token_size_cpu, self.head_dim)
+            self._cpu_stage = (torch.empty(shape, dtype=self.dtype, device=self.device),
+                               torch.empty(shape, dtype=self.dtype, device=self.device),
+                               torch.zeros(shape[:2], dtype=torch.float32, device=self.device))
+        ks, vs, zero_bias = self._cpu_stage
+        ks[:, :T_cpu].copy_(self.key_cache_hot_cpu[slot, :, :T_cpu], non_blocking=True)
+        vs[:, :T_cpu].copy_(self.value_cache_hot_cpu[slot, :, :T_cpu], non_blocking=True)
+        out, _ = self._attend(query_states, slot, ks, vs, zero_bias, T_cpu)
         return out
 
     # ------------------------------------------------------------------ prune
@@ -286,10 +331,20 @@ class KVManager:
         return self._offset_hot.copy()
 
     def get_offset_cpu(self) -> List[int]:
-        return [0] * self._L_eff
+        if getattr(self, "_offset_hot_cpu", None) is None:
+            return [0] * self._L_eff
+        return self._offset_hot_cpu.copy()
 
     def get_cpu_memory_usage(self) -> Tuple[float, float]:
-        return 0.0, 0.0
+        """(used MB, allocated MB) of the host part; zeros while nothing was spilled
+        (stac/kv_manager.py:488-503)."""
+        if not getattr(self, "use_cpu", False) or getattr(self, "_offset_hot_cpu", None) is None:
+            return 0.0, 0.0
+        eb = torch.finfo(self.dtype).bits // 8
+        mb = 1024.0 ** 2
+        usage = sum(2 * self.num_heads * T * self.head_dim * eb for T in self._offset_hot_cpu) / mb
+        alloc = self._L_eff * 2 * self.reserved_buffer_token_size_cpu * self.num_heads * self.head_dim * eb / mb
+        return usage, alloc
 
     def get_memory_usage(self) -> Tuple[float, float]:
         eb = torch.finfo(self.dtype).bits // 8

@@ -177,3 +177,50 @@ def test_window_manager_and_h2o_manager():
     assert win.get_offset() == [3 * tpf] * L
     first = win.get_token_indices()[0, 0, : 3 * tpf].numpy()
     assert np.array_equal(first[:tpf], np.arange(tpf)) and np.array_equal(first[tpf:], np.arange(5 * tpf, 7 * tpf))
+
+
+def test_cpu_spill_of_the_window_manager():
+    """Buffers longer than gpu_limit frames: the oldest tokens of an append that does not fit go to
+    the host buffer, plain attention still sees them, the host buffer raises when full
+    (stac/kv_manager.py:227-360)."""
+    import warnings
+    from stac_b200.stac import KVManager
+    dev = torch.device("cuda:0")
+    tpf, H, D, L = 40, 2, 64, 2
+    mgr = KVManager(num_layers=L, num_heads=H, head_dim=D, token_per_frame=tpf, chunk_size=1, buffer_size=5,
+                    recent_size=1, pinned_idx=[0], dtype=torch.bfloat16, device=dev, gpu_limit=2)
+    mgr.reset()
+    assert mgr.reserved_buffer_token_size == 2 * tpf and mgr.reserved_buffer_token_size_cpu == 3 * tpf
+    g = torch.Generator().manual_seed(4)
+    ks, vs = [], []
+
+    def append(frames):
+        k = torch.randn(L, 1, H, frames * tpf, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(L, 1, H, frames * tpf, D, generator=g).to(torch.bfloat16)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            for l in range(L):
+                mgr.append_kv(k[l].to(dev), v[l].to(dev), l)
+        ks.append(k), vs.append(v)
+
+    append(1)                       # fits
+    assert mgr.get_offset() == [tpf] * L and mgr.get_offset_cpu() == [0] * L and not mgr.use_cpu
+    append(3)                       # one frame of room: the first two frames spill, the last stays
+    assert mgr.get_offset() == [2 * tpf] * L and mgr.get_offset_cpu() == [2 * tpf] * L and mgr.use_cpu
+    ti = mgr.get_token_indices()
+    assert np.array_equal(ti[0, 0].numpy(), np.r_[np.arange(tpf), np.arange(3 * tpf, 4 * tpf)])
+    used, alloc = mgr.get_cpu_memory_usage()
+    assert used == pytest.approx(L * 2 * H * 2 * tpf * D * 2 / 1024.0 ** 2) and alloc > used
+    q = torch.randn(1, 50, H, D, generator=g).to(torch.bfloat16)
+    for l in range(L):
+        out = mgr.decode_sparse_attn(q.to(dev), l)
+        torch.cuda.synchronize()
+        k_all = torch.cat([x[l, 0] for x in ks], dim=1).float().numpy().transpose(1, 0, 2)   # [T, H, D]
+        v_all = torch.cat([x[l, 0] for x in vs], dim=1).float().numpy().transpose(1, 0, 2)
+        o_ref, _, _ = oracle_attn(q[0].float().numpy(), k_all, v_all, None)
+        assert np.abs(out[0].float().cpu().numpy() - o_ref).max() <= 2e-2
+    mgr.check_status() if hasattr(mgr, "check_status") else None
+    append(1)                       # GPU part full: everything goes to the host (3 of 3 frames now)
+    assert mgr.get_offset_cpu() == [3 * tpf] * L
+    with pytest.raises(RuntimeError, match="CPU buffer overflow"):
+        append(1)
