@@ -455,6 +455,54 @@ def run_microbench_attn(args):
                       "config": {"workload": f"config2 attention microbench M={M} Lk={Lk} pivots={n_ret} H=16 D=64 bf16"}}))
 
 
+def run_microbench_pointmap(args):
+    """Point maps of one chunk (4 frames, 518 x 392) -> patch points + mask -> voxel ids: the
+    fused kernel against the reference's torch sequence (permute, two interpolates, reshape, cat)
+    on the same device, both followed by the same voxel upsert."""
+    import torch
+    from stac_b200 import _lib
+    from stac_b200.stac.pointmap import pointmap_to_positions
+    dev = torch.device("cuda:0")
+    S, H, W, patch, special = CFG["chunk"], 392, 518, 14, 5
+    g = torch.Generator(device="cpu").manual_seed(0)
+    wp = (torch.rand(1, S, H, W, 3, generator=g) * 8 - 4).to(dev)
+    cf = (torch.rand(1, S, H, W, generator=g) * 2).to(dev)
+
+    def torch_path():
+        p = wp.permute(0, 1, 4, 2, 3).view(-1, 3, H, W)
+        c = cf.unsqueeze(-1).permute(0, 1, 4, 2, 3).view(-1, 1, H, W)
+        ds = (H // patch, W // patch)
+        p = torch.nn.functional.interpolate(p, size=ds, mode="bilinear", align_corners=False)
+        c = torch.nn.functional.interpolate(c, size=ds, mode="bilinear", align_corners=False)
+        p = torch.cat((p.new_zeros((S, special, 3)), p.permute(0, 2, 3, 1).reshape(S, -1, 3)), dim=1)
+        m = c.permute(0, 2, 3, 1).reshape(S, -1) > 1.0
+        return p, torch.cat((m.new_zeros((S, special)), m), dim=1)
+
+    def ours():
+        return pointmap_to_positions(wp, cf, patch, 1.0, special)
+
+    res = {}
+    for name, fn in (("torch_sequence", torch_path), ("fused_kernel", ours)):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) / args.steps * 1e3
+    a, b = torch_path(), ours()
+    same = bool(torch.equal(a[1], b[1])) and float((a[0] - b[0]).abs().max()) < 1e-5
+    n_tok = S * (special + (H // patch) * (W // patch))
+    print(json.dumps({"metric": "pointmap_to_positions_us", "value": round(res["fused_kernel"], 2), "unit": "us",
+                      "torch_sequence_us": round(res["torch_sequence"], 2), "tokens": n_tok,
+                      "algorithmic_bytes": n_tok * (4 * 16 + 13), "agrees_with_torch_sequence": same,
+                      "kernels": _lib.kernel_launches(), "steps": args.steps,
+                      "config": {"workload": f"point maps {S} x {H} x {W} -> {n_tok} patch points (latency-bound)"}}))
+
+
 def run_microbench_merge(args):
     """Merge + retrieve on config-3-like shapes (384 pool heads, bf16, T_d tokens per head per
     step drawn around a smooth surface); prints GB/s with E*(4*D*e+12) algorithmic bytes."""
@@ -610,7 +658,7 @@ if __name__ == "__main__":
     ap.add_argument("--shard", default="streams", choices=["streams", "heads"],
                     help="N > 1: one independent stream per GPU (default, weak scaling) or ONE stream whose heads "
                          "and voxel memory are sharded over the GPUs (strong scaling)")
-    ap.add_argument("--microbench", default=None, choices=["attn", "merge"],
+    ap.add_argument("--microbench", default=None, choices=["attn", "merge", "pointmap"],
                     help="kernel microbenchmarks used for profiling (not the headline line)")
     ap.add_argument("--lk", type=int, default=10376, help="attention microbench: number of keys")
     ap.add_argument("--m", type=int, default=None, help="microbench: query rows (attn) / evicted tokens per head (merge)")
@@ -622,6 +670,8 @@ if __name__ == "__main__":
     elif a.microbench == "merge":
         a.m = a.m or 8328
         run_microbench_merge(a)
+    elif a.microbench == "pointmap":
+        run_microbench_pointmap(a)
     elif a.impl == "reference":
         run_reference(a)
     else:

@@ -115,6 +115,19 @@ int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* ma
                       int* n_voxels, int* ids_out, void* scratch, size_t scratch_bytes,
                       int* dev_status, stac_stream_t stream);
 
+/* StreamSession.get_pointmap (stream_session.py:213-256) for the "pointmap" prediction mode,
+ * without the permutes and interpolate calls: world points f32 [S,H,W,3] and their confidence
+ * f32 [S,H,W] are reduced to one point per patch by bilinear interpolation (align_corners =
+ * False; output size H' = max(1, H/patch), W' = max(1, W/patch)); every frame gets `special`
+ * zero points with mask 0 in front.  points_out f32 [S * (special + H'W'), 3], mask_out u8
+ * [S * (special + H'W')] = (interpolated confidence > conf_threshold): the arguments of
+ * STACVoxelKV.append_positions / stac_voxel_upsert.  fp32 arithmetic in the order of torch's
+ * CPU kernel for this (channels-last) layout: the axis weights are multiplied first and the
+ * four taps added left to right, nothing fused. */
+int stac_pointmap_to_positions(const float* world_points, const float* conf, int S, int H, int W, int patch,
+                               int special, float conf_threshold, float* points_out, uint8_t* mask_out,
+                               stac_stream_t stream);
+
 /* Ascending unique ids of the existing voxels inside the Chebyshev cube of `radius_cells`
  * around the voxels of `token_voxel_ids` (negative entries ignored); with all_ids != 0 every id
  * in the table instead.  flags u8 [table_cap] must be zero on entry and is zero on exit;

@@ -65,6 +65,8 @@ SIGNATURES = {
     "stac_voxel_rehash": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_i64, c_void_p]),
     "stac_voxel_upsert": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_f32, c_void_p, c_int, c_void_p, c_void_p, c_i64,
                                   c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "stac_pointmap_to_positions": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_f32, c_void_p,
+                                           c_void_p, c_void_p]),
     "stac_voxel_neighbors": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_i64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "stac_append_kv": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_void_p, c_void_p, c_i64, c_void_p,
@@ -88,7 +90,7 @@ SIGNATURES = {
 # left out when the call has fewer (head, query tile) items than the GPU has SMs)
 KERNELS_PER_CALL = {
     "stac_attn_colsum": 4, "stac_attn_colsum_noalloc": 3, "stac_selftest_bounded_wait": 1,
-    "stac_voxel_hash_clear": 1, "stac_voxel_rehash": 2, "stac_voxel_upsert": 3, "stac_voxel_neighbors": 2,
+    "stac_voxel_hash_clear": 1, "stac_voxel_rehash": 2, "stac_voxel_upsert": 3, "stac_voxel_neighbors": 2, "stac_pointmap_to_positions": 1,
     "stac_append_kv": 1, "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 16, "stac_retrieve": 2,
 }
 CALLS = {}

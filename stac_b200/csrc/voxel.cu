@@ -270,6 +270,52 @@ __global__ void rehash_kernel(const long long* __restrict__ table_keys, const in
 
 bool is_pow2(long long x) { return x > 0 && (x & (x - 1)) == 0; }
 
+
+// One thread per output token: frame s, token t (the first `special` tokens of a frame are zero
+// points with mask 0, the others patch centres in row-major order).
+__global__ void pointmap_kernel(const float* __restrict__ wp, const float* __restrict__ conf, int S, int H, int W,
+                                int oh, int ow, int special, float conf_threshold, float* __restrict__ pts,
+                                uint8_t* __restrict__ mask) {
+  const int n_tok = special + oh * ow;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(S) * n_tok) return;
+  const int s = static_cast<int>(idx / n_tok), t = static_cast<int>(idx - static_cast<long long>(s) * n_tok);
+  float* o = pts + idx * 3;
+  if (t < special) {
+    o[0] = 0.f; o[1] = 0.f; o[2] = 0.f;
+    mask[idx] = 0;
+    return;
+  }
+  const int py = (t - special) / ow, px = (t - special) - py * ow;
+  // source index and weights along one axis: src = max(scale * (d + 0.5) - 0.5, 0), every step rounded
+  auto plan = [](int n_in, int n_out, int d, int& i0, int& i1, float& l0, float& l1) {
+    const float scale = __fdiv_rn(static_cast<float>(n_in), static_cast<float>(n_out));
+    float src = __fsub_rn(__fmul_rn(scale, __fadd_rn(static_cast<float>(d), 0.5f)), 0.5f);
+    src = fmaxf(src, 0.f);
+    i0 = min(static_cast<int>(src), n_in - 1);
+    i1 = i0 + (i0 < n_in - 1 ? 1 : 0);
+    l1 = fminf(fmaxf(__fsub_rn(src, static_cast<float>(i0)), 0.f), 1.f);
+    l0 = __fsub_rn(1.f, l1);
+  };
+  int h0, h1, w0, w1;
+  float a0, a1, b0, b1;
+  plan(H, oh, py, h0, h1, a0, a1);
+  plan(W, ow, px, w0, w1, b0, b1);
+  const float w00 = __fmul_rn(a0, b0), w01 = __fmul_rn(a0, b1), w10 = __fmul_rn(a1, b0), w11 = __fmul_rn(a1, b1);
+  const long long frame = static_cast<long long>(s) * H * W;
+  const long long p00 = frame + static_cast<long long>(h0) * W + w0, p01 = frame + static_cast<long long>(h0) * W + w1;
+  const long long p10 = frame + static_cast<long long>(h1) * W + w0, p11 = frame + static_cast<long long>(h1) * W + w1;
+  auto tap4 = [&](float v00, float v01, float v10, float v11) {
+    float r = __fmul_rn(w00, v00);
+    r = __fadd_rn(r, __fmul_rn(w01, v01));
+    r = __fadd_rn(r, __fmul_rn(w10, v10));
+    return __fadd_rn(r, __fmul_rn(w11, v11));
+  };
+#pragma unroll
+  for (int c = 0; c < 3; ++c) o[c] = tap4(wp[p00 * 3 + c], wp[p01 * 3 + c], wp[p10 * 3 + c], wp[p11 * 3 + c]);
+  mask[idx] = tap4(conf[p00], conf[p01], conf[p10], conf[p11]) > conf_threshold ? 1 : 0;
+}
+
 }  // namespace
 }  // namespace stac
 
@@ -366,6 +412,22 @@ int stac_voxel_neighbors(const int* token_voxel_ids, int n_tokens, int radius_ce
         static_cast<const unsigned long long*>(hash_keys), hash_vals, static_cast<int>(hash_cap), flags);
   }
   stac::compact_flags_kernel<<<1, 1024, 0, st>>>(flags, n_voxels, all_ids, out_ids, out_count);
+  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+}
+
+int stac_pointmap_to_positions(const float* world_points, const float* conf, int S, int H, int W, int patch,
+                               int special, float conf_threshold, float* points_out, uint8_t* mask_out,
+                               stac_stream_t stream) {
+  if (world_points == nullptr || conf == nullptr || points_out == nullptr || mask_out == nullptr)
+    return STAC_ERR_BAD_ARG;
+  if (S <= 0 || H <= 0 || W <= 0 || patch <= 0 || special < 0) return STAC_ERR_BAD_ARG;
+  const int oh = H / patch > 1 ? H / patch : 1, ow = W / patch > 1 ? W / patch : 1;
+  const long long n = static_cast<long long>(S) * (special + static_cast<long long>(oh) * ow);
+  const int threads = 128;
+  const long long blocks = (n + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return STAC_ERR_BAD_ARG;
+  stac::pointmap_kernel<<<static_cast<unsigned>(blocks), threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      world_points, conf, S, H, W, oh, ow, special, conf_threshold, points_out, mask_out);
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 

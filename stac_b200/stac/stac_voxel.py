@@ -151,6 +151,19 @@ class STACVoxelKV(HeavyHittersKV):
         self._offset_voxel = [total] * self._L_eff
         self._search_recent_neighbors(slot_idx=self._L_eff - 1, dist_thres=2 * self._voxel_size_f)
 
+    @torch.no_grad()
+    def append_pointmap(self, world_points: torch.Tensor, world_points_conf: torch.Tensor, patch_size: int,
+                        conf_threshold: float = 1.0, special_tokens_size: int = 0):
+        """get_pointmap + append_positions of the reference's streaming loop in one call
+        (stream_session.py:213-256, aggregator.py:309-335): the chunk's world-point maps
+        [S,H,W,3] / confidences [S,H,W] go straight to voxel ids without intermediate tensors on
+        the host side.  Returns (pts3d [S,N,3], valid_mask [S,N]) like get_pointmap."""
+        from .pointmap import pointmap_to_positions
+        pts, mask = pointmap_to_positions(world_points, world_points_conf, patch_size, conf_threshold,
+                                          special_tokens_size)
+        self.append_positions(pts.view(-1, 3), mask.view(-1))
+        return pts, mask
+
     def _clear_retrieval_cache(self, slot_idx: int):
         dev = self.device
         self._offset_retrieval[slot_idx] = 0

@@ -147,3 +147,24 @@ def attention_inputs(name):
         b[rs.rand(c["H"], c["n_bias"]) < 0.25] = -np.inf
         bias[:, c["N"] - c["n_bias"]:] = b
     return q, k, v, bias
+
+
+# ---------------------------------------------------------------- point map -> patch points
+# "frame" is the production shape (518 x 392, 14-pixel patches, 5 special tokens per frame);
+# "ragged" is not a multiple of the patch (weights other than 1/4).
+POINTMAP = {
+    "frame": dict(S=2, H=392, W=518, patch=14, special=5, conf_threshold=1.0, seed=51),
+    "ragged": dict(S=3, H=45, W=61, patch=14, special=2, conf_threshold=1.5, seed=52),
+}
+
+
+def pointmap_inputs(name):
+    """world points f32 [S,H,W,3] (a smooth surface plus noise, metres) and confidence [S,H,W]."""
+    c = POINTMAP[name]
+    rs = np.random.RandomState(c["seed"])
+    S, H, W = c["S"], c["H"], c["W"]
+    yy, xx = np.meshgrid(np.linspace(-1, 1, H), np.linspace(-1, 1, W), indexing="ij")
+    depth = 3.0 + np.sin(2.0 * xx)[None] + 0.5 * np.cos(3.0 * yy)[None] + 0.3 * np.arange(S)[:, None, None]
+    pts = np.stack([xx[None] * depth, yy[None] * depth, depth], axis=-1) + rs.randn(S, H, W, 3) * 0.01
+    conf = 0.2 + 2.0 * rs.rand(S, 1, 1) * (0.5 + 0.5 * np.cos(4.0 * xx + yy)[None]) + rs.rand(S, H, W) * 1.2
+    return pts.astype(np.float32), conf.astype(np.float32)

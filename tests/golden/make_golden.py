@@ -180,6 +180,25 @@ def gen_attention():
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **out)
 
 
+def gen_pointmap(ref_path):
+    """StreamSession.get_pointmap (stream_session.py:213-256) called unbound with a stand-in for
+    `self` that carries only the patch size; CPU."""
+    import types
+    import torch
+    sys.path.insert(0, ref_path)
+    from stream_session import StreamSession
+    out = {}
+    for name, c in cases.POINTMAP.items():
+        wp, cf = cases.pointmap_inputs(name)
+        me = types.SimpleNamespace(model=types.SimpleNamespace(point_head=types.SimpleNamespace(patch_size=c["patch"])))
+        outputs = {"world_points": torch.from_numpy(wp)[None], "world_points_conf": torch.from_numpy(cf)[None]}
+        pts, mask = StreamSession.get_pointmap(me, outputs, conf_threshold=c["conf_threshold"],
+                                               special_tokens_size=c["special"])
+        out[f"{name}_pts"] = pts.numpy()
+        out[f"{name}_mask"] = mask.numpy()
+    np.savez_compressed(os.path.join(HERE, "pointmap.npz"), **out)
+
+
 if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     BinaryVoxel, VoxelKVMerger, STACVoxelKV = _import_reference(ref)
@@ -188,4 +207,5 @@ if __name__ == "__main__":
         gen_merger(BinaryVoxel, VoxelKVMerger, nm)
     gen_manager(STACVoxelKV)
     gen_attention()
+    gen_pointmap(ref)
     print("golden fixtures written to", HERE)

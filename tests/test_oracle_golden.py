@@ -143,3 +143,20 @@ def test_subsample_plan():
     assert subsample_plan(100, 0.25) == (100, 1, 1.0)
     assert subsample_plan(1041, 0.999) == (1024, 1, 1041 / 1024)
     assert subsample_plan(4164, 0.5) == (2048, 2, 4164 / 2048)
+
+
+@pytest.mark.parametrize("name", list(cases.POINTMAP))
+def test_pointmap(golden_dir, name):
+    """Patch points and masks against StreamSession.get_pointmap run on CPU: bit-identical at the
+    production frame size (all weights 1/4), one unit in the last place at a ragged size."""
+    from oracle.pointmap import pointmap_to_positions
+    g = _load(golden_dir, "pointmap.npz")
+    c = cases.POINTMAP[name]
+    wp, cf = cases.pointmap_inputs(name)
+    pts, mask = pointmap_to_positions(wp, cf, c["patch"], c["conf_threshold"], c["special"])
+    assert np.array_equal(mask, g[f"{name}_mask"])
+    if name == "frame":
+        assert np.array_equal(pts, g[f"{name}_pts"])
+    else:
+        np.testing.assert_allclose(pts, g[f"{name}_pts"], rtol=4e-6, atol=1e-7)
+    assert mask[:, :c["special"]].sum() == 0 and np.all(pts[:, :c["special"]] == 0)
