@@ -44,7 +44,7 @@ def test_append_pointmap_gives_the_voxel_ids_of_the_two_step_path():
     L, H, D = 1, 2, 64
     kv = STACVoxelKV(num_layers=L, num_heads=H, head_dim=D, token_per_frame=tpf, buffer_size=S + 3, chunk_size=S,
                      recent_size=1, pinned_idx=[0], hh_size=1, temperature=0.9, device=dev, dtype=torch.bfloat16,
-                     voxel_size=0.05, init_voxels=64, retrieval_size=1)
+                     voxel_size=0.05, init_voxels=64, voxel_buf_cap=8, voxel_piv_cap=4, retrieval_size=1)
     kv.reset()
     k = torch.zeros(1, H, S * tpf, D, dtype=torch.bfloat16, device=dev)
     kv.append_kv(k, k, 0)
