@@ -59,6 +59,21 @@ class HeavyHittersKV(KVManager):
         self._last_score_offset = [0] * L
         self._last_query_offset = [0] * L
 
+    def state_dict(self):
+        sd = super().state_dict()
+        T = max(self._offset_hot)
+        sd.update(scores=self._scores_hot[:, :, :T].cpu().clone(), counts=self._scores_hot_count[:, :, :T].cpu().clone(),
+                  last_score_offset=list(self._last_score_offset), last_query_offset=list(self._last_query_offset))
+        return sd
+
+    def load_state_dict(self, sd):
+        super().load_state_dict(sd)
+        T = sd["scores"].shape[2]
+        self._scores_hot[:, :, :T].copy_(sd["scores"])
+        self._scores_hot_count[:, :, :T].copy_(sd["counts"])
+        self._last_score_offset = list(sd["last_score_offset"])
+        self._last_query_offset = list(sd["last_query_offset"])
+
     def _bind_scores(self):
         self._scores_hot = self._sc[self._cur]
         self._scores_hot_count = self._cn[self._cur]

@@ -146,6 +146,47 @@ class KVManager:
         torch.cuda.synchronize(self.device)
         torch.cuda.empty_cache()
 
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self):
+        """Live contents of the hot cache (and of the host spill buffer) with their counters, on
+        the CPU.  The reference has no checkpointing; a stream restored with load_state_dict
+        continues with the same bits as the uninterrupted one."""
+        T = max(self._offset_hot)
+        Tc = max(self._offset_hot_cpu) if self.key_cache_hot_cpu is not None else 0
+        cpu = lambda t: t.cpu().clone()
+        return {
+            "format": 1, "class": type(self).__name__,
+            "shape": [self._L_eff, self.num_heads, self.head_dim, self.token_per_f, self.reserved_buffer_token_size],
+            "processed_frames": int(self._processed_frames), "offset_hot": list(self._offset_hot),
+            "key": cpu(self.key_cache_hot[:, :, :T]), "value": cpu(self.value_cache_hot[:, :, :T]),
+            "token_idx": cpu(self._token_indices_hot[:, :, :T]),
+            "use_cpu": bool(self.use_cpu), "offset_hot_cpu": list(self._offset_hot_cpu),
+            "key_cpu": self.key_cache_hot_cpu[:, :, :Tc].clone() if Tc else None,
+            "value_cpu": self.value_cache_hot_cpu[:, :, :Tc].clone() if Tc else None,
+        }
+
+    def load_state_dict(self, sd):
+        """Into a manager constructed with the same arguments (checked); resets it first."""
+        if sd.get("format") != 1 or sd.get("class") != type(self).__name__:
+            raise ValueError(f"state of {sd.get('class')} (format {sd.get('format')}) does not fit {type(self).__name__}")
+        shape = [self._L_eff, self.num_heads, self.head_dim, self.token_per_f, self.reserved_buffer_token_size]
+        if list(sd["shape"]) != shape:
+            raise ValueError(f"state was saved with [layers, heads, head_dim, tokens/frame, buffer tokens] = "
+                             f"{list(sd['shape'])}, this manager has {shape}")
+        self.reset()
+        T = sd["key"].shape[2]
+        self.key_cache_hot[:, :, :T].copy_(sd["key"])
+        self.value_cache_hot[:, :, :T].copy_(sd["value"])
+        self._token_indices_hot[:, :, :T].copy_(sd["token_idx"])
+        self._offset_hot = list(sd["offset_hot"])
+        self._processed_frames = int(sd["processed_frames"])
+        self.use_cpu = bool(sd["use_cpu"])
+        self._offset_hot_cpu = list(sd["offset_hot_cpu"])
+        if sd["key_cpu"] is not None:
+            Tc = sd["key_cpu"].shape[2]
+            self.key_cache_hot_cpu[:, :, :Tc].copy_(sd["key_cpu"])
+            self.value_cache_hot_cpu[:, :, :Tc].copy_(sd["value_cpu"])
+
     # ------------------------------------------------------------------ append
     def append_kv(self, key_states, value_states, layer_idx: int):
         """key_states, value_states: [B, H, T_new, D] with B == 1."""

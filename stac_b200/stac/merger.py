@@ -137,6 +137,56 @@ class VoxelKVMerger:
     def reset(self):
         pass
 
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self):
+        """Everything a later insert / retrieve depends on, cut to the used extents: row maps of
+        the used voxels, both pools up to their bump pointers, the free list, the carried-over
+        overflow list and the device counters."""
+        m = self._meta_host
+        V = int(self._voxel_offset)
+        top_b, n_free, top_p, n_over = m[META_BUF_TOP], m[META_BUF_FREE_LEN], m[_lib.META_PIV_TOP], m[META_OVER_COUNT]
+        cur = self._over[self._over_cur]
+        cpu = lambda t: t.cpu().clone()
+        return {
+            "voxel_alloc": int(self._voxel_alloc), "voxel_offset": V, "token_count": int(self._token_count),
+            "meta": cpu(self._meta), "over_max_head": int(self._over_max_head),
+            "buf_row_seg": cpu(self._buf_row_seg[:, :V]), "buf_row_cnt": cpu(self._buf_row_cnt[:, :V]),
+            "piv_row_seg": cpu(self._piv_row_seg[:, :V]), "piv_row_cnt": cpu(self._piv_row_cnt[:, :V]),
+            "buf_K": cpu(self._buf_K[:top_b]), "buf_V": cpu(self._buf_V[:top_b]), "buf_S": cpu(self._buf_S[:top_b]),
+            "buf_free": cpu(self._buf_free[:n_free]),
+            "piv_K": cpu(self._piv_K[:top_p]), "piv_V": cpu(self._piv_V[:top_p]), "piv_W": cpu(self._piv_W[:top_p]),
+            "piv_S": cpu(self._piv_S[:top_p]), "piv_C": cpu(self._piv_C[:top_p]),
+            "over": {f: cpu(cur[f][:n_over]) for f in ("K", "V", "S", "hv")} | {"start": cpu(cur["start"])},
+        }
+
+    def load_state_dict(self, sd):
+        """Into a freshly constructed merger of the same configuration."""
+        V = int(sd["voxel_offset"])
+        self._voxel_alloc = max(int(sd["voxel_alloc"]), self._voxel_alloc)
+        self._grow_rows(self._voxel_alloc)
+        self._voxel_offset = V
+        self._token_count = int(sd["token_count"])
+        for name in ("buf_row_seg", "buf_row_cnt", "piv_row_seg", "piv_row_cnt"):
+            getattr(self, "_" + name)[:, :V].copy_(sd[name])
+        top_b, n_free, top_p = sd["buf_K"].shape[0], sd["buf_free"].shape[0], sd["piv_K"].shape[0]
+        self._grow_buf(max(top_b, n_free, 1))
+        self._grow_piv(max(top_p, 1))
+        for name in ("buf_K", "buf_V", "buf_S"):
+            getattr(self, "_" + name)[:top_b].copy_(sd[name])
+        self._buf_free[:n_free].copy_(sd["buf_free"])
+        for name in ("piv_K", "piv_V", "piv_W", "piv_S", "piv_C"):
+            getattr(self, "_" + name)[:top_p].copy_(sd[name])
+        n_over = sd["over"]["S"].shape[0]
+        self._over_cap = max(n_over, 1)
+        self._over = [self._new_over(self._over_cap), self._new_over(self._over_cap)]
+        self._over_cur = 0
+        for f in ("K", "V", "S", "hv"):
+            self._over[0][f][:n_over].copy_(sd["over"][f])
+        self._over[0]["start"].copy_(sd["over"]["start"])
+        self._meta.copy_(sd["meta"])
+        self._meta_host = sd["meta"].tolist()
+        self._over_max_head = int(sd["over_max_head"])
+
     def update_voxel_zones(self, voxel_zones):
         """Morton zones only steer the reference's CUDA pivot allocator; nothing to do here."""
 

@@ -96,6 +96,49 @@ class STACVoxelKV(HeavyHittersKV):
         self._vstore = None
         return super().free()
 
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self):
+        """Hot cache, scores, voxel ids per token, the voxel table, the voxel memory and the
+        retrieved pivots that the next attention calls would read."""
+        sd = super().state_dict()
+        T = max(self._offset_voxel)
+        rec = None
+        if self._recent_voxel_ids is not None:
+            ids, count = self._recent_voxel_ids
+            n = int(count.item())
+            rec = ids[:n].cpu().clone()
+        sd.update(voxel_idx=self._token_voxel_indices[:, :, :T].cpu().clone(), offset_voxel=list(self._offset_voxel),
+                  recent_voxel_ids=rec, table=self._vm.state_dict(), memory=self._vstore.state_dict(),
+                  retrieved=None if self._ret is None else [t.cpu().clone() for t in self._ret],
+                  offset_retrieval=list(self._offset_retrieval),
+                  scores_retrieval=[t.cpu().clone() for t in self._scores_retrieval])
+        return sd
+
+    def load_state_dict(self, sd):
+        super().load_state_dict(sd)          # resets everything, then hot cache and scores
+        dev, L, H = self.device, self._L_eff, self.num_heads
+        T = sd["voxel_idx"].shape[2]
+        self._token_voxel_indices[:, :, :T].copy_(sd["voxel_idx"])
+        self._offset_voxel = list(sd["offset_voxel"])
+        self._vm.load_state_dict(sd["table"])
+        self._vstore.load_state_dict(sd["memory"])
+        self._recent_voxel_ids = None
+        if sd["recent_voxel_ids"] is not None:
+            ids = sd["recent_voxel_ids"].to(dev)
+            self._recent_voxel_ids = (ids, torch.tensor([ids.numel()], dtype=torch.int32, device=dev))
+        if sd["retrieved"] is not None:
+            K, V, M, B = (t.to(dev) for t in sd["retrieved"])
+            self._ret = (K, V, M, B)
+            for s in range(L):
+                Tm = int(sd["offset_retrieval"][s])
+                if Tm == 0:
+                    continue
+                self.key_cache_retrieval[s] = K[s * H:(s + 1) * H, :Tm]
+                self.value_cache_retrieval[s] = V[s * H:(s + 1) * H, :Tm]
+                self._bias_retrieval[s] = B[s * H:(s + 1) * H, :Tm]
+                self._offset_retrieval[s] = Tm
+        self._scores_retrieval = [t.to(dev) for t in sd["scores_retrieval"]]
+
     # ------------------------------------------------------------------ attention
     @torch.no_grad()
     def decode_sparse_attn(self, query_states: torch.Tensor, layer_idx: int) -> torch.Tensor:

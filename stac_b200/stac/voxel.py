@@ -62,6 +62,23 @@ class BinaryVoxel:
                                            ptr(self._hash_keys), ptr(self._hash_vals), self._hash_cap,
                                            stream_ptr()), "stac_voxel_rehash")
 
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self):
+        """The table is its key list (id = position); the hash table is rebuilt on load."""
+        return {"n": int(self._n), "table_keys": self._table_keys[: self._n].cpu()}
+
+    def load_state_dict(self, sd):
+        n = int(sd["n"])
+        self._alloc(self._init_capacity)
+        if n > self._cap:
+            self._grow(n)
+        self._table_keys[:n].copy_(sd["table_keys"])
+        self._n = n
+        self._n_dev.fill_(n)
+        check(_lib.lib().stac_voxel_rehash(ptr(self._table_keys), ptr(self._n_dev), self._cap,
+                                           ptr(self._hash_keys), ptr(self._hash_vals), self._hash_cap,
+                                           stream_ptr()), "stac_voxel_rehash")
+
     # ------------------------------------------------------------------ upsert
     def _upsert(self, points, ijk, mask, n):
         if n == 0:

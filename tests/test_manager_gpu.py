@@ -224,3 +224,73 @@ def test_cpu_spill_of_the_window_manager():
     assert mgr.get_offset_cpu() == [3 * tpf] * L
     with pytest.raises(RuntimeError, match="CPU buffer overflow"):
         append(1)
+
+
+def _drive(kv, c, steps, start=0, log=None):
+    """Steps [start, steps) of the seeded manager trace (column sums injected, retrieval on the
+    configured steps); appends the retrieved pivots of every retrieval to `log`."""
+    L = c["L"]
+    for step, (k, v, cs, pts, mask) in enumerate(cases.manager_inputs(c)):
+        if step < start:
+            continue
+        if step >= steps:
+            break
+        Tq = k.shape[2]
+        for l in range(L):
+            tk = torch.from_numpy(k[l]).to(torch.bfloat16)
+            tv = torch.from_numpy(v[l]).to(torch.bfloat16)
+            kv.append_kv(tk[None].to(DEV), tv[None].to(DEV), l)
+            T_live = kv._offset_hot[l]
+            kv._last_query_offset[l] = Tq
+            kv._update_scores(torch.from_numpy(cs[l][:, :T_live])[None, :, None, :].to(DEV), l)
+        kv.append_positions(torch.from_numpy(pts).to(DEV), torch.from_numpy(mask).to(DEV))
+        if step in c["retrieve_steps"]:
+            for l in range(L):
+                kv.retrieve_kv(l, return_buf=True)
+            if log is not None:
+                log.append((torch.stack(kv.key_cache_retrieval).float().cpu().numpy(),
+                            torch.stack(kv._bias_retrieval).cpu().numpy()))
+        kv.prune_kv()
+
+
+def _full_state(kv):
+    T = kv.get_offset()[0]
+    snap = kv._vstore.snapshot()
+    out = {"ti": kv._token_indices_hot[:, :, :T].cpu().numpy(), "vx": kv._token_voxel_indices[:, :, :T].cpu().numpy(),
+           "sc": kv._scores_hot[:, :, :T].cpu().numpy(), "cn": kv._scores_hot_count[:, :, :T].cpu().numpy(),
+           "k": kv.key_cache_hot[:, :, :T].float().cpu().numpy(), "v": kv.value_cache_hot[:, :, :T].float().cpu().numpy(),
+           "n_vox": np.array(kv._vm.get_voxel_num()), "keys": kv._vm.get_voxel_keys_1d().cpu().numpy()}
+    for key, val in snap.items():
+        out["mem_" + key] = np.asarray(val)
+    return out
+
+
+def test_checkpoint_resume_continues_with_the_same_bits(tmp_path):
+    """A stream saved after step 9 (between a retrieval and the next attention) and restored into a
+    new manager ends with exactly the state of the uninterrupted stream."""
+    from stac_b200.stac.checkpoint import load_state, save_state
+    c = cases.MANAGER_GPU
+    cut = 9
+    a_log, b_log = [], []
+    a = _make(c)
+    _drive(a, c, c["steps"], log=a_log)
+    want = _full_state(a)
+    b = _make(c)
+    _drive(b, c, cut, log=b_log)
+    path = str(tmp_path / "stream_state.pt")
+    save_state(b, path)
+    b.free()
+    r = _make(c)
+    load_state(r, path)
+    assert r._processed_frames == cut * c["chunk"]
+    _drive(r, c, c["steps"], start=cut, log=b_log)
+    r.check_status()
+    got = _full_state(r)
+    assert set(got) == set(want)
+    for key in want:
+        assert np.array_equal(got[key], want[key]), key
+    assert len(a_log) == len(b_log) and len(a_log) > 2
+    for (ka, ba), (kb, bb) in zip(a_log, b_log):
+        assert np.array_equal(ka, kb) and np.array_equal(ba, bb)
+    with pytest.raises(ValueError):
+        _make(c, buffer_size=c["buffer"] + 1).load_state_dict(torch.load(path, weights_only=False))
