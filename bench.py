@@ -189,7 +189,10 @@ class Stream:
         self.copy_stream = torch.cuda.Stream(device=device)
         self.ready = [None, None]
         self.done = [None, None]
-        self.out_host = torch.empty((1, Tq, H, D), dtype=torch.bfloat16).pin_memory()
+        # results land in pinned memory; the host consumes the result of step i while step i + 1 runs
+        self.out_host = [torch.empty((1, Tq, H, D), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        self.out_landed = [None, None]
+        self.out_checksum = 0.0
         self.chunk_idx = 0
         self.share_counts = False
         self.head_counts = None
@@ -206,15 +209,20 @@ class Stream:
         with torch.cuda.stream(self.copy_stream):
             if self.done[slot] is not None:
                 self.copy_stream.wait_event(self.done[slot])
-            for dst, src in zip(self.stage[slot], self.host[s]):
-                dst.copy_(src, non_blocking=True)
             self.pin_pts[slot].copy_(torch.from_numpy(pts))
             self.pin_mask[slot].copy_(torch.from_numpy(mask))
             self.stage_pts[slot][0].copy_(self.pin_pts[slot], non_blocking=True)
             self.stage_pts[slot][1].copy_(self.pin_mask[slot], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(self.copy_stream)
-            self.ready[slot] = ev
+            # layer by layer, one event each: layer l of the step starts as soon as its own q/k/v have
+            # landed, so even a step whose copies could not be issued ahead overlaps them with compute
+            events = []
+            for l in range(self.cfg["layers"]):
+                for dst, src in zip(self.stage[slot], self.host[s]):
+                    dst[l].copy_(src[l], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.copy_stream)
+                events.append(ev)
+            self.ready[slot] = events
 
     def step(self, pts, mask, host_io=False, time_kernels=False, next_inputs=None):
         torch, kv, c = self.torch, self.kv, self.cfg
@@ -227,7 +235,7 @@ class Stream:
             slot = self.chunk_idx & 1
             if self.ready[slot] is None:
                 self._prefetch(self.chunk_idx, pts, mask)
-            torch.cuda.current_stream().wait_event(self.ready[slot])
+            ready = self.ready[slot]
             q, k, v = self.stage[slot]
             pts_d, mask_d = self.stage_pts[slot]
             h2d = sum(t.numel() * 2 for t in self.host[s]) + pts.nbytes + mask.nbytes
@@ -238,6 +246,8 @@ class Stream:
             pts_d, mask_d = pts, mask  # already device tensors
         out = None
         for l in range(L):
+            if host_io:
+                torch.cuda.current_stream().wait_event(ready[l])
             kv.append_kv(k[l], v[l], l)
             if time_kernels:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -262,15 +272,33 @@ class Stream:
             e1.record()
             self.merge_events.append((e0, e1))
         if host_io:
-            self.out_host.copy_(out, non_blocking=True)
+            slot = self.chunk_idx & 1
+            self.out_host[slot].copy_(out, non_blocking=True)
             d2h += out.numel() * 2
             ev = torch.cuda.Event()
             ev.record()
-            self.done[self.chunk_idx & 1] = ev
-            self.ready[self.chunk_idx & 1] = None
-            torch.cuda.current_stream().synchronize()
+            self.done[slot] = ev
+            self.out_landed[slot] = ev
+            self.ready[slot] = None
+            # consume the previous step's result on the host (waits until its copy has landed);
+            # the result of the last step is consumed by finish_host_io()
+            prev = self.out_landed[1 - slot]
+            if prev is not None:
+                prev.synchronize()
+                self.out_checksum += float(self.out_host[1 - slot][0, 0, 0, 0])
+                self.out_landed[1 - slot] = None
         self.chunk_idx += 1
         self.h2d, self.d2h = h2d, d2h
+
+
+def finish_host_io(stream):
+    """Wait for and consume the results still in flight (end of a host-buffer phase)."""
+    for slot in (0, 1):
+        ev = stream.out_landed[slot]
+        if ev is not None:
+            ev.synchronize()
+            stream.out_checksum += float(stream.out_host[slot][0, 0, 0, 0])
+            stream.out_landed[slot] = None
 
 
 def max_over_ranks(ms, device=None):
@@ -341,6 +369,8 @@ def run_ours(args):
             else:
                 stream.step(pts_dev[i][0], pts_dev[i][1], time_kernels=timed)
         e1.record()
+        if host_io:
+            finish_host_io(stream)
         torch.cuda.synchronize()
         return max_over_ranks(e0.elapsed_time(e1), dev)
 

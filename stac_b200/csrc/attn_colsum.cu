@@ -29,8 +29,19 @@ constexpr int kBN = 128;
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 bf16
 constexpr int kFwdStages = 4;
 constexpr int kFwdThreads = 384;       // warpgroup 0: warp 0 TMA, warp 1 MMA (2, 3 idle); warpgroups 1, 2: softmax
-constexpr int kColStages = 4;
-constexpr int kColThreads = 512;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA issue), 1..3 exponent
+static_assert(128 * 40 + 256 * 232 <= kFwdThreads * ((65536 / kFwdThreads) / 8 * 8),
+              "exact forward kernel: setmaxnreg targets exceed the CTA's register allocation");
+constexpr int kColGroup = 3;           // key tiles per item = exponent warpgroups of the column-sum kernel
+constexpr int kColStages = kColGroup == 4 ? 3 : 4;
+constexpr int kColThreads = 128 + kColGroup * 128;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA issue), then exponent
+constexpr int kColCtlRegs = 56;
+constexpr int kColExpRegs = kColGroup == 4 ? 104 : 152;
+// setmaxnreg only moves registers inside the CTA's allocation, which is fixed at launch to
+// (registers per thread the launch bound allows, a multiple of 8) x threads.  A request beyond
+// what the control warpgroup released would wait forever.
+constexpr int kColLaunchRegs = (65536 / kColThreads) / 8 * 8;
+static_assert(128 * kColCtlRegs + (kColThreads - 128) * kColExpRegs <= kColThreads * kColLaunchRegs,
+              "column-sum kernel: setmaxnreg targets exceed the CTA's register allocation");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -408,6 +419,9 @@ constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 constexpr int kPartFloats = kBM * kD + 2 * kBM; // one partial result: O[128][64], row sums, row references
 constexpr int kFastMaxCtas = 160;               // partial-result slots are provided for this many CTAs
 constexpr int kFastMinSplitTiles = 8;           // shorter key ranges run one CTA per item
+constexpr int kFastCtlRegs = 56, kFastSoftmaxRegs = 152;   // setmaxnreg targets; must fit the launch allocation
+static_assert(128 * kFastCtlRegs + 384 * kFastSoftmaxRegs <= kFastThreads * ((65536 / kFastThreads) / 8 * 8),
+              "fast forward kernel: setmaxnreg targets exceed the CTA's register allocation");
 
 struct FastSmem {
   uint8_t q[2][kTileBytes];                     // query tile of the segment (parity)
@@ -545,7 +559,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t o_tmem = tmem + kFastRing * kFT;   // columns 448..511
 
   if (warp < 4) {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<kFastCtlRegs>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer: Q and K
       tma_prefetch_desc(&tm_q);
@@ -657,7 +671,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    setmaxnreg_inc<152>();
+    setmaxnreg_inc<kFastSoftmaxRegs>();
     const int g = (warp - 4) >> 2;
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
@@ -884,20 +898,20 @@ attn_fwd_combine_kernel(const FwdParams p, int n_tiles, int grid) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Column sums.  An item = (head, group of three 128-key tiles), head-major; its units are the
+// Column sums.  An item = (head, group of kColGroup 128-key tiles), head-major; its units are the
 // 128-row query tiles.  All units of the launch form one sequence that is cut into equal
 // contiguous ranges, one per persistent CTA, so every SM gets the same amount of work; an item
 // that straddles a cut is finished by two CTAs, each adding its partial sums to the zeroed
 // output with one atomic add per key (two addends onto zero give the same bits in either
 // order).  A query tile is scored in two halves of 64 rows: for each half the MMA warp
-// computes S^T = K Q^T for the three key tiles against the same query rows in shared memory
+// computes S^T = K Q^T for the key tiles of the group against the same query rows in shared memory
 // (N = 64, two 64-column TMEM buffers per key tile); warpgroup w owns key tile w, one key
-// (TMEM lane) per thread, so a thread's column sum never leaves its registers.  Three
-// exponent warps per scheduler keep the exp2 unit busier than two did.
+// (TMEM lane) per thread, so a thread's column sum never leaves its registers.  Three exponent
+// warps per scheduler keep the exp2 unit busier than two did (85 % against 75 % of the active
+// cycles); a fourth (kColGroup = 4, 104 registers per thread) measured the same as three.
 // lse2 holds the row log-sum-exp in the log2 domain; rows past M_sub read as +inf so that
 // padded query columns contribute exp2(-inf) = 0.
 // ---------------------------------------------------------------------------------------
-constexpr int kColGroup = 3;           // key tiles per item = exponent warpgroups
 constexpr int kColExpThreads = kColGroup * 128;
 constexpr int kColHalf = 64;           // query rows per score buffer
 
@@ -972,48 +986,65 @@ __device__ __forceinline__ void col_exp_chunk(const uint32_t (&s)[32], const flo
   }
 }
 
+// 16 scores of one key against 16 query rows: sum of exp2(score * c2 - lse2[row]).
+__device__ __forceinline__ void col_exp_chunk16(const uint32_t (&s)[32], const float4* nl4, float c2, float& a0,
+                                                float& a1, float& a2, float& a3) {
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) {
+    const float4 nl = nl4[q4];
+    a0 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 0]), c2, nl.x));
+    a1 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 1]), c2, nl.y));
+    a2 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 2]), c2, nl.z));
+    a3 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 3]), c2, nl.w));
+  }
+}
+
 // All half tiles of one item for one key (thread): returns the sum over the item's query rows.
 // kFast: the key's bias was taken out of the exponent (every lane of the warp agrees).
+// A 64-row half is read from TMEM in four pieces of 16 rows, the next piece always in flight
+// (the first piece of the next half included: its buffer does not depend on this warpgroup
+// finishing the current one).
 template <bool kFast>
 __device__ __forceinline__ float col_item_sum(ColSmem& sm, const ColParams& p, uint32_t t_base, const float* nl_item,
                                               int n_half, int& ui, float c2, float b2_in) {
-  uint32_t ra[32], rb[32];
+  uint32_t ra[32], rb[32];   // 16 registers of each are used
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  auto consume = [&](const uint32_t (&r)[32], const float* nl) {
+    if (kFast) {
+      col_exp_chunk16(r, reinterpret_cast<const float4*>(nl), c2, a0, a1, a2, a3);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 16; ++q) a0 += fast_exp2(fmaf(__uint_as_float(r[q]), c2, b2_in + nl[q]));
+    }
+  };
   // first half tile of the item: nothing is in flight yet
   {
     const int g = ui & 1, it = ui >> 1;
     mbar_wait(&sm.s_full[g], it & 1, p.err, DEV_TIMEOUT_MMA);
     tc_fence_after();
-    tmem_ld32(t_base + g * kColHalf, ra);
+    tmem_ld16(t_base + g * kColHalf, ra);
   }
   for (int hu = 0; hu < n_half; ++hu, ++ui) {
     const int g = ui & 1;
     const uint32_t s_addr = t_base + g * kColHalf;
     const float* nl = nl_item + hu * kColHalf;
-    const float4* nl4 = reinterpret_cast<const float4*>(nl);
-    tmem_ld_wait();                 // rows 0..31 of the half are in ra
-    tmem_ld32(s_addr + 32, rb);
-    if (kFast) {
-      col_exp_chunk(ra, nl4, c2, a0, a1, a2, a3);
-    } else {
-#pragma unroll
-      for (int q = 0; q < 32; ++q) a0 += fast_exp2(fmaf(__uint_as_float(ra[q]), c2, b2_in + nl[q]));
-    }
-    tmem_ld_wait();                 // rows 32..63 are in rb
-    // the next half tile was scored while this one was summed: fetch its first 32 rows
-    // (its buffer does not depend on this warpgroup finishing the current one)
+    tmem_ld_wait();
+    tmem_ld16(s_addr + 16, rb);
+    consume(ra, nl);
+    tmem_ld_wait();
+    tmem_ld16(s_addr + 32, ra);
+    consume(rb, nl + 16);
+    tmem_ld_wait();
+    tmem_ld16(s_addr + 48, rb);
+    consume(ra, nl + 32);
+    tmem_ld_wait();
     if (hu + 1 < n_half) {
       const int g2 = (ui + 1) & 1, it2 = (ui + 1) >> 1;
       mbar_wait(&sm.s_full[g2], it2 & 1, p.err, DEV_TIMEOUT_MMA);
       tc_fence_after();
-      tmem_ld32(t_base + g2 * kColHalf, ra);
+      tmem_ld16(t_base + g2 * kColHalf, ra);
     }
-    if (kFast) {
-      col_exp_chunk(rb, nl4 + 8, c2, a0, a1, a2, a3);
-    } else {
-#pragma unroll
-      for (int q = 0; q < 32; ++q) a0 += fast_exp2(fmaf(__uint_as_float(rb[q]), c2, b2_in + nl[32 + q]));
-    }
+    consume(rb, nl + 48);
     tc_fence_before();
     mbar_arrive(&sm.s_free[g]);
   }
@@ -1052,7 +1083,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tmem = sm.tmem_base;
 
   if (warp < 4) {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<kColCtlRegs>();
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------------ TMA producer
       tma_prefetch_desc(&tm_q);
@@ -1123,7 +1154,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ exponent warpgroups
-    setmaxnreg_inc<152>();
+    setmaxnreg_inc<kColExpRegs>();
     const int w = (warp - 4) >> 2;   // which key tile of the group
     const int wq = warp & 3;
     const int key = wq * 32 + lane;  // key inside the tile = TMEM lane
