@@ -38,7 +38,7 @@ CFG = dict(layers=24, heads=16, head_dim=64, tpf=1041, special=5, patch_h=37, pa
            temperature=0.9, prefill_chunks=40,
            # bounded voxel memory of BASELINE config 5: 2M slots per layer
            max_buffer_slots=2_000_000 * 24, max_pivot_slots=2_000_000 * 24)
-ATTN_TRAFFIC_BYTES_PER_CALL = 130.5e6
+ATTN_TRAFFIC_BYTES_PER_CALL = 153.7e6
 METRIC = "stac_hot_path_streaming_frames_per_sec"
 WORKLOAD = ("config4-hot-path: CausalVGGT+STAC stream shapes (24 layers x 16 heads x 64, 1041 tokens/frame, "
             "chunk 4, window 8, hh 2, pinned [0], retrieval 2 frames, bf16); backbone replaced by synthetic "
@@ -381,7 +381,9 @@ def run_ours(args):
     sampler.start()
     time.sleep(0.25)
     launches0 = stac_lib.kernel_launches()
+    torch.cuda.nvtx.range_push("timed_steps")      # lets a profiler pick exactly the timed steps
     ms_dev = run_phase(K, False, True)             # timed, device-resident inputs
+    torch.cuda.nvtx.range_pop()
     launches = stac_lib.kernel_launches() - launches0
     clocks = sampler.stop()
     run_phase(min(W, 3), True, False)              # warm the host path
@@ -425,8 +427,10 @@ def run_ours(args):
                      "frac": round(achieved / peak_tf, 4) if achieved else None, "peak_source": peak_src,
                      "flops_formula": "(4+2r)*H*M*N*D, r=1", "avg_ms_per_call": round(float(np.mean(att_ms)), 4),
                      # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one call at this
-                     # shape (M=4164, N=17697), one ncu capture: profiles/attention_traffic__stream_shape.md
-                     "traffic": ATTN_TRAFFIC_BYTES_PER_CALL, "traffic_unit": "bytes per call (fwd 85.2 MB + colsum 45.2 MB)"},
+                     # shape (M=4164, N=17700), one ncu capture:
+                     # profiles/attention_kernels__stream_shape_M4164_Lk17700.md
+                     "traffic": ATTN_TRAFFIC_BYTES_PER_CALL,
+                     "traffic_unit": "bytes per call (fwd 108.4 MB + colsum 45.3 MB; algorithmic 135 MB)"},
         "stages_ms_per_step": {"attention_24_layers": round(sum(att_ms) / K, 3),
                                "prune_merge_compact": round(sum(mrg_ms) / K, 3)},
         "pool": {"voxels": info["used_voxels"], "pivots": info["pivot_pool_used"],
