@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 CFG = dict(layers=24, heads=16, head_dim=64, tpf=1041, special=5, patch_h=37, patch_w=28, chunk=4, window=8,
            hh=2, pinned=[0], retrieval=2, voxel_size=0.05, init_voxels=4096, buf_cap=8, piv_cap=4,
            temperature=0.9, prefill_chunks=40,
-           # bounded voxel memory of BASELINE config 5: 2M slots per layer
+           # bounded voxel memory of the long-stream configuration: 2M slots per layer
            max_buffer_slots=2_000_000 * 24, max_pivot_slots=2_000_000 * 24)
 ATTN_TRAFFIC_BYTES_PER_CALL = 153.7e6
 METRIC = "stac_hot_path_streaming_frames_per_sec"
@@ -447,7 +447,7 @@ def run_ours(args):
 
 # ------------------------------------------------------------------------------------ microbenchmarks
 def run_microbench_attn(args):
-    """BASELINE config 2: bf16 q [1041,16,64] against Lk keys; prints one JSON line per run with
+    """Column-sum attention microbenchmark: bf16 q [1041,16,64] against Lk keys; prints one JSON line per run with
     TFLOP/s counted as (4+2r)*H*M*N*D.  Used for kernel profiling; not the headline line."""
     import torch
     from stac_b200 import ops

@@ -200,7 +200,9 @@ def gen_pointmap(ref_path):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python make_golden.py <path to a checkout of Rainzor/STAC>")
+    ref = sys.argv[1]
     BinaryVoxel, VoxelKVMerger, STACVoxelKV = _import_reference(ref)
     gen_voxel(BinaryVoxel)
     for nm in cases.MERGER:
