@@ -65,8 +65,9 @@ int stac_abi_version(void);
  *              retrieved keys; or NULL to skip the column-sum pass
  *   workspace  scratch of at least stac_attn_workspace_bytes(M, H) bytes, 256-byte aligned, contents
  *              need no initialisation: the per-row log-sum-exps passed from the forward to the
- *              column-sum pass, then ~11 MB for the partial results of query tiles whose keys are
- *              shared by two CTAs when the forward pass is cut evenly over the SMs
+ *              column-sum pass, a few flags and counters (cleared by the call), then ~11 MB for the
+ *              partial results of query tiles whose keys are shared by two CTAs when the forward
+ *              pass is cut evenly over the SMs
  *   subsample_ratio in (0,1]: the column sums use rows 0, s, 2s, ... as in
  *              attn-cuda/csrc/bindings.cpp:63-83 (exact at 1.0)
  * All pointers 16-byte aligned; D must be 64.

@@ -86,10 +86,9 @@ SIGNATURES = {
 
 # kernels launched by one call of each entry point (the upper figure where it depends on arguments);
 # used to report how many of this library's kernels ran in a timed region
-# (stac_attn_colsum: fast forward, combine, exact forward, column sums; the combine kernel is
-# left out when the call has fewer (head, query tile) items than the GPU has SMs)
+# (stac_attn_colsum: fast forward, exact forward, column sums)
 KERNELS_PER_CALL = {
-    "stac_attn_colsum": 4, "stac_attn_colsum_noalloc": 3, "stac_selftest_bounded_wait": 1,
+    "stac_attn_colsum": 3, "stac_attn_colsum_noalloc": 3, "stac_selftest_bounded_wait": 1,
     "stac_voxel_hash_clear": 1, "stac_voxel_rehash": 2, "stac_voxel_upsert": 3, "stac_voxel_neighbors": 2, "stac_pointmap_to_positions": 1,
     "stac_append_kv": 1, "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 16, "stac_retrieve": 2,
 }

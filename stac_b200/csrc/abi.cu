@@ -40,7 +40,7 @@ int stac_abi_version(void) { return 1; }
 size_t stac_attn_workspace_bytes(int M, int H) {
   if (M <= 0 || H <= 0) return 0;
   // row log-sum-exps (rounded up to 256 bytes), then the partial results of the split forward kernel
-  const size_t lse_bytes = (stac::attn_lse2_elems(M, H) * sizeof(float) + 255) & ~static_cast<size_t>(255);
+  const size_t lse_bytes = (stac::attn_lse2_elems_split(M, H) * sizeof(float) + 255) & ~static_cast<size_t>(255);
   return lse_bytes + stac::attn_part_elems() * sizeof(float);
 }
 
@@ -65,7 +65,7 @@ int stac_attn_colsum(const void* q, int64_t q_row_stride, const void* k_hot, con
   a.out = out; a.out_row_stride = out_row_stride;
   a.lse = lse; a.colsum = colsum; a.colsum_head_stride = colsum_head_stride;
   a.M = M; a.H = H; a.D = D; a.scale = scale; a.subsample_ratio = subsample_ratio;
-  const size_t lse_bytes = (stac::attn_lse2_elems(M, H) * sizeof(float) + 255) & ~static_cast<size_t>(255);
+  const size_t lse_bytes = (stac::attn_lse2_elems_split(M, H) * sizeof(float) + 255) & ~static_cast<size_t>(255);
   float* part = reinterpret_cast<float*>(static_cast<char*>(workspace) + lse_bytes);
   return stac::attn_colsum_launch(a, static_cast<float*>(workspace), part, dev_status,
                                   reinterpret_cast<cudaStream_t>(stream));

@@ -82,6 +82,11 @@ struct FwdParams {
   int n_q_tiles, n_items;
   int split;                 // 1: the (item, key tile) units are cut evenly over the grid
   float* part;               // split == 1: two partial-result slots per CTA
+  int* part_count;           // split == 1: one arrival counter per cut between CTA c and c + 1, zero on entry
+  // column sums that the column-sum kernel will accumulate with atomic adds: cleared here
+  float* zero_colsum;        // [H, zero_stride], entries [0, zero_width) of every head; or nullptr
+  long long zero_stride;
+  int zero_width;
 };
 
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
@@ -401,8 +406,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // CTA per SM and cuts that unit sequence into equal contiguous ranges (no partly filled last
 // wave); a CTA walks its range segment by segment, a segment being a run of key tiles of one
 // item.  An item on a cut is computed in two parts by two CTAs, each with its own row
-// references; the parts (unnormalised accumulator, row sums, references) go to a workspace and
-// attn_fwd_combine_kernel joins them.  Barrier phases, the score ring and the K/V rings run on
+// references; the parts (unnormalised accumulator, row sums, references) go to a workspace, each
+// CTA counts its arrival at the cut and the one that arrives second joins the two parts (plain
+// split-softmax algebra, operands in a fixed order: same bits whichever CTA does it).  Barrier phases, the score ring and the K/V rings run on
 // across segments; the query tile, the row references and the partial row sums are double
 // buffered by segment parity, and so are the barriers that several warpgroups arrive on per
 // segment: a warpgroup without a tile in a short first or last segment runs one segment ahead,
@@ -444,6 +450,7 @@ struct FastSmem {
   uint64_t o_done;               // all P V MMAs of the segment are complete
   uint64_t o_free;               // the segment's accumulator has been read out of TMEM
   uint32_t tmem_base;
+  int join_flag;                 // arrival count seen at a cut (1: the other part is complete)
 };
 
 // The (item, key tile) units of one CTA, walked segment by segment: a segment is a run of key
@@ -557,6 +564,16 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t o_tmem = tmem + kFastRing * kFT;   // columns 448..511
+
+  if (p.zero_colsum != nullptr) {
+    // a slice of the column-sum output per CTA (the next kernel adds partial sums onto zeros)
+    const long long total = static_cast<long long>(p.H) * p.zero_width;
+    const long long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    for (long long e = lo + threadIdx.x; e < hi; e += kFastThreads) {
+      const long long hh = e / p.zero_width;
+      p.zero_colsum[hh * p.zero_stride + (e - hh * p.zero_width)] = 0.f;
+    }
+  }
 
   if (warp < 4) {
     setmaxnreg_dec<kFastCtlRegs>();
@@ -830,8 +847,10 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         } else {
           // part of an item: unnormalised accumulator, row sum and row reference go to this
           // CTA's slot (slot 1: the item starts here and ends in the next CTA; slot 0: it began
-          // in the previous CTA); attn_fwd_combine_kernel joins the two parts
-          float* slot = p.part + static_cast<size_t>(2 * blockIdx.x + (t0 == 0 ? 1 : 0)) * kPartFloats;
+          // in the previous CTA).  Whichever of the two CTAs gets there second joins the parts.
+          const bool first_part = t0 == 0;
+          const int cut = first_part ? blockIdx.x : blockIdx.x - 1;   // between CTA cut and cut + 1
+          float* slot = p.part + static_cast<size_t>(2 * blockIdx.x + (first_part ? 1 : 0)) * kPartFloats;
           float4* orow = reinterpret_cast<float4*>(slot + row * kD);
 #pragma unroll
           for (int q4 = 0; q4 < 8; ++q4)
@@ -843,6 +862,47 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                        __uint_as_float(rb[q4 * 4 + 2]), __uint_as_float(rb[q4 * 4 + 3]));
           slot[kBM * kD + row] = l;
           slot[kBM * kD + kBM + row] = m_ref;
+          __threadfence();                       // this thread's part is visible device-wide ...
+          named_bar_sync(4, 128);                // ... and so is every other row's
+          if (row == 0) sm.join_flag = atomicAdd(p.part_count + cut, 1);
+          named_bar_sync(4, 128);
+          if (sm.join_flag == 1) {
+            // the other CTA's part was complete before its counter increment, which came first
+            __threadfence();
+            const float* other = p.part + static_cast<size_t>(first_part ? 2 * (cut + 1) : 2 * cut + 1) * kPartFloats;
+            const float lo_ = __ldcg(other + kBM * kD + row), mo_ = __ldcg(other + kBM * kD + kBM + row);
+            // a = the part with the item's first tiles, b = the part with its last ones
+            const float la = first_part ? l : lo_, ma = first_part ? m_ref : mo_;
+            const float lb = first_part ? lo_ : l, mb = first_part ? mo_ : m_ref;
+            const float m = fmaxf(ma, mb);
+            const float wa = exp2f(ma - m), wb = exp2f(mb - m);
+            // explicit operation order: the same bits whichever of the two CTAs computes the join
+            const float lsum2 = __fmaf_rn(la, wa, __fmul_rn(lb, wb));
+            const float inv = lsum2 > 0.f ? 1.f / lsum2 : 0.f;
+            if (mrow < p.M) {
+              const float4* orow_o = reinterpret_cast<const float4*>(other + row * kD);
+              __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
+              auto join = [&](uint32_t own, float oth) {
+                const float x = __uint_as_float(own);
+                const float va = first_part ? x : oth, vb = first_part ? oth : x;
+                return __fmul_rn(__fmaf_rn(va, wa, __fmul_rn(vb, wb)), inv);
+              };
+#pragma unroll
+              for (int q8 = 0; q8 < 8; ++q8) {
+                const float4 o0 = __ldcg(orow_o + 2 * q8), o1 = __ldcg(orow_o + 2 * q8 + 1);
+                const uint32_t* r8 = q8 < 4 ? &ra[q8 * 8] : &rb[(q8 - 4) * 8];
+                uint4 val;
+                val.x = pack_bf16x2(join(r8[0], o0.x), join(r8[1], o0.y));
+                val.y = pack_bf16x2(join(r8[2], o0.z), join(r8[3], o0.w));
+                val.z = pack_bf16x2(join(r8[4], o1.x), join(r8[5], o1.y));
+                val.w = pack_bf16x2(join(r8[6], o1.z), join(r8[7], o1.w));
+                *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
+              }
+              const float l2 = m + log2f(lsum2);
+              if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
+              p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
+            }
+          }
         }
       }
       c_base += len;
@@ -855,46 +915,6 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
-}
-
-// Joins the two parts of every item that straddles a cut between CTA c and CTA c + 1 of the
-// split fast kernel: block c, one thread per query row.  Plain split-softmax algebra in a fixed
-// order, so the result does not depend on timing.
-__global__ void __launch_bounds__(kBM)
-attn_fwd_combine_kernel(const FwdParams p, int n_tiles, int grid) {
-  const int c = blockIdx.x;
-  const long long total = static_cast<long long>(p.n_items) * n_tiles;
-  const long long cut = total * (c + 1) / grid;      // first unit of CTA c + 1
-  if (cut % n_tiles == 0) return;                    // the cut falls between two items
-  const int item = static_cast<int>(cut / n_tiles);
-  const int h = item / p.n_q_tiles, m_tile = item - h * p.n_q_tiles;
-  const int row = threadIdx.x;
-  const int mrow = m_tile * kBM + row;
-  if (mrow >= p.M) return;
-  const float* a = p.part + static_cast<size_t>(2 * c + 1) * kPartFloats;
-  const float* b = p.part + static_cast<size_t>(2 * (c + 1)) * kPartFloats;
-  const float la = a[kBM * kD + row], ma = a[kBM * kD + kBM + row];
-  const float lb = b[kBM * kD + row], mb = b[kBM * kD + kBM + row];
-  const float m = fmaxf(ma, mb);
-  const float wa = exp2f(ma - m), wb = exp2f(mb - m);
-  const float l = la * wa + lb * wb;
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  const float4* oa = reinterpret_cast<const float4*>(a + row * kD);
-  const float4* ob = reinterpret_cast<const float4*>(b + row * kD);
-  __nv_bfloat16* dst = p.out + static_cast<long long>(mrow) * p.out_row_stride + h * kD;
-#pragma unroll
-  for (int q8 = 0; q8 < 8; ++q8) {
-    const float4 a0 = oa[2 * q8], a1 = oa[2 * q8 + 1], b0 = ob[2 * q8], b1 = ob[2 * q8 + 1];
-    uint4 val;
-    val.x = pack_bf16x2((a0.x * wa + b0.x * wb) * inv, (a0.y * wa + b0.y * wb) * inv);
-    val.y = pack_bf16x2((a0.z * wa + b0.z * wb) * inv, (a0.w * wa + b0.w * wb) * inv);
-    val.z = pack_bf16x2((a1.x * wa + b1.x * wb) * inv, (a1.y * wa + b1.y * wb) * inv);
-    val.w = pack_bf16x2((a1.z * wa + b1.z * wb) * inv, (a1.w * wa + b1.w * wb) * inv);
-    *reinterpret_cast<uint4*>(dst + q8 * 8) = val;
-  }
-  const float l2 = m + log2f(l);
-  if (p.lse != nullptr) p.lse[static_cast<long long>(h) * p.M + mrow] = l2 * kLn2;
-  p.lse2[static_cast<long long>(h) * p.lse2_stride + mrow] = l2;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1269,7 +1289,9 @@ void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* cor
 }
 
 // row log-sum-exps [H, M] followed by the fallback flag (64 floats of padding keep it aligned)
+// fallback flag and the arrival counters of the split forward kernel follow the [H, M] values
 size_t attn_lse2_elems(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 64; }
+size_t attn_lse2_elems_split(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 256; }
 
 // partial results of the split forward kernel: two slots per CTA
 size_t attn_part_elems() { return static_cast<size_t>(2) * kFastMaxCtas * kPartFloats; }
@@ -1369,12 +1391,18 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   const int n_tiles_f = (a.T_hot + kFT - 1) / kFT + (a.T_ret + kFT - 1) / kFT;
   fp.split = (part != nullptr && fp.n_items >= n_sm && n_sm <= kFastMaxCtas && n_tiles_f >= kFastMinSplitTiles) ? 1 : 0;
   fp.part = part;
+  fp.part_count = fp.fallback + 1;      // only used (and only present in the workspace) when split
   const int grid_fast = fp.split ? n_sm : fp.n_items;
-  if (cudaMemsetAsync(fp.fallback, 0, sizeof(int), stream) != cudaSuccess) return STAC_ERR_CUDA;
+  if (cudaMemsetAsync(fp.fallback, 0, sizeof(int) * (fp.split ? 1 + kFastMaxCtas : 1), stream) != cudaSuccess)
+    return STAC_ERR_CUDA;
+  // the column-sum kernel adds partial sums with atomics when its own units are cut evenly over
+  // the SMs (same rule as below): the forward kernel clears the output for it
+  const bool col_split = a.colsum != nullptr &&
+                         ((fp.n_hot_tiles + fp.n_ret_tiles + kColGroup - 1) / kColGroup) * a.H >= n_sm;
+  fp.zero_colsum = col_split ? a.colsum : nullptr;
+  fp.zero_stride = a.colsum_head_stride;
+  fp.zero_width = a.T_hot + a.T_ret;
   attn_fwd_fast_kernel<<<grid_fast, kFastThreads, fast_smem, stream>>>(tm_q, tf_kh, tf_vh, tf_kr, tf_vr, fp);
-  if (fp.split) {
-    attn_fwd_combine_kernel<<<grid_fast - 1, kBM, 0, stream>>>(fp, n_tiles_f, grid_fast);
-  }
   attn_fwd_kernel<<<grid_f, kFwdThreads, fwd_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
   if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
 
@@ -1393,12 +1421,8 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
     cp.err = err;
     // enough items: cut the units evenly over one CTA per SM (an item is then shared by at most
     // two CTAs, which add their partial sums onto zeros); else one item per CTA
-    cp.split = cp.n_items >= n_sm ? 1 : 0;
+    cp.split = cp.n_items >= n_sm ? 1 : 0;      // then the forward kernel has cleared a.colsum
     const int grid_c = cp.split ? n_sm : cp.n_items;
-    if (cp.split && cudaMemset2DAsync(a.colsum, static_cast<size_t>(a.colsum_head_stride) * sizeof(float), 0,
-                                      static_cast<size_t>(a.T_hot + a.T_ret) * sizeof(float), a.H, stream) !=
-                        cudaSuccess)
-      return STAC_ERR_CUDA;
     attn_colsum_kernel<<<grid_c, kColThreads, col_smem, stream>>>(tm_qs, tm_kh, tm_kr, cp);
     if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
   }

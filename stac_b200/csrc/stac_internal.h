@@ -36,6 +36,7 @@ struct AttnArgs {
 
 void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* correction);
 size_t attn_lse2_elems(int M, int H);
+size_t attn_lse2_elems_split(int M, int H);
 size_t attn_part_elems();
 // `part`: attn_part_elems() floats for the split forward kernel, or nullptr (one CTA per item then)
 int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cudaStream_t stream);
