@@ -131,7 +131,8 @@ int stac_pointmap_to_positions(const float* world_points, const float* conf, int
 
 /* Ascending unique ids of the existing voxels inside the Chebyshev cube of `radius_cells`
  * around the voxels of `token_voxel_ids` (negative entries ignored); with all_ids != 0 every id
- * in the table instead.  flags u8 [table_cap] must be zero on entry and is zero on exit;
+ * in the table instead.  flags u8 [table_cap] (16-byte aligned, table_cap a multiple of 16) must
+ * be zero on entry and is zero on exit;
  * out_ids i32 [table_cap], *out_count i32 on the device. */
 int stac_voxel_neighbors(const int* token_voxel_ids, int n_tokens, int radius_cells, int all_ids,
                          const int64_t* table_keys, const int* n_voxels, int table_cap,

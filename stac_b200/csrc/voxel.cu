@@ -204,7 +204,9 @@ __global__ void neighbor_flag_kernel(const int* __restrict__ token_vx, int n_tok
   if (nb >= 0) flags[nb] = 1;
 }
 
-// Single CTA: ascending list of flagged ids (or of all ids), flags cleared on the way.
+// Single CTA: ascending list of flagged ids (or of all ids), flags cleared on the way.  Every
+// thread takes 16 consecutive flags per round (one 16-byte load; the flag array is as long as the
+// table capacity, a multiple of 16), so a table of 200 k voxels takes 13 rounds.
 __global__ void __launch_bounds__(1024, 1)
 compact_flags_kernel(unsigned char* __restrict__ flags, const int* __restrict__ n_voxels, int all_ids,
                      int* __restrict__ out_ids, int* __restrict__ out_count) {
@@ -214,13 +216,23 @@ compact_flags_kernel(unsigned char* __restrict__ flags, const int* __restrict__ 
   if (threadIdx.x == 0) carry = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int base = 0; base < n; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    int f = 0;
-    if (i < n) {
-      f = all_ids ? 1 : flags[i];
-      if (f) flags[i] = 0;
+  constexpr int kPer = 16;
+  for (int base = 0; base < n; base += blockDim.x * kPer) {
+    const int i0 = base + threadIdx.x * kPer;
+    unsigned int w[4] = {0u, 0u, 0u, 0u};
+    if (i0 < n) {
+      if (all_ids) {
+        w[0] = w[1] = w[2] = w[3] = 0x01010101u;
+      } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(flags + i0);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+        if (v.x | v.y | v.z | v.w) *reinterpret_cast<uint4*>(flags + i0) = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
+    int f = 0;   // flagged ids among this thread's 16 (ids >= n are never flagged, but all_ids fills them)
+#pragma unroll
+    for (int k = 0; k < kPer; ++k)
+      if (((w[k >> 2] >> ((k & 3) * 8)) & 0xffu) != 0u && i0 + k < n) ++f;
     int incl = f;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -230,16 +242,19 @@ compact_flags_kernel(unsigned char* __restrict__ flags, const int* __restrict__ 
     if (lane == 31) warp_sums[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      int w = warp_sums[lane];
+      int ws = warp_sums[lane];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += t;
+        const int t = __shfl_up_sync(0xffffffffu, ws, o);
+        if (lane >= o) ws += t;
       }
-      warp_sums[lane] = w;
+      warp_sums[lane] = ws;
     }
     __syncthreads();
-    if (f) out_ids[carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - 1] = i;
+    int pos = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - f;
+#pragma unroll
+    for (int k = 0; k < kPer; ++k)
+      if (((w[k >> 2] >> ((k & 3) * 8)) & 0xffu) != 0u && i0 + k < n) out_ids[pos++] = i0 + k;
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) carry = carry + warp_sums[31];
     __syncthreads();
@@ -399,6 +414,8 @@ int stac_voxel_neighbors(const int* token_voxel_ids, int n_tokens, int radius_ce
       flags == nullptr || out_ids == nullptr || out_count == nullptr || radius_cells < 0 || radius_cells > 8 ||
       table_cap <= 0)
     return STAC_ERR_BAD_ARG;
+  // the flags are read 16 at a time
+  if ((table_cap % 16) != 0 || (reinterpret_cast<uintptr_t>(flags) % 16) != 0) return STAC_ERR_BAD_ARG;
   if (!stac::is_pow2(hash_cap) || hash_cap > (1ll << 30)) return STAC_ERR_BAD_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (!all_ids && n_tokens > 0) {

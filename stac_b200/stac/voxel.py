@@ -30,7 +30,7 @@ class BinaryVoxel:
 
     def _alloc(self, cap):
         dev = self.device
-        self._cap = int(cap)
+        self._cap = max(16, (int(cap) + 15) // 16 * 16)   # the flag array is scanned 16 bytes at a time
         self._hash_cap = _pow2_at_least(4 * self._cap)
         self._table_keys = torch.zeros(self._cap, dtype=torch.int64, device=dev)
         self._hash_keys = torch.empty(self._hash_cap, dtype=torch.int64, device=dev)
