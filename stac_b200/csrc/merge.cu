@@ -1117,13 +1117,11 @@ __global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p)
 
 // Freed ids are appended after the part of the free list that was not handed out.
 __global__ void finalize_kernel(const MergeParams p) {
-  const int any = p.plan[kPlanAnyValid];
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (any && p.plan[kPlanAbort] == 0) {
-    const int n_freed = p.plan[kPlanTotalFull] * p.B;
-    const int base = p.plan[kPlanFreeLen] - p.plan[kPlanK];
-    if (i < n_freed) p.buf_free[base + i] = p.free_stage[i];
-  }
+  if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
+  const int n_freed = p.plan[kPlanTotalFull] * p.B;
+  const int base = p.plan[kPlanFreeLen] - p.plan[kPlanK];
+  const int stride = gridDim.x * blockDim.x;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_freed; i += stride) p.buf_free[base + i] = p.free_stage[i];
 }
 
 // No valid evicted token in the whole call: the reference returns before touching the
@@ -1196,8 +1194,7 @@ int launch_merge(MergeParams& mp, cudaStream_t st) {
   dim3 grid_tok(static_cast<unsigned>((static_cast<long long>(mp.ncap) * 2 * vec + 255) / 256), mp.heads);
   tokens_place_kernel<<<grid_tok, 256, 0, st>>>(mp, vec, static_cast<int>(sizeof(T)));
   rows_phase_b2_kernel<T, 2><<<148 * 8, 128, 0, st>>>(mp);
-  const int fin_blocks = (mp.buf_cap + 255) / 256;
-  finalize_kernel<<<fin_blocks, 256, 0, st>>>(mp);
+  finalize_kernel<<<148 * 4, 256, 0, st>>>(mp);   // grid-stride over the freed ids (known on the device only)
   carry_overflow_kernel<T><<<148, 256, 0, st>>>(mp);
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
