@@ -294,3 +294,51 @@ def test_checkpoint_resume_continues_with_the_same_bits(tmp_path):
         assert np.array_equal(ka, kb) and np.array_equal(ba, bb)
     with pytest.raises(ValueError):
         _make(c, buffer_size=c["buffer"] + 1).load_state_dict(torch.load(path, weights_only=False))
+
+
+def test_long_stream_with_bounded_voxel_memory():
+    """400 frames through a narrow manager (2 layers x 4 heads) with real attention every step and
+    voxel-memory pools far smaller than the stream needs: no device error, the pools stay inside
+    their bounds, rows are trimmed and retrieval returns pivots."""
+    from stac_b200.stac import STACVoxelKV
+    import bench
+    dev = torch.device(DEV)
+    L, H, D, tpf, chunk = 2, 4, 64, 1041, 4
+    max_buf, max_piv = 1_000_000, 100_000
+    kv = STACVoxelKV(num_layers=L, num_heads=H, head_dim=D, token_per_frame=tpf, buffer_size=chunk + 1 + 4 + 1,
+                     chunk_size=chunk, recent_size=4, pinned_idx=[0], hh_size=1, temperature=0.9, device=dev,
+                     dtype=torch.bfloat16, voxel_size=0.05, init_voxels=4096, voxel_buf_cap=8, voxel_piv_cap=4,
+                     retrieval_size=1, max_buffer_slots=max_buf, max_pivot_slots=max_piv)
+    kv.reset()
+    n_chunks = 100
+    pts = bench.synth_points(n_chunks, seed=3)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    Tq = chunk * tpf
+    q = (torch.randn(L, 1, Tq, H, D, generator=g) / 2).to(torch.bfloat16).to(dev)
+    k = (torch.randn(L, 1, H, Tq, D, generator=g) / 2).to(torch.bfloat16).to(dev)
+    v = (torch.randn(L, 1, H, Tq, D, generator=g) / 8).to(torch.bfloat16).to(dev)
+    valid_retrieved = 0
+    for i in range(n_chunks):
+        for l in range(L):
+            kv.append_kv(k[l].roll(i, dims=2), v[l].roll(i, dims=2), l)
+            out = kv.decode_sparse_attn(q[l], l)
+        kv.append_positions(torch.from_numpy(pts[i][0]).to(dev), torch.from_numpy(pts[i][1]).to(dev))
+        if bench.retrieval_due(i):
+            for l in range(L):
+                kv.retrieve_kv(l, return_buf=True)
+            valid_retrieved = max(valid_retrieved, int(torch.isfinite(torch.stack(kv._bias_retrieval)).sum()))
+        kv.prune_kv()
+    kv.check_status()
+    info = kv.get_merger_info()
+    assert info["buffer_pool_used"] <= max_buf and info["pivot_pool_used"] <= max_piv
+    assert info["dropped_tokens"] > 0 and info["pivot_pool_used"] > 0
+    assert info["used_voxels"] > 10_000
+    assert bool(torch.isfinite(out.float()).all())
+    R = kv.retrieval_token_size
+    assert kv.get_retrieval_size() == [R] * L
+    # (once the pools are full, rows of new voxels are the first to be trimmed, so late retrievals
+    # around the newest frames may find no pivot at all; earlier ones must have)
+    assert bool(torch.isfinite(torch.stack(kv.key_cache_retrieval).float()).all()) and valid_retrieved > 0
+    # the pools themselves never grow past their bounds (the row maps grow with the voxel count)
+    assert kv._vstore._buf_cap <= max_buf and kv._vstore._piv_cap <= max_piv
+    kv.free()
