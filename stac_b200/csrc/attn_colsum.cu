@@ -34,6 +34,10 @@ static_assert(128 * 40 + 256 * 232 <= kFwdThreads * ((65536 / kFwdThreads) / 8 *
 constexpr int kColGroup = 3;           // key tiles per item = exponent warpgroups of the column-sum kernel
 constexpr int kColStages = kColGroup == 4 ? 3 : 4;
 constexpr int kColThreads = 128 + kColGroup * 128;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA issue), then exponent
+#ifndef STAC_COL_POLY_MASK
+#define STAC_COL_POLY_MASK 0x8888
+#endif
+constexpr unsigned kColPolyMask = STAC_COL_POLY_MASK;   // which of 16 consecutive exponentials of the column-sum kernel run on the FMA pipes
 constexpr int kColCtlRegs = 56;
 constexpr int kColExpRegs = kColGroup == 4 ? 104 : 152;
 // setmaxnreg only moves registers inside the CTA's allocation, which is fixed at launch to
@@ -425,6 +429,10 @@ constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 constexpr int kPartFloats = kBM * kD + 2 * kBM; // one partial result: O[128][64], row sums, row references
 constexpr int kFastMaxCtas = 160;               // partial-result slots are provided for this many CTAs
 constexpr int kFastMinSplitTiles = 8;           // shorter key ranges run one CTA per item
+#ifndef STAC_FAST_POLY_MASK
+#define STAC_FAST_POLY_MASK 0x80808080u
+#endif
+constexpr unsigned kFastPolyMask = STAC_FAST_POLY_MASK;   // which of 32 consecutive exponentials run on the FMA pipes
 constexpr int kFastCtlRegs = 56, kFastSoftmaxRegs = 152;   // setmaxnreg targets; must fit the launch allocation
 static_assert(128 * kFastCtlRegs + 384 * kFastSoftmaxRegs <= kFastThreads * ((65536 / kFastThreads) / 8 * 8),
               "fast forward kernel: setmaxnreg targets exceed the CTA's register allocation");
@@ -482,28 +490,34 @@ struct FwdWalk {
   }
 };
 
-// kN scores -> kN probabilities relative to the row reference, packed as bf16 pairs.
-template <bool kBias, int kN>
+// kN scores -> kN probabilities relative to the row reference, packed as bf16 pairs.  The
+// elements whose bit is set in kFastPolyMask take their exponential on the FMA pipes (cubic,
+// 8.6e-5 relative, far below the bf16 rounding of P) to relieve the exponential unit.
+template <int kE>
+__device__ __forceinline__ float fast_exp_one(float x) {
+  return ((kFastPolyMask >> (kE & 31)) & 1u) ? poly_exp2(x) : fast_exp2(x);
+}
+template <bool kBias, int kN, int kI = 0>
 __device__ __forceinline__ void fast_exp_chunk(const uint32_t (&s)[32], uint32_t (&pk)[16], const float* bias2,
                                                float c2, float m_ref, float& l0, float& l1) {
-#pragma unroll
-  for (int i = 0; i < kN; i += 4) {
+  if constexpr (kI < kN) {
     float e0, e1, e2, e3;
     if (kBias) {
-      e0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), c2, bias2[i + 0]) - m_ref);
-      e1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c2, bias2[i + 1]) - m_ref);
-      e2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c2, bias2[i + 2]) - m_ref);
-      e3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c2, bias2[i + 3]) - m_ref);
+      e0 = fast_exp_one<kI + 0>(fmaf(__uint_as_float(s[kI + 0]), c2, bias2[kI + 0]) - m_ref);
+      e1 = fast_exp_one<kI + 1>(fmaf(__uint_as_float(s[kI + 1]), c2, bias2[kI + 1]) - m_ref);
+      e2 = fast_exp_one<kI + 2>(fmaf(__uint_as_float(s[kI + 2]), c2, bias2[kI + 2]) - m_ref);
+      e3 = fast_exp_one<kI + 3>(fmaf(__uint_as_float(s[kI + 3]), c2, bias2[kI + 3]) - m_ref);
     } else {
-      e0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), c2, -m_ref));
-      e1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), c2, -m_ref));
-      e2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), c2, -m_ref));
-      e3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), c2, -m_ref));
+      e0 = fast_exp_one<kI + 0>(fmaf(__uint_as_float(s[kI + 0]), c2, -m_ref));
+      e1 = fast_exp_one<kI + 1>(fmaf(__uint_as_float(s[kI + 1]), c2, -m_ref));
+      e2 = fast_exp_one<kI + 2>(fmaf(__uint_as_float(s[kI + 2]), c2, -m_ref));
+      e3 = fast_exp_one<kI + 3>(fmaf(__uint_as_float(s[kI + 3]), c2, -m_ref));
     }
     l0 += e0 + e1;
     l1 += e2 + e3;
-    pk[i / 2] = pack_bf16x2(e0, e1);
-    pk[i / 2 + 1] = pack_bf16x2(e2, e3);
+    pk[kI / 2] = pack_bf16x2(e0, e1);
+    pk[kI / 2 + 1] = pack_bf16x2(e2, e3);
+    fast_exp_chunk<kBias, kN, kI + 4>(s, pk, bias2, c2, m_ref, l0, l1);
   }
 }
 
@@ -1006,17 +1020,33 @@ __device__ __forceinline__ void col_exp_chunk(const uint32_t (&s)[32], const flo
   }
 }
 
-// 16 scores of one key against 16 query rows: sum of exp2(score * c2 - lse2[row]).
+// 16 scores of one key against 16 query rows: sum of exp2(score * c2 - lse2[row]).  The rows
+// whose bit is set in kColPolyMask take their exponential on the FMA pipes (cubic, 8.6e-5
+// relative): the exponential unit is the bottleneck of this kernel and its issue slots are half
+// empty.
+template <int kE>
+__device__ __forceinline__ float col_exp_one(float x) {
+  return ((kColPolyMask >> kE) & 1) ? poly_exp2(x) : fast_exp2(x);
+}
 __device__ __forceinline__ void col_exp_chunk16(const uint32_t (&s)[32], const float4* nl4, float c2, float& a0,
                                                 float& a1, float& a2, float& a3) {
-#pragma unroll
-  for (int q4 = 0; q4 < 4; ++q4) {
-    const float4 nl = nl4[q4];
-    a0 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 0]), c2, nl.x));
-    a1 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 1]), c2, nl.y));
-    a2 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 2]), c2, nl.z));
-    a3 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 3]), c2, nl.w));
-  }
+  const float4 n0 = nl4[0], n1 = nl4[1], n2 = nl4[2], n3 = nl4[3];
+  a0 += col_exp_one<0>(fmaf(__uint_as_float(s[0]), c2, n0.x));
+  a1 += col_exp_one<1>(fmaf(__uint_as_float(s[1]), c2, n0.y));
+  a2 += col_exp_one<2>(fmaf(__uint_as_float(s[2]), c2, n0.z));
+  a3 += col_exp_one<3>(fmaf(__uint_as_float(s[3]), c2, n0.w));
+  a0 += col_exp_one<4>(fmaf(__uint_as_float(s[4]), c2, n1.x));
+  a1 += col_exp_one<5>(fmaf(__uint_as_float(s[5]), c2, n1.y));
+  a2 += col_exp_one<6>(fmaf(__uint_as_float(s[6]), c2, n1.z));
+  a3 += col_exp_one<7>(fmaf(__uint_as_float(s[7]), c2, n1.w));
+  a0 += col_exp_one<8>(fmaf(__uint_as_float(s[8]), c2, n2.x));
+  a1 += col_exp_one<9>(fmaf(__uint_as_float(s[9]), c2, n2.y));
+  a2 += col_exp_one<10>(fmaf(__uint_as_float(s[10]), c2, n2.z));
+  a3 += col_exp_one<11>(fmaf(__uint_as_float(s[11]), c2, n2.w));
+  a0 += col_exp_one<12>(fmaf(__uint_as_float(s[12]), c2, n3.x));
+  a1 += col_exp_one<13>(fmaf(__uint_as_float(s[13]), c2, n3.y));
+  a2 += col_exp_one<14>(fmaf(__uint_as_float(s[14]), c2, n3.z));
+  a3 += col_exp_one<15>(fmaf(__uint_as_float(s[15]), c2, n3.w));
 }
 
 // All half tiles of one item for one key (thread): returns the sum over the item's query rows.
@@ -1209,6 +1239,9 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // taken out of the exponent while it is small, else kept inside (rare, slower path)
       float b2 = 0.f;
       if (key < valid && is_ret) b2 = p.bias_ret[h * p.bias_head_stride + n0 + key] * kLog2e;
+      // a bias of -inf (padding behind the valid pivots) masks the key: its column sum is 0
+      const bool masked = b2 == -INFINITY;
+      if (masked) b2 = 0.f;
       const bool b2_small = fabsf(b2) <= 32.f;
       const float b2_in = b2_small ? 0.f : b2;
       const bool warp_fast = __all_sync(0xffffffffu, b2_small);
@@ -1219,6 +1252,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (key < valid) {
         sum *= p.correction;
         if (b2_small) sum *= exp2f(b2);
+        if (masked) sum = 0.f;
         float* dst = p.colsum + static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key;
         if (i0 == 0 && i1 == nq) *dst = sum;
         else atomicAdd(dst, sum);
