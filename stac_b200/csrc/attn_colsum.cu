@@ -730,20 +730,44 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int n0 = (is_ret ? j - n_hot : j) * kFT;
         const int valid = min(kFT, (is_ret ? p.T_ret : p.T_hot) - n0);
         const bool need_bias = is_ret || valid < kFT;
+        bool tile_live = true;   // false: every key of the tile is masked (padding behind the valid pivots)
         if (need_bias) {
           named_bar_sync(1 + g, 128);
+          bool live = false;
           if (row < kFT) {
             float bv = -INFINITY;
             if (row < valid) bv = is_ret ? p.bias_ret[h * p.bias_head_stride + n0 + row] * kLog2e : 0.f;
             sm.bias2[g][row] = bv;
+            live = bv != -INFINITY;
           }
-          named_bar_sync(1 + g, 128);
+          tile_live = named_bar_or(1 + g, 128, live);
         }
         const uint32_t s_addr = tmem + lane_base + b * kFT;
         if (!fetching) {
           mbar_wait(&sm.s_full[b], round & 1, p.err, DEV_TIMEOUT_MMA);
           tc_fence_after();
-          tmem_ld32(s_addr, ra);
+          if (tile_live || !have_ref) tmem_ld32(s_addr, ra);
+        }
+        if (!tile_live && have_ref) {
+          // nothing to exponentiate: all probabilities of this tile are zero
+          if (fetching) tmem_ld_wait();      // the prefetched scores are not needed
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = 0u;
+          tmem_st16(s_addr, pk);
+          tmem_st16(s_addr + 16, pk);
+          tmem_st16(s_addr + 32, pk);
+          tmem_st8(s_addr + 48, pk);
+          const int b2n = (c + 3) & (kFastRing - 1), round2n = (c + 3) >> 2;
+          fetching = false;
+          if (x + 3 < len && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2n], round2n & 1))) {
+            tc_fence_after();
+            tmem_ld32(tmem + lane_base + b2n * kFT, ra);
+            fetching = true;
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&sm.p_full[b]);
+          continue;
         }
         if (!have_ref) {
           have_ref = true;
@@ -1247,6 +1271,8 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool warp_fast = __all_sync(0xffffffffu, b2_small);
       const int n_half = 2 * (i1 - i0);
       const float* nl_item = nl_s + i0 * kBM;
+      // (warps whose 32 keys are all masked still run the sums: letting them only follow the
+      // score buffers was measured slower in the stream, their polling disturbs the others)
       float sum = warp_fast ? col_item_sum<true>(sm, p, t_base, nl_item, n_half, ui, c2, 0.f)
                             : col_item_sum<false>(sm, p, t_base, nl_item, n_half, ui, c2, b2_in);
       if (key < valid) {
