@@ -222,11 +222,14 @@ typedef struct stac_evicted {
   int tokens_per_head;
 } stac_evicted;
 
+#define STAC_MERGE_MAX_LIST (1 << 22) /* (evicted + carried overflow) tokens of one pool head per call */
+
 size_t stac_merge_scratch_bytes(int heads, int list_cap_per_head, int buf_cap);
 
 /* One VoxelKVMerger.insert_and_merge call (stac/merger.py:1157-1255 and :765-918) with the
  * evicted tokens read in place.  list_cap_per_head bounds (evicted + carried overflow) tokens
- * of one head (<= 32767).  Counters in pool->meta are updated on the device. */
+ * of one head (<= STAC_MERGE_MAX_LIST; the scratch grows with heads * list_cap_per_head, about
+ * 150 bytes each).  Counters in pool->meta are updated on the device. */
 int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scratch, size_t scratch_bytes,
                       int list_cap_per_head, int* dev_status, stac_stream_t stream);
 

@@ -13,8 +13,13 @@ import numpy as np
 from .numerics import f32
 
 
-def subsample_plan(M, ratio, block_m=128):
+def subsample_plan(M, ratio, block_m=128, rule="cuda"):
     """Return (M_sub, row_stride, correction) for the column-sum pass.
+
+    rule="cuda" is the reference's default backend (attn-cuda/csrc/bindings.cpp:63-83) and what
+    the library implements; rule="triton" is the Triton entry point
+    (stac/flash_attn_triton.py:964-974), used only to compare this oracle with fixtures made by
+    running that entry point.
 
     ratio >= 0.999999 is exact over all M rows (attn-cuda/csrc/bindings.cpp:67-71, the
     default backend; the Triton entry point lacks this special case and drops the last
@@ -22,7 +27,7 @@ def subsample_plan(M, ratio, block_m=128):
     down to a multiple of block_m; if that covers all rows the pass is exact, else rows
     0, s, 2s, ... (s = M // M_sub) are used and the sums are scaled by M / M_sub.
     """
-    if ratio >= 0.999999:
+    if ratio >= 0.999999 and rule == "cuda":
         return M, 1, 1.0
     m_sub = max(block_m, int(M * ratio))
     m_sub = (m_sub // block_m) * block_m
@@ -31,7 +36,7 @@ def subsample_plan(M, ratio, block_m=128):
     return m_sub, max(1, M // m_sub), M / m_sub
 
 
-def attn_colsum(q, k, v, bias=None, scale=None, subsample_ratio=1.0):
+def attn_colsum(q, k, v, bias=None, scale=None, subsample_ratio=1.0, rule="cuda"):
     """q [M,H,D], k/v [N,H,D] (token-major, like the reference's [B,T,H,D] with B=1),
     bias [H,N] float32 or None.  Returns O [M,H,D], lse [H,M], colsum [H,N] (float32)."""
     q = f32(q)
@@ -44,7 +49,7 @@ def attn_colsum(q, k, v, bias=None, scale=None, subsample_ratio=1.0):
     out = np.empty((M, H, D), np.float32)
     lse = np.empty((H, M), np.float32)
     colsum = np.empty((H, N), np.float32)
-    m_sub, stride, corr = subsample_plan(M, subsample_ratio)
+    m_sub, stride, corr = subsample_plan(M, subsample_ratio, rule=rule)
     rows = np.arange(m_sub) * stride
     for h in range(H):
         s = (q[:, h, :] @ k[:, h, :].T) * np.float32(scale)

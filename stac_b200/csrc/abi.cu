@@ -21,6 +21,25 @@ __global__ void bounded_wait_selftest_kernel(int max_polls, int* err) {
 }
 
 }  // namespace
+
+int current_device(int* dev) {
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || !device_index_ok(d)) return STAC_ERR_CUDA;
+  *dev = d;
+  return STAC_OK;
+}
+
+int device_sm_count(int dev, int* n_sm) {
+  static PerDeviceValue<int> cache;
+  int n = cache.get(dev);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return STAC_ERR_CUDA;
+    cache.set(dev, n);
+  }
+  *n_sm = n;
+  return STAC_OK;
+}
+
 }  // namespace stac
 
 extern "C" {

@@ -444,6 +444,7 @@ struct FastSmem {
   float bias2[3][kBN];
   float m_ref[2][kBM];                          // row references of the segment (parity)
   float lpart[2][2][kBM];                       // row sums of warpgroups 1 and 2 (segment parity)
+  int live[2][2];                               // did warpgroup 1 / 2 see a key that is not masked (segment parity)
   uint64_t q_full[2];
   uint64_t q_empty[2];
   uint64_t k_full[kFastKStages];
@@ -721,6 +722,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       float m_ref = 0.f;
       float l0 = 0.f, l1 = 0.f;
       bool have_ref = false;
+      bool any_live = false;  // some key tile of this warpgroup in this segment had a key that is not masked
       bool fetching = false;  // the first 32 scores of the next tile are already on their way into ra
       for (int x = (g + 3 - c_base % 3) % 3; x < len; x += 3) {
         const int c = c_base + x;
@@ -742,6 +744,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
           tile_live = named_bar_or(1 + g, 128, live);
         }
+        any_live = any_live || tile_live;
         const uint32_t s_addr = tmem + lane_base + b * kFT;
         if (!fetching) {
           mbar_wait(&sm.s_full[b], round & 1, p.err, DEV_TIMEOUT_MMA);
@@ -839,6 +842,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       overflow = overflow || !(lsum <= kFastRowSumLimit);   // also true for NaN
       if (g != 0) {
         sm.lpart[sb][g - 1][row] = lsum;
+        if (row == 0) sm.live[sb][g - 1] = any_live ? 1 : 0;
         mbar_arrive(&sm.l_ready[sb]);
       } else {
         if (!have_ref) {
@@ -847,6 +851,12 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         mbar_wait(&sm.l_ready[sb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
         const float l = (lsum + sm.lpart[sb][0][row]) + sm.lpart[sb][1][row];
+        // A segment whose keys are all masked has no reference (m_ref is a placeholder): it must not
+        // take part in a join.  A segment with live keys whose probabilities all underflowed (its
+        // first tile was masked, so the placeholder was used, and the live scores lie far below
+        // it) cannot be represented: the exact kernel redoes the call.
+        const bool seg_live = any_live || sm.live[sb][0] != 0 || sm.live[sb][1] != 0;
+        if (seg_live && !(l > 0.f)) overflow = true;
         mbar_wait(&sm.o_done, seg & 1, p.err, DEV_TIMEOUT_MMA);
         tc_fence_after();
         tmem_ld32(o_tmem + lane_base, ra);
@@ -899,7 +909,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             orow[8 + q4] = make_float4(__uint_as_float(rb[q4 * 4 + 0]), __uint_as_float(rb[q4 * 4 + 1]),
                                        __uint_as_float(rb[q4 * 4 + 2]), __uint_as_float(rb[q4 * 4 + 3]));
           slot[kBM * kD + row] = l;
-          slot[kBM * kD + kBM + row] = m_ref;
+          const float m_pub = seg_live ? m_ref : -INFINITY;
+          slot[kBM * kD + kBM + row] = m_pub;
           __threadfence();                       // this thread's part is visible device-wide ...
           named_bar_sync(4, 128);                // ... and so is every other row's
           if (row == 0) sm.join_flag = atomicAdd(p.part_count + cut, 1);
@@ -910,10 +921,11 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const float* other = p.part + static_cast<size_t>(first_part ? 2 * (cut + 1) : 2 * cut + 1) * kPartFloats;
             const float lo_ = __ldcg(other + kBM * kD + row), mo_ = __ldcg(other + kBM * kD + kBM + row);
             // a = the part with the item's first tiles, b = the part with its last ones
-            const float la = first_part ? l : lo_, ma = first_part ? m_ref : mo_;
-            const float lb = first_part ? lo_ : l, mb = first_part ? mo_ : m_ref;
-            const float m = fmaxf(ma, mb);
-            const float wa = exp2f(ma - m), wb = exp2f(mb - m);
+            const float la = first_part ? l : lo_, ma = first_part ? m_pub : mo_;
+            const float lb = first_part ? lo_ : l, mb = first_part ? mo_ : m_pub;
+            const float mm = fmaxf(ma, mb);
+            const float m = (mm == -INFINITY) ? 0.f : mm;     // both parts fully masked: zeros, lse = -inf
+            const float wa = exp2f(ma - m), wb = exp2f(mb - m);   // a masked part (-inf) weighs nothing
             // explicit operation order: the same bits whichever of the two CTAs computes the join
             const float lsum2 = __fmaf_rn(la, wa, __fmul_rn(lb, wb));
             const float inv = lsum2 > 0.f ? 1.f / lsum2 : 0.f;
@@ -1366,7 +1378,9 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
        reinterpret_cast<uintptr_t>(a.out)) & 15)
     return STAC_ERR_BAD_ARG;
 
-  static bool attr_done = false;
+  int dev = 0;
+  if (current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
+  static PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
   const int fwd_smem = static_cast<int>(sizeof(FwdSmem)) + 1024;
   int m_sub, stride;
   float corr;
@@ -1375,7 +1389,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   const int col_smem = static_cast<int>(sizeof(ColSmem)) + nq * kBM * 4 + 1024;
   if (col_smem > 227 * 1024) return STAC_ERR_BAD_ARG;
   const int fast_smem = static_cast<int>(sizeof(FastSmem)) + 1024;
-  if (!attr_done) {
+  if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem) != cudaSuccess)
       return STAC_ERR_CUDA;
     if (cudaFuncSetAttribute(attn_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fast_smem) !=
@@ -1384,7 +1398,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
     if (cudaFuncSetAttribute(attn_colsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess)
       return STAC_ERR_CUDA;
-    attr_done = true;
+    attr_done.mark(dev);
   }
 
   const uint64_t eb = 2;  // bytes per element
@@ -1436,13 +1450,8 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   fp.err = err;
   fp.fallback = reinterpret_cast<int*>(lse2 + static_cast<size_t>(a.H) * a.M);
   dim3 grid_f((a.M + kBM - 1) / kBM, a.H);
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
-      return STAC_ERR_CUDA;
-  }
+  int n_sm = 0;
+  if (device_sm_count(dev, &n_sm) != STAC_OK) return STAC_ERR_CUDA;
   // fast kernel (fixed per-row reference) first; the exact kernel behind it returns at once
   // unless the fast one raised the flag.  With at least one item per SM (and a workspace for
   // the parts) the units are cut evenly over one CTA per SM, else every CTA takes one item.
@@ -1502,7 +1511,6 @@ namespace {
 // until the process exits.
 static __device__ __align__(256) float g_static_lse2[STAC_ATTN_STATIC_MAX_ROWS + 64];  // + fallback flag
 
-constexpr int kMaxDevices = 64;
 float* g_static_lse2_ptr[kMaxDevices] = {nullptr};
 
 // The array's name is only a host-side handle; the kernels need its device address, which

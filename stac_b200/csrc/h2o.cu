@@ -252,12 +252,14 @@ int stac_h2o_select(const float* scores, int64_t row_stride, int n_rows, const u
     return STAC_ERR_BAD_ARG;
   const int smem = T * 4;
   if (smem > 200 * 1024) return STAC_ERR_CAPACITY;
-  static int attr_smem = 0;
-  if (smem > attr_smem) {
+  int dev = 0;
+  if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
+  static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
+  if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(stac::h2o_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
         cudaSuccess)
       return STAC_ERR_CUDA;
-    attr_smem = 200 * 1024;
+    attr_done.mark(dev);
   }
   stac::h2o_select_kernel<<<n_rows, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
       scores, row_stride, is_base, T, n_keep, keep_idx, drop_idx);

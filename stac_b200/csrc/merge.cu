@@ -110,7 +110,7 @@ struct MergeParams {
   int* row_start;      // [heads][ncap + 1]
   int4* row_info;      // [heads][ncap]: add_cnt, over_cnt, flags, n_sel
   int4* row_pref;      // [heads][ncap]: exclusive prefixes inside the head
-  short* old_dest;     // [heads][ncap][8]
+  int* old_dest;       // [heads][ncap][8] new rank of each buffered token (>= B: goes to the overflow list)
   int* tok_dest;       // [heads][ncap]
   float* tok_sim;      // [heads][ncap]
   float* tok_score;    // [heads][ncap]
@@ -499,8 +499,8 @@ __device__ __forceinline__ void phase_a_row(const MergeParams& p, const int h, c
       if (lane < nbuf && s2 > ex_s) ++ex_rank;  // tokens arrive after every existing entry
     }
   }
-  short* od = p.old_dest + (hb + ri) * kMaxB;
-  if (lane < nbuf) od[lane] = static_cast<short>(min(ex_rank, 32767));
+  int* od = p.old_dest + (hb + ri) * kMaxB;
+  if (lane < nbuf) od[lane] = ex_rank;
   // selected tokens
   for (int base = s0; base < s1; base += 32) {
     const int i = base + lane;
@@ -574,13 +574,13 @@ __global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p)
     p.tok_row[hb + i] = ri;
   }
   const int n_sel = s1 - s0;
-  short* od = p.old_dest + (hb + ri) * kMaxB;
+  int* od = p.old_dest + (hb + ri) * kMaxB;
 #pragma unroll
   for (int c = 0; c < kMaxB; ++c) {
     if (c < nbuf) {
       int rank = c;  // buffered tokens are stored in rank order
       for (int i = s0; i < s1; ++i) rank += (tscore[i] > ex[c]) ? 1 : 0;
-      od[c] = static_cast<short>(min(rank, 32767));
+      od[c] = rank;
     }
   }
   for (int i = s0; i < s1; ++i) {
@@ -777,7 +777,7 @@ __global__ void __launch_bounds__(256) rows_phase_b1a_kernel(const MergeParams p
     const int q = add_off + (col - nbuf);
     p.buf_row_seg[r * p.B + col] = q < k_take ? p.buf_free[free_len - k_take + q] : buf_top + (q - k_take);
   }
-  const short* od = p.old_dest + (hb + ri) * kMaxB;
+  const int* od = p.old_dest + (hb + ri) * kMaxB;
   bool moves = false;
   for (int c = 0; c < nbuf; ++c) moves = moves || (od[c] != c);
   if (moves) p.move_list[atomicAdd(&p.plan[kPlanMoveCount], 1)] = make_int2(h, ri);
@@ -809,7 +809,7 @@ __global__ void __launch_bounds__(256) rows_phase_b1m_kernel(const MergeParams p
     const int over_off = p.head_base[h].y + p.row_pref[hb + ri].y;
     const int nbuf = info.z >> 4;
     const int newcnt = nbuf + info.x;
-    const short* od = p.old_dest + (hb + ri) * kMaxB;
+    const int* od = p.old_dest + (hb + ri) * kMaxB;
     int my_seg = -1, ex_dest = -1;
     if (lane < newcnt) my_seg = p.buf_row_seg[r * B + lane];
     if (lane < nbuf) ex_dest = od[lane];
@@ -1164,7 +1164,7 @@ ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
   L.keys_a = take(hn * 4); L.keys_b = take(hn * 4); L.vals_a = take(hn * 4); L.vals_b = take(hn * 4);
   L.n_tok = take(static_cast<size_t>(heads) * 4); L.n_rows = take(static_cast<size_t>(heads) * 4);
   L.row_vx = take(hn * 4); L.row_start = take(static_cast<size_t>(heads) * (ncap + 1) * 4);
-  L.row_info = take(hn * 16); L.row_pref = take(hn * 16); L.old_dest = take(hn * kMaxB * 2);
+  L.row_info = take(hn * 16); L.row_pref = take(hn * 16); L.old_dest = take(hn * kMaxB * 4);
   L.tok_dest = take(hn * 4); L.tok_sim = take(hn * 4); L.tok_score = take(hn * 4);
   L.head_tot = take(static_cast<size_t>(heads) * 16); L.head_base = take(static_cast<size_t>(heads) * 16);
   L.plan = take(kPlanSize * 4); L.free_stage = take(static_cast<size_t>(buf_cap) * 4);
@@ -1218,7 +1218,7 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
     return STAC_ERR_BAD_ARG;
   if (pool->heads <= 0 || pool->voxel_cap <= 0 || pool->voxel_used < 0 || pool->voxel_used > pool->voxel_cap)
     return STAC_ERR_BAD_ARG;
-  if (ev->tokens_per_head <= 0 || list_cap_per_head < ev->tokens_per_head || list_cap_per_head > 32767)
+  if (ev->tokens_per_head <= 0 || list_cap_per_head < ev->tokens_per_head || list_cap_per_head > STAC_MERGE_MAX_LIST)
     return STAC_ERR_BAD_ARG;
   const stac::ScratchLayout L = stac::scratch_layout(pool->heads, list_cap_per_head, pool->buf_cap);
   if (scratch_bytes < L.total) return STAC_ERR_CAPACITY;
@@ -1252,7 +1252,7 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
   mp.row_start = reinterpret_cast<int*>(base + L.row_start);
   mp.row_info = reinterpret_cast<int4*>(base + L.row_info);
   mp.row_pref = reinterpret_cast<int4*>(base + L.row_pref);
-  mp.old_dest = reinterpret_cast<short*>(base + L.old_dest);
+  mp.old_dest = reinterpret_cast<int*>(base + L.old_dest);
   mp.tok_dest = reinterpret_cast<int*>(base + L.tok_dest);
   mp.tok_sim = reinterpret_cast<float*>(base + L.tok_sim);
   mp.tok_score = reinterpret_cast<float*>(base + L.tok_score);

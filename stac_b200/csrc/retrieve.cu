@@ -202,13 +202,15 @@ int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_
   rp.sel = sel; rp.out_K = out_K; rp.out_V = out_V; rp.out_mask = out_mask; rp.out_bias = out_bias;
   rp.out_idx = out_idx;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  static bool attr_done = false;
+  int dev = 0;
+  if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
+  static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
   const int smem = stac::kSelCap * 8;
-  if (!attr_done) {
+  if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(stac::retrieve_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return STAC_ERR_CUDA;
-    attr_done = true;
+    attr_done.mark(dev);
   }
   stac::retrieve_select_kernel<<<pool->heads, 1024, smem, st>>>(rp);
   const int vpt = token_bytes / 16;

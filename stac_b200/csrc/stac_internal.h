@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "../../include/stac_b200.h"
+#include "per_device.h"
 
 namespace stac {
 
@@ -33,6 +34,10 @@ struct AttnArgs {
   float scale;
   float subsample_ratio;
 };
+
+// Ordinal of the current device (checked against kMaxDevices) / its SM count, cached per device.
+int current_device(int* dev);
+int device_sm_count(int dev, int* n_sm);
 
 void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* correction);
 size_t attn_lse2_elems(int M, int H);

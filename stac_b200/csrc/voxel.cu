@@ -389,13 +389,15 @@ int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* ma
                                                           static_cast<const unsigned long long*>(hash_keys),
                                                           hash_vals, static_cast<int>(hash_cap), pt_keys, ids_out,
                                                           new_keys, new_cnt);
-  static bool attr_done = false;
+  int dev = 0;
+  if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
+  static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
   const int smem = stac::kSortCap * 8;
-  if (!attr_done) {
+  if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(stac::insert_new_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return STAC_ERR_CUDA;
-    attr_done = true;
+    attr_done.mark(dev);
   }
   stac::insert_new_kernel<<<1, 1024, smem, st>>>(new_keys, new_cnt, reinterpret_cast<long long*>(table_keys),
                                                  table_cap, static_cast<unsigned long long*>(hash_keys), hash_vals,

@@ -35,11 +35,15 @@ _workspaces = {}
 
 
 def _attn_workspace(device, M, H):
+    """Scratch of stac_attn_colsum (row log-sum-exps, split partials, arrival counters).  One per
+    (device, stream): calls on one stream are ordered and may share it, calls issued on different
+    streams may overlap on the GPU and must not."""
     need = _lib.lib().stac_attn_workspace_bytes(M, H)
-    ws = _workspaces.get(device)
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() * 4 < need:
         ws = torch.empty(max(need // 4, 1), dtype=torch.float32, device=device)
-        _workspaces[device] = ws
+        _workspaces[key] = ws
     return ws
 
 

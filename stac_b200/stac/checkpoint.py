@@ -10,11 +10,19 @@ ids, scores, slot maps, pool contents and retrieved pivots.
 import torch
 
 
+def _sync(manager):
+    dev = torch.device(manager.device)
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)
+
+
 def save_state(manager, path: str) -> None:
-    torch.cuda.synchronize(manager.device)
+    _sync(manager)
     torch.save(manager.state_dict(), path)
 
 
 def load_state(manager, path: str) -> None:
-    manager.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))
-    torch.cuda.synchronize(manager.device)
+    """The file holds only tensors, lists, numbers, strings, None and nested dicts, so it is read
+    with ``weights_only=True``: a checkpoint from an untrusted source cannot run code on load."""
+    manager.load_state_dict(torch.load(path, map_location="cpu", weights_only=True))
+    _sync(manager)

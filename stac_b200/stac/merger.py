@@ -16,7 +16,7 @@ from .. import _lib
 from .._lib import META_BUF_FREE_LEN, META_BUF_TOP, META_BUF_USED, META_OVER_COUNT, META_PIV_TOP, META_PIV_USED
 from .._lib import StacEvicted, StacPool, check, ptr, stream_ptr
 
-MAX_LIST = 32767
+MAX_LIST = 1 << 22        # STAC_MERGE_MAX_LIST
 
 
 class VoxelKVMerger:
@@ -273,7 +273,7 @@ class VoxelKVMerger:
             self._over[1 - self._over_cur] = self._new_over(cap)
             self._over_cap = cap
         ncap = Tn + self._over_max_head
-        ncap = min(MAX_LIST, max(ncap, (ncap + 2047) // 2048 * 2048)) if ncap <= MAX_LIST else ncap
+        ncap = (ncap + 2047) // 2048 * 2048        # few distinct scratch sizes
         if ncap > MAX_LIST:
             raise _lib.StacError(f"{ncap} tokens for one pool head in one call; the limit is {MAX_LIST}")
         need = _lib.lib().stac_merge_scratch_bytes(H, ncap, self._buf_cap)

@@ -83,14 +83,16 @@ def retrieve_query(name, tag):
 
 
 # ---------------------------------------------------------------- manager trace
-MANAGER = dict(L=2, H=2, D=16, tpf=21, special=5, chunk=2, window=3, hh=1, buffer=7, steps=14,
-               voxel_size=0.05, init_voxels=32, retrieval=1, retrieve_steps=(6, 8, 10, 12),
-               seed=31)
+# `motion` = camera shift per frame (m): slow enough that a voxel is seen in many frames, so buffer
+# rows fill up, pivots form and the retrieval around the newest frames returns valid pivots.
+MANAGER = dict(L=2, H=2, D=16, tpf=21, special=5, chunk=2, window=3, hh=1, buffer=7, steps=24,
+               voxel_size=0.05, init_voxels=32, retrieval=1, retrieve_steps=(6, 10, 14, 16, 18, 20, 22),
+               seed=31, motion=0.003)
 
 
-MANAGER_GPU = dict(L=2, H=3, D=64, tpf=41, special=5, chunk=2, window=3, hh=1, buffer=7, steps=18,
-                   voxel_size=0.05, init_voxels=32, retrieval=1, retrieve_steps=(6, 8, 10, 12, 14, 16),
-                   seed=61)
+MANAGER_GPU = dict(L=2, H=3, D=64, tpf=41, special=5, chunk=2, window=3, hh=1, buffer=7, steps=26,
+                   voxel_size=0.05, init_voxels=32, retrieval=1, retrieve_steps=(6, 8, 10, 12, 14, 16, 18, 20, 22, 24),
+                   seed=61, motion=0.003)
 
 
 def manager_inputs(c=None):
@@ -112,7 +114,7 @@ def manager_inputs(c=None):
         mask = np.zeros(Tn, bool)
         for f in range(c["chunk"]):
             frame = step * c["chunk"] + f
-            p = grid * np.float32(0.06) + np.array([0.02 * frame, 0.0, 0.3], np.float32)
+            p = grid * np.float32(0.06) + np.array([c.get("motion", 0.02) * frame, 0.0, 0.3], np.float32)
             p = p + (rs.rand(npatch, 3).astype(np.float32) - 0.5) * np.float32(0.02)
             lo = f * tpf + c["special"]
             pts[lo:lo + npatch] = p
@@ -127,9 +129,24 @@ ATTENTION = {
 }
 
 
+# Cases run through the reference's own Triton kernels on a B200 (make_attention_ref.py).
+# "ratio" is the subsample_ratio passed; where M is not a multiple of 128 the Triton entry
+# point sums rows [0, M//128*128) and rescales even at ratio 1 (the CUDA backend, which the
+# library follows, is exact there), so "same_rule" says whether the column sums of the two
+# backends are defined identically for the case.
+ATTENTION_REF = {
+    "plain": dict(M=70, N=200, H=2, D=64, n_bias=0, seed=41, ratio=1.0, same_rule=True),
+    "pivots": dict(M=130, N=300, H=2, D=64, n_bias=64, seed=42, ratio=1.0, same_rule=False),
+    "pivots256": dict(M=256, N=700, H=3, D=64, n_bias=190, seed=43, ratio=1.0, same_rule=True),
+    "subsample": dict(M=512, N=900, H=2, D=64, n_bias=130, seed=44, ratio=0.25, same_rule=True),
+    "config2_tail": dict(M=1024, N=2082, H=4, D=64, n_bias=2048, seed=45, ratio=1.0, same_rule=True),
+    "config2_frame": dict(M=1041, N=2082, H=2, D=64, n_bias=2048, seed=46, ratio=1.0, same_rule=False),
+}
+
+
 def attention_inputs(name):
     """q [M,H,D], k/v [N,H,D] float32 holding bf16-representable values, bias [H,N] or None."""
-    c = ATTENTION[name]
+    c = ATTENTION[name] if name in ATTENTION else ATTENTION_REF[name]
     rs = np.random.RandomState(c["seed"])
 
     def bf16(x):

@@ -154,3 +154,65 @@ def test_head_sharding_counts_two_ranks():
     from stac_b200.sharding import head_slice
     with pytest.raises(ValueError):
         head_slice(0, 3, 16)
+
+
+def test_launch_state_is_kept_per_device(tmp_path):
+    """The shared-memory opt-in of a kernel and the SM count belong to a GPU: the bookkeeping the
+    launchers use (csrc/per_device.h, host-only C++) keeps one entry per device ordinal."""
+    import subprocess
+    src = tmp_path / "per_device_test.cpp"
+    src.write_text('#include "per_device.h"\n'
+                   "int main() {\n"
+                   "  stac::PerDeviceFlag f;\n"
+                   "  stac::PerDeviceValue<int> sm;\n"
+                   "  if (!f.needs_setup(0) || !f.needs_setup(1)) return 1;\n"
+                   "  f.mark(0);\n"
+                   "  if (f.needs_setup(0)) return 2;\n"
+                   "  if (!f.needs_setup(1)) return 3;          // device 1 still has to opt in\n"
+                   "  sm.set(0, 148);\n"
+                   "  if (sm.get(0) != 148 || sm.get(1) != 0) return 4;\n"
+                   "  if (!stac::device_index_ok(63) || stac::device_index_ok(64) || stac::device_index_ok(-1)) return 5;\n"
+                   "  return 0;\n"
+                   "}\n")
+    exe = tmp_path / "per_device_test"
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "stac_b200", "csrc"), str(src), "-o", str(exe)],
+                   check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
+    # no launcher keeps a process-wide "attribute already set" or SM-count static any more
+    for name in ("attn_colsum.cu", "h2o.cu", "retrieve.cu", "voxel.cu"):
+        text = open(os.path.join(ROOT, "stac_b200", "csrc", name)).read()
+        assert not re.search(r"static\s+(bool|int)\s+(attr_done|attr_smem|n_sm)\b", text), name
+
+
+def test_checkpoint_file_loads_without_pickle(tmp_path):
+    """save_state / load_state round trip of a state dictionary with every value type the managers
+    emit (tensors, lists, numbers, strings, None, nested dicts), read back with weights_only=True."""
+    import torch
+    from stac_b200.stac.checkpoint import load_state, save_state
+
+    class Stub:
+        device = torch.device("cpu")
+
+        def __init__(self):
+            self.loaded = None
+
+        def state_dict(self):
+            return {"format": 1, "class": "STACVoxelKV", "shape": [2, 3, 64, 21, 147], "use_cpu": False,
+                    "key": torch.arange(12, dtype=torch.bfloat16).view(2, 3, 2), "key_cpu": None,
+                    "offset_hot": [5, 5], "temperature": 0.9,
+                    "memory": {"meta": torch.arange(8, dtype=torch.int32), "over": {"S": torch.zeros(0)},
+                               "voxel_alloc": 64},
+                    "retrieved": [torch.ones(2, 2), torch.zeros(2, dtype=torch.bool)]}
+
+        def load_state_dict(self, sd):
+            self.loaded = sd
+
+    a, b = Stub(), Stub()
+    path = str(tmp_path / "stream.pt")
+    save_state(a, path)
+    load_state(b, path)
+    want = a.state_dict()
+    assert b.loaded["offset_hot"] == want["offset_hot"] and b.loaded["key_cpu"] is None
+    assert torch.equal(b.loaded["key"], want["key"]) and b.loaded["key"].dtype == torch.bfloat16
+    assert torch.equal(b.loaded["memory"]["meta"], want["memory"]["meta"])
+    assert b.loaded["retrieved"][1].dtype == torch.bool

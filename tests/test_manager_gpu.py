@@ -293,7 +293,7 @@ def test_checkpoint_resume_continues_with_the_same_bits(tmp_path):
     for (ka, ba), (kb, bb) in zip(a_log, b_log):
         assert np.array_equal(ka, kb) and np.array_equal(ba, bb)
     with pytest.raises(ValueError):
-        _make(c, buffer_size=c["buffer"] + 1).load_state_dict(torch.load(path, weights_only=False))
+        _make(c, buffer_size=c["buffer"] + 1).load_state_dict(torch.load(path, weights_only=True))
 
 
 def test_long_stream_with_bounded_voxel_memory():

@@ -93,6 +93,7 @@ def test_manager_trace(golden_dir):
                      voxel_size=c["voxel_size"], init_voxels=c["init_voxels"],
                      retrieval_size=c["retrieval"], dtype="f32")
     pruned = 0
+    valid_pivots = 0      # retrieved pivots with a finite bias (log C) in the reference's own trace
     for step, (k, v, cs, pts, mask) in enumerate(cases.manager_inputs()):
         Tq = k.shape[2]
         for l in range(c["L"]):
@@ -111,6 +112,7 @@ def test_manager_trace(golden_dir):
                 _close(Kr.reshape(L, H, -1, c["D"]), g[f"s{step}_ret_K"])
                 refb = g[f"s{step}_ret_bias"]
                 fin = np.isfinite(refb)
+                valid_pivots += int(fin.sum())
                 assert np.array_equal(np.isfinite(Br.reshape(refb.shape)), fin)
                 _close(Br.reshape(refb.shape)[fin], refb[fin], rtol=1e-5)
         mg.prune()
@@ -123,6 +125,10 @@ def test_manager_trace(golden_dir):
         assert mg.merger.V_used == int(g[f"s{step}_Vused"])
         _check_slot_map(mg.merger, g, f"s{step}")
     assert pruned >= 8
+    # the trace must reach the states that matter: rows that filled up and became pivots, and
+    # retrievals that returned them (log C hand-off, width rule of stac/stac_voxel.py:722-738)
+    assert valid_pivots >= 300
+    assert (g[f"s{c['steps'] - 1}_piv_offset"] > 0).sum() >= 100
     _close(mg.K[:, :, : mg.off[0]], g["final_K"], rtol=0, atol=0)
 
 
@@ -137,12 +143,37 @@ def test_attention(golden_dir, name):
     _close(cs.sum(axis=1), np.full(cs.shape[0], q.shape[0], np.float32), rtol=1e-4)
 
 
+def _bf16_bits_to_f32(a):
+    return (a.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("name", list(cases.ATTENTION_REF))
+def test_attention_against_the_reference_kernels(golden_dir, name):
+    """attention_ref.npz holds what the reference's own Triton kernels (fa_forward_colsum_fast_sub,
+    stac/flash_attn_triton.py:900-1006) returned on a B200 for these seeded inputs
+    (make_attention_ref.py).  The oracle, using that entry point's row sub-sampling rule, must
+    reproduce O, lse and the column sums."""
+    g = _load(golden_dir, "attention_ref.npz")
+    c = cases.ATTENTION_REF[name]
+    q, k, v, bias = cases.attention_inputs(name)
+    out, lse, cs = attn_colsum(q, k, v, bias, subsample_ratio=c["ratio"], rule="triton")
+    assert np.abs(out - _bf16_bits_to_f32(g[f"{name}_out_bf16"])).max() <= 2e-2      # bf16 output
+    _close(lse, g[f"{name}_lse"], rtol=1e-3, atol=1e-3)
+    _close(cs, g[f"{name}_colsum"], rtol=1e-3, atol=1e-6)
+    if c["same_rule"]:   # both backends of the reference define the column sums identically here
+        _, _, cs_cuda = attn_colsum(q, k, v, bias, subsample_ratio=c["ratio"])
+        _close(cs_cuda, g[f"{name}_colsum"], rtol=1e-3, atol=1e-6)
+
+
 def test_subsample_plan():
     assert subsample_plan(1041, 1.0) == (1041, 1, 1.0)
     assert subsample_plan(4164, 0.25) == (1024, 4, 4164 / 1024)
     assert subsample_plan(100, 0.25) == (100, 1, 1.0)
     assert subsample_plan(1041, 0.999) == (1024, 1, 1041 / 1024)
     assert subsample_plan(4164, 0.5) == (2048, 2, 4164 / 2048)
+    # the Triton entry point has no exact special case at ratio 1
+    assert subsample_plan(1041, 1.0, rule="triton") == (1024, 1, 1041 / 1024)
+    assert subsample_plan(1024, 1.0, rule="triton") == (1024, 1, 1.0)
 
 
 @pytest.mark.parametrize("name", list(cases.POINTMAP))

@@ -38,10 +38,25 @@ def _call_noalloc(q, kh, vh, kr, vr, bias, status):
     return rc, out, lse, cs
 
 
-def test_noalloc_matches_workspace_entry_twice():
+def _oracle(q, kh, vh, kr, vr, bias):
+    from oracle.attention import attn_colsum as oracle_attn
+    H, T_hot = kh.shape[0], kh.shape[1]
+    k_all = torch.cat([kh, kr], 1).float().cpu().numpy().transpose(1, 0, 2)
+    v_all = torch.cat([vh, vr], 1).float().cpu().numpy().transpose(1, 0, 2)
+    b_all = np.concatenate([np.zeros((H, T_hot), np.float32), bias.cpu().numpy()], 1)
+    return oracle_attn(q.float().cpu().numpy(), k_all, v_all, b_all)
+
+
+# The third shape has 160 (head, key group) column-sum items, more than the 148 SMs: without a
+# workspace the forward pass runs one CTA per item while the column-sum pass is cut evenly over
+# the SMs and adds partial sums onto the zeros the forward pass left in the output.
+SHAPES = [(700, 4, 900, 130, 7), (260, 2, 300, 70, 8), (300, 16, 3400, 140, 9)]
+
+
+def test_noalloc_matches_oracle_and_workspace_entry_in_a_row():
     from stac_b200 import ops
     status = ops.DeviceStatus(torch.device(DEV))
-    for M, H, T_hot, T_ret, seed in [(700, 4, 900, 130, 7), (260, 2, 300, 70, 8)]:
+    for M, H, T_hot, T_ret, seed in SHAPES:
         q, kh, vh, kr, vr, bias = _inputs(M, H, T_hot, T_ret, seed)
         rc, out, lse, cs = _call_noalloc(q, kh, vh, kr, vr, bias, status)
         assert rc == 0
@@ -49,9 +64,16 @@ def test_noalloc_matches_workspace_entry_twice():
                                                    status=status)
         torch.cuda.synchronize()
         status.raise_if_set("attention")
-        assert np.abs(out.float().cpu().numpy() - ref_out.float().cpu().numpy()).max() <= 2e-2
-        np.testing.assert_allclose(lse.cpu().numpy(), ref_lse.cpu().numpy(), rtol=1e-3, atol=1e-3)
-        np.testing.assert_allclose(cs.cpu().numpy(), ref_cs.cpu().numpy(), rtol=1e-3, atol=1e-6)
+        o_np, lse_np, cs_np = out.float().cpu().numpy(), lse.cpu().numpy(), cs.cpu().numpy()
+        # against the existing entry point ...
+        assert np.abs(o_np - ref_out.float().cpu().numpy()).max() <= 2e-2
+        np.testing.assert_allclose(lse_np, ref_lse.cpu().numpy(), rtol=1e-3, atol=1e-3)
+        np.testing.assert_allclose(cs_np, ref_cs.cpu().numpy(), rtol=1e-3, atol=1e-6)
+        # ... and against the CPU oracle
+        o_or, lse_or, cs_or = _oracle(q, kh, vh, kr, vr, bias)
+        assert np.abs(o_np - o_or).max() <= 2e-2
+        np.testing.assert_allclose(lse_np, lse_or, rtol=1e-3, atol=1e-3)
+        np.testing.assert_allclose(cs_np, cs_or, rtol=1e-3, atol=1e-6)
 
 
 def test_noalloc_rejects_oversize():
