@@ -46,40 +46,46 @@ WORKLOAD = ("config4-hot-path: CausalVGGT+STAC stream shapes (24 layers x 16 hea
 
 
 # ------------------------------------------------------------------------------------ inputs
-def synth_points(n_chunks, seed=0):
-    """Per chunk: points [chunk*tpf, 3] fp32 and mask [chunk*tpf] bool.  A pinhole camera moves
-    along a smooth random trajectory in front of a smooth depth surface (depth in [1, 10] m);
-    patch centres of a 37 x 28 grid are unprojected; the 5 special tokens of each frame carry
-    zero points and are masked out (stream_session.py:249-255)."""
+def synth_points(n_chunks, seed=0, sway=1.0):
+    """Per chunk: points [chunk*tpf, 3] fp32 and mask [chunk*tpf] bool.  A hand-held pinhole camera
+    hovers in front of a smooth depth surface that is fixed in the world (depth in [1, 10] m): it
+    sways a few centimetres (sines of incommensurate periods plus millimetre jitter) and drifts
+    slowly sideways, so the same 5 cm voxels are seen again and again, buffer rows fill up, pivots
+    form, saturate and are re-merged, while new voxels keep appearing at the edge of the view.
+    Patch centres of a 37 x 28 grid are unprojected onto the surface; the 5 special tokens of each
+    frame carry zero points and are masked out (stream_session.py:249-255).  `sway` scales the
+    camera motion (larger = more new voxels per frame)."""
     rs = np.random.RandomState(seed)
     c = CFG
     ph, pw = c["patch_h"], c["patch_w"]
     u = (np.arange(pw) + 0.5) / pw - 0.5
     v = (np.arange(ph) + 0.5) / ph - 0.5
     uu, vv = np.meshgrid(u, v)
+    x, y = uu * 1.2, vv * 0.9
     freq = rs.rand(4, 2) * 3 + 0.5
     phase = rs.rand(4) * 2 * np.pi
     amp = rs.rand(4)
     out = []
     frame = 0
-    pos = np.zeros(3)
-    vel = np.array([0.012, 0.0, 0.004])     # a slow hand-held scan: ~1 cm per frame
-    yaw = 0.0
+    two_pi = 2 * math.pi
     for _ in range(n_chunks):
         pts = np.zeros((c["chunk"] * c["tpf"], 3), np.float32)
         mask = np.zeros(c["chunk"] * c["tpf"], bool)
         for f in range(c["chunk"]):
-            vel = 0.9 * vel + 0.1 * rs.randn(3) * 0.01 + np.array([0.0012, 0, 0])
-            pos = pos + vel
-            yaw += 0.003 * rs.randn() + 0.0015
-            x = uu * 1.2
-            y = vv * 0.9
-            wx = x * math.cos(yaw) + pos[0]
-            depth = 5.5 + 4.5 * sum(a * np.sin(fr[0] * (wx + frame * 0.0) + fr[1] * y + p)
-                                    for a, fr, p in zip(amp, freq, phase)) / amp.sum()
-            depth = np.clip(depth, 1.0, 10.0)
-            cam = np.stack([x * depth, y * depth, depth], -1).reshape(-1, 3)
+            t = frame
+            pos = np.array([0.08 * math.sin(two_pi * t / 97) + 0.0002 * t,
+                            0.0125 * math.sin(two_pi * t / 53),
+                            0.025 * math.sin(two_pi * t / 61)]) * sway + rs.randn(3) * 0.0005 * sway
+            yaw = (0.01 * math.sin(two_pi * t / 131) + 0.00025 * rs.randn()) * sway
             cs, sn = math.cos(yaw), math.sin(yaw)
+            depth = np.full_like(x, 5.0)
+            for _it in range(3):      # fixed-point intersection of the pixel rays with the surface
+                wx = cs * x * depth + sn * depth + pos[0]
+                wy = y * depth + pos[1]
+                surf = 5.5 + 4.5 * sum(a * np.sin(fr[0] * wx * 0.5 + fr[1] * wy * 0.5 + p_)
+                                       for a, fr, p_ in zip(amp, freq, phase)) / amp.sum()
+                depth = np.clip(surf, 1.0, 10.0) - pos[2]
+            cam = np.stack([x * depth, y * depth, depth], -1).reshape(-1, 3)
             world = np.stack([cs * cam[:, 0] + sn * cam[:, 2], cam[:, 1], -sn * cam[:, 0] + cs * cam[:, 2]], 1) + pos
             lo = f * c["tpf"] + c["special"]
             pts[lo:lo + ph * pw] = world.astype(np.float32)
@@ -197,7 +203,8 @@ class Stream:
         self.share_counts = False
         self.head_counts = None
         self.attn_events = []
-        self.merge_events = []
+        self.prune_events = []
+        self.query_counts = []       # device scalars: voxels queried by each retrieval of the timed steps
         self.h2d = self.d2h = 0
 
     def _prefetch(self, chunk_idx, pts, mask):
@@ -260,6 +267,8 @@ class Stream:
         if retrieval_due(self.chunk_idx):
             for l in range(L):
                 kv.retrieve_kv(l, return_buf=True)
+            if time_kernels and kv._recent_voxel_ids is not None:
+                self.query_counts.append(kv._recent_voxel_ids[1])
             if self.share_counts and kv._ret is not None:
                 # head-sharded stream: every rank learns the valid pivot count of every head
                 from stac_b200.sharding import gather_head_counts
@@ -270,7 +279,7 @@ class Stream:
         kv.prune_kv()
         if time_kernels:
             e1.record()
-            self.merge_events.append((e0, e1))
+            self.prune_events.append((e0, e1))
         if host_io:
             slot = self.chunk_idx & 1
             self.out_host[slot].copy_(out, non_blocking=True)
@@ -299,6 +308,20 @@ def finish_host_io(stream):
             ev.synchronize()
             stream.out_checksum += float(stream.out_host[slot][0, 0, 0, 0])
             stream.out_landed[slot] = None
+
+
+def bench_config(world, shard_heads, K, W):
+    """The `config` object of the JSON line; the same for both arms at the same N, K, W."""
+    c = CFG
+    return {"workload": WORKLOAD, "frames_per_step": c["chunk"], "streams": 1 if shard_heads else world,
+            "frames_timed": c["chunk"] * K, "frames_before_timed_region": c["chunk"] * (c["prefill_chunks"] + W),
+            "l2_policy": "inputs larger than L2 (hot cache 1.5 GB per stream, rotating q/k/v sets)",
+            "prefill_chunks": c["prefill_chunks"],
+            "masked_keys": "retrieved pivots beyond a head's valid count carry bias -inf; attention FLOPs count "
+                           "all keys, `roofline.live_key_fraction` gives the share that is not masked",
+            "parallelism": (f"1 stream, {c['heads']} heads sharded over {world} ranks (voxel memory sharded by head, "
+                            "NCCL all-gather of per-head retrieval counts)") if shard_heads
+            else f"{world} independent stream(s)"}
 
 
 def max_over_ranks(ms, device=None):
@@ -382,59 +405,102 @@ def run_ours(args):
     time.sleep(0.25)
     launches0 = stac_lib.kernel_launches()
     torch.cuda.nvtx.range_push("timed_steps")      # lets a profiler pick exactly the timed steps
+    stream.kv.stage_trace = []                     # per-stage CUDA events of the timed steps
     ms_dev = run_phase(K, False, True)             # timed, device-resident inputs
     torch.cuda.nvtx.range_pop()
     launches = stac_lib.kernel_launches() - launches0
     clocks = sampler.stop()
+    trace, stream.kv.stage_trace = stream.kv.stage_trace, None
     run_phase(min(W, 3), True, False)              # warm the host path
     ms_e2e = run_phase(K, True, False)             # timed, host buffers
     stream.kv.check_status()
+    copy_gbs = h2d_copy_ceiling(stream, dev)       # the same copies with no compute behind them
 
     n_streams = 1 if shard_heads else world
     value = job_throughput(c["chunk"] * K, ms_dev, n_streams)
     e2e = job_throughput(c["chunk"] * K, ms_e2e, n_streams)
-    # roofline of the dominant kernel pair (attention forward + column sums), per call
-    att_ms, att_fl = [], []
-    for e0, e1, M, N in stream.attn_events:
-        att_ms.append(e0.elapsed_time(e1))
-        att_fl.append(attn_flops(M, N, heads=local_heads))
-    mrg_ms = [e0.elapsed_time(e1) for e0, e1 in stream.merge_events]
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except Exception:
         pass
     peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
-    peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1.4 PFLOP/s sustained"
+    peak_hbm = peaks.get("hbm_gbs", 6650.0)
+    peak_src = "measured (MEASURED_PEAKS.json)" if peaks else "fallback (1.4 PFLOP/s sustained, 6.65 TB/s)"
+    # ---- roofline of the dominant kernel pair (attention forward + column sums), per call
+    att_ms, att_fl = [], []
+    for e0, e1, M, N in stream.attn_events:
+        att_ms.append(e0.elapsed_time(e1))
+        att_fl.append(attn_flops(M, N, heads=local_heads))
     achieved = sum(att_fl) / (sum(att_ms) / 1e3) / 1e12 if att_ms else None
+    # ---- the memory-bound stages, timed inside the same steps
+    prune_ms = [e0.elapsed_time(e1) for e0, e1 in stream.prune_events]
+    stage_ms = {}
+    for name, e0, e1 in trace:
+        stage_ms.setdefault(name, []).append(e0.elapsed_time(e1))
+    LH, D, eb = c["layers"] * local_heads, c["head_dim"], 2
+    T_d = c["chunk"] * c["tpf"]                     # tokens evicted per (layer, head) per steady-state step
+    R = c["retrieval"] * c["tpf"]
+    T_keep = (len(c["pinned"]) + c["window"] + c["hh"]) * c["tpf"]
+    q_counts = [int(t.item()) for t in stream.query_counts]
+    Q = float(np.mean(q_counts)) if q_counts else 0.0
+
+    def mem_roof(stage, nbytes, formula):
+        if stage not in stage_ms:
+            return None
+        ms = float(np.mean(stage_ms[stage]))
+        gbs = nbytes / ms / 1e6
+        return {"kernel": stage, "bytes": int(nbytes), "bytes_formula": formula, "ms": round(ms, 4),
+                "calls": len(stage_ms[stage]), "gbs": round(gbs, 1), "peak": peak_hbm,
+                "frac": round(gbs / peak_hbm, 4), "unit": "GB/s"}
+    roof_mem = {
+        "merge": mem_roof("merge", LH * T_d * (4 * D * eb + 12), "E*(4*D*e+12), E = L*H*T_d evicted tokens"),
+        "retrieve": mem_roof("retrieve", LH * R * (4 * D * eb + 5) + LH * Q * c["piv_cap"] * 12,
+                             "L*H*R*(4*D*e+5) + L*H*Q*P*12, Q = queried voxels"),
+        "compact": mem_roof("compact", LH * T_keep * (4 * D * eb + 24), "L*H*T_keep*(4*D*e+24)"),
+        "h2o_select": mem_roof("h2o_select", LH * (T_keep + T_d) * 8, "L*H*T*(4 read + 4 written)"),
+    }
     info = stream.kv.get_merger_info()
+    ret_valid = None
+    if stream.kv._ret is not None:
+        per_head = stream.kv._ret[2].sum(dim=1).float()
+        ret_valid = {"mean_per_head": round(float(per_head.mean()), 1), "min_per_head": int(per_head.min()),
+                     "of": R, "fraction": round(float(per_head.mean()) / R, 4)}
+    live_frac = None
+    if ret_valid is not None and att_ms:
+        N_full = T_keep + T_d + R
+        live_frac = round((T_keep + T_d + ret_valid["mean_per_head"]) / N_full, 4)
+    h2d_gbs = stream.h2d / (ms_e2e / K) / 1e6 if stream.h2d else None
     line = {
         "metric": METRIC, "value": round(value, 3), "unit": "frames/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms_dev / K, 4), "higher_is_better": True,
         "scaling": "strong" if shard_heads else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames_per_step": c["chunk"], "streams": n_streams,
-                   "l2_policy": "inputs larger than L2 (hot cache 1.5 GB per stream, rotating q/k/v sets)",
-                   "prefill_chunks": c["prefill_chunks"], "parallelism": (f"1 stream, {c['heads']} heads sharded over {world} ranks (voxel memory sharded by head, "
-                                   "NCCL all-gather of per-head retrieval counts)") if shard_heads
-                   else f"{world} independent stream(s)"},
+        "config": bench_config(world, shard_heads, K, W),
         "e2e": {"value": round(e2e, 3), "unit": "frames/s", "h2d_bytes_per_step": stream.h2d,
-                "d2h_bytes_per_step": stream.d2h, "ms_per_step": round(ms_e2e / K, 4)},
+                "d2h_bytes_per_step": stream.d2h, "ms_per_step": round(ms_e2e / K, 4),
+                "h2d_gbs_per_rank": round(h2d_gbs, 1) if h2d_gbs else None,
+                "h2d_copy_only_gbs_per_rank": round(copy_gbs, 1) if copy_gbs else None},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "attn_fwd_fast_kernel + attn_colsum_kernel (one call per layer)",
                      "achieved": round(achieved, 2) if achieved else None, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": round(achieved / peak_tf, 4) if achieved else None, "peak_source": peak_src,
-                     "flops_formula": "(4+2r)*H*M*N*D, r=1", "avg_ms_per_call": round(float(np.mean(att_ms)), 4),
-                     # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one call at this
-                     # shape (M=4164, N=17700), one ncu capture:
-                     # profiles/attention_kernels__stream_shape_M4164_Lk17700.md
+                     "flops_formula": "(4+2r)*H*M*N*D, r=1, N = all keys", "live_key_fraction": live_frac,
+                     "avg_ms_per_call": round(float(np.mean(att_ms)), 4),
+                     # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one call at
+                     # this shape (M=4164, N=17700), one ncu capture
                      "traffic": ATTN_TRAFFIC_BYTES_PER_CALL,
                      "traffic_unit": "bytes per call (fwd 108.4 MB + colsum 45.3 MB; algorithmic 135 MB)"},
-        "stages_ms_per_step": {"attention_24_layers": round(sum(att_ms) / K, 3),
-                               "prune_merge_compact": round(sum(mrg_ms) / K, 3)},
+        "roofline_memory": roof_mem,
+        "stages_ms_per_step": dict({"attention_24_layers": round(sum(att_ms) / K, 3),
+                                    "prune_total": round(sum(prune_ms) / K, 3)},
+                                   **{k_: round(sum(v_) / K, 4) for k_, v_ in stage_ms.items()}),
         "pool": {"voxels": info["used_voxels"], "pivots": info["pivot_pool_used"],
-                 "buffered": info["buffer_pool_used"]},
+                 "buffered": info["buffer_pool_used"], "buffer_slots_max": c["max_buffer_slots"],
+                 "pivot_slots_max": c["max_pivot_slots"], "dropped_tokens": info["dropped_tokens"],
+                 "tokens_evicted": info["token_count"], "retrieved_valid_pivots": ret_valid,
+                 "queried_voxels_mean": round(Q, 1)},
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
@@ -443,6 +509,29 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def h2d_copy_ceiling(stream, dev, reps=3):
+    """GB/s of the e2e leg's host -> device copies (one step's q/k/v, layer by layer, from the same
+    pinned buffers into the same staging set) with no compute behind them: what the host side of
+    this box can deliver to this rank while the other ranks do the same."""
+    import torch
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+    nbytes = sum(t.numel() * 2 for t in stream.host[0])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream.copy_stream):
+        e0.record()
+        for r in range(reps):
+            for l in range(stream.cfg["layers"]):
+                for dst, src in zip(stream.stage[r & 1], stream.host[r % len(stream.host)]):
+                    dst[l].copy_(src[l], non_blocking=True)
+        e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    return nbytes * reps / ms / 1e6 if ms > 0 else None
 
 
 # ------------------------------------------------------------------------------------ microbenchmarks
@@ -537,60 +626,184 @@ def run_microbench_pointmap(args):
                       "config": {"workload": f"point maps {S} x {H} x {W} -> {n_tok} patch points (latency-bound)"}}))
 
 
-def run_microbench_merge(args):
-    """Merge + retrieve on config-3-like shapes (384 pool heads, bf16, T_d tokens per head per
-    step drawn around a smooth surface); prints GB/s with E*(4*D*e+12) algorithmic bytes."""
+def run_config3(args):
+    """Voxel pool stress as the configuration states it: 24 layers x 16 heads x 64 bf16 (384 pool
+    heads), buffer and pivot pools bounded at 1 M slots each, 8 frames (8328 tokens per head)
+    evicted per step with points from the synthetic depth surface, `--steps` steps (512) of merge
+    each followed by retrieval of the top 2048 pivots per head around that step's voxels.
+    Prints one JSON line: median and p95 milliseconds and GB/s (algorithmic bytes) of both calls,
+    pivots formed, tokens dropped by the bounded pool."""
     import torch
     from stac_b200 import ops
     from stac_b200.stac.merger import VoxelKVMerger
     from stac_b200.stac.voxel import BinaryVoxel
     dev = torch.device("cuda", 0)
     c = CFG
-    LH, D, Td = c["layers"] * c["heads"], c["head_dim"], args.m
+    LH, D, Td, R = c["layers"] * c["heads"], c["head_dim"], args.m, 2048
+    slots = args.pool_slots
     st = ops.DeviceStatus(dev)
     vm = BinaryVoxel(c["voxel_size"], dev, status=st)
     mg = VoxelKVMerger(LH, D, init_voxels=c["init_voxels"], pivot_cap=4, budget_cap=8, sim_thresh=0.8,
-                       replace_thresh=0.8, score_thresh=0.2, dtype=torch.bfloat16, device=dev, status=st)
+                       replace_thresh=0.8, score_thresh=0.2, dtype=torch.bfloat16, device=dev, status=st,
+                       max_buffer_slots=slots, max_pivot_slots=slots)
     torch.manual_seed(0)
     n_steps = args.warmup + args.steps
-    chunks = synth_points((n_steps * Td + c["chunk"] * c["tpf"] - 1) // (c["chunk"] * c["tpf"]) + 1, seed=0)
+    per_chunk = c["chunk"] * c["tpf"]
+    chunks = synth_points((n_steps * Td + per_chunk - 1) // per_chunk + 1, seed=0)
     allpts = np.concatenate([p for p, _ in chunks])
     allmask = np.concatenate([m for _, m in chunks])
-    K = (torch.randn(LH, Td, D, device=dev)).to(torch.bfloat16)
-    V = (torch.randn(LH, Td, D, device=dev)).to(torch.bfloat16)
-    times_m, times_r = [], []
+    sets = [((torch.randn(LH, Td, D, device=dev)).to(torch.bfloat16), (torch.randn(LH, Td, D, device=dev)).to(torch.bfloat16),
+             torch.rand(LH, Td, device=dev)) for _ in range(3)]      # rotate: 3 x 0.8 GB > L2
+    times_m, times_r, q_sizes = [], [], []
     for step in range(n_steps):
         pts = torch.from_numpy(allpts[step * Td:(step + 1) * Td]).to(dev)
         msk = torch.from_numpy(allmask[step * Td:(step + 1) * Td]).to(dev)
         ids = vm.upsert_points(pts, msk)
         VX = ids.view(1, -1).expand(LH, -1).contiguous()
-        S = torch.rand(LH, Td, device=dev)
-        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        K, V, S = sets[step % 3]
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         e[0].record()
-        mg.insert_evicted(K, V, S, VX, None, Td, vm.get_voxel_num())
+        mg.insert_evicted(K, V, S, VX, None, Td, vm.voxel_num_bound(), voxel_count_dev=vm._n_dev)
         e[1].record()
         q_ids, q_cnt = vm.neighbor_ids(ids, 2)
-        mg.retrieve_device(q_ids, q_cnt, 2048)
         e[2].record()
+        mg.retrieve_device(q_ids, q_cnt, R)
+        e[3].record()
         torch.cuda.synchronize()
         if step >= args.warmup:
             times_m.append(e[0].elapsed_time(e[1]))
-            times_r.append(e[1].elapsed_time(e[2]))
-    st.raise_if_set("merge microbench")
+            times_r.append(e[2].elapsed_time(e[3]))
+            q_sizes.append(int(q_cnt.item()))
+    st.raise_if_set("voxel pool stress")
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = peaks.get("hbm_gbs", 6650.0)
     E = LH * Td
     bytes_m = E * (4 * D * 2 + 12)
-    bytes_r = LH * 2048 * (4 * D * 2 + 5)
-    # median: pool growth (row arrays re-allocated at x1.5 voxel counts) lands in some steps
-    ms_m, ms_r = float(np.median(times_m)), float(np.median(times_r))
-    print(json.dumps({"metric": "merge_hbm_gbs", "value": round(bytes_m / ms_m / 1e6, 1), "unit": "GB/s",
-                      "ms_per_call": round(ms_m, 4), "retrieve_gbs": round(bytes_r / ms_r / 1e6, 1),
-                      "retrieve_ms": round(ms_r, 4), "steps": args.steps, "merge_ms_all": [round(t, 3) for t in times_m],
-                      "pool": mg.info(),
-                      "config": {"workload": f"merge microbench: 384 pool heads x {Td} evicted tokens/step, bf16, "
-                                             "synthetic smooth surface, retrieve top-2048"}}))
+    bytes_r = LH * R * (4 * D * 2 + 5) + LH * float(np.mean(q_sizes)) * 4 * 12
+    tm, tr = np.array(times_m), np.array(times_r)
+
+    def stats(t, nbytes):
+        med, p95 = float(np.median(t)), float(np.percentile(t, 95))
+        return {"median_ms": round(med, 4), "p95_ms": round(p95, 4), "max_ms": round(float(t.max()), 3),
+                "gbs_at_median": round(nbytes / med / 1e6, 1), "gbs_at_p95": round(nbytes / p95 / 1e6, 1),
+                "frac_of_peak_at_median": round(nbytes / med / 1e6 / peak, 4), "algorithmic_bytes": int(nbytes)}
+    info = mg.info()
+    print(json.dumps({"metric": "voxel_pool_stress_merge_hbm_gbs", "value": stats(tm, bytes_m)["gbs_at_median"],
+                      "unit": "GB/s", "steps": args.steps, "warmup": args.warmup, "peak_gbs": peak,
+                      "merge": stats(tm, bytes_m), "retrieve": stats(tr, bytes_r),
+                      "queried_voxels_mean": round(float(np.mean(q_sizes)), 1),
+                      "pool": {"slots_per_pool": slots, "voxels": info["used_voxels"], "pivots": info["pivot_pool_used"],
+                               "buffered": info["buffer_pool_used"], "tokens_evicted": info["token_count"],
+                               "dropped_tokens": info["dropped_tokens"]},
+                      "config": {"workload": f"config3 voxel pool stress: 384 pool heads x {Td} evicted tokens/step, bf16, "
+                                             f"pools bounded at {slots} slots, synthetic depth surface, retrieve top-{R} "
+                                             "per head after every merge"}}))
 
 
 # ------------------------------------------------------------------------------------ CPU arm
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+CPU_SAMPLE = (2, 4)      # (layers, heads) of the stream that the CPU arms run: 8 of the 384 (layer, head) rows
+
+
+def _reference_available():
+    return os.path.isfile(os.path.join(REF_DIR, "stac", "stac_voxel.py"))
+
+
+class ReferenceCpuStream:
+    """The reference's OWN manager (stac/stac_voxel.py STACVoxelKV with voxel_backend="python",
+    allocator="segment", seg_size=1, device="cpu", fp32: its CPU torch path) driven through one
+    chunk at a time on a subset of (layers, heads).  The reference has no CPU attention (its
+    decode_sparse_attn asserts CUDA, stac/stac_voxel.py:217), so the attention is the fp32 torch
+    computation of its own self-check (stac/flash_attn_triton.py:1018-1036) and the column sums
+    are handed to its _update_scores exactly as decode_sparse_attn does (stac/stac_voxel.py:252-265)."""
+
+    kind = "reference"
+
+    def __init__(self, n_layers, n_heads, seed=0):
+        import logging
+        import torch
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        logging.disable(logging.INFO)
+        from stac.stac_voxel import STACVoxelKV
+        c = CFG
+        self.torch, self.L, self.H = torch, n_layers, n_heads
+        torch.set_num_threads(os.cpu_count() or 1)
+        self.threads = torch.get_num_threads()
+        buffer_size = c["chunk"] + len(c["pinned"]) + c["window"] + c["hh"]
+        self.kv = STACVoxelKV(num_layers=n_layers, num_heads=n_heads, head_dim=c["head_dim"],
+                              token_per_frame=c["tpf"], buffer_size=buffer_size, chunk_size=c["chunk"],
+                              recent_size=c["window"], pinned_idx=list(c["pinned"]), hh_size=c["hh"],
+                              temperature=c["temperature"], device=torch.device("cpu"), dtype=torch.float32,
+                              voxel_size=c["voxel_size"], init_voxels=c["init_voxels"], voxel_buf_cap=c["buf_cap"],
+                              voxel_piv_cap=c["piv_cap"], voxel_backend="python", sim_threshold=0.8,
+                              replace_threshold=0.8, score_threshold=0.2, slab_growth=1024, slab_cap=10000,
+                              seg_size=1, retrieval_size=c["retrieval"], allocator="segment", attn_backend="cuda")
+        self.kv.reset()
+        self.points = synth_points(64, seed=seed)
+        self.gen = torch.Generator().manual_seed(seed)
+        self.chunk = 0
+
+    def step(self):
+        torch, kv, c = self.torch, self.kv, CFG
+        Tq, D, H = c["chunk"] * c["tpf"], c["head_dim"], self.H
+        pts, mask = self.points[self.chunk % len(self.points)]
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            for l in range(self.L):
+                q = torch.randn(H, Tq, D, generator=self.gen) / 2
+                k = torch.randn(1, H, Tq, D, generator=self.gen) / 2
+                v = torch.randn(1, H, Tq, D, generator=self.gen) / 8
+                kv.append_kv(k, v, l)
+                T = kv._offset_hot[l]
+                K_all, V_all = kv.key_cache_hot[l][:, :T], kv.value_cache_hot[l][:, :T]
+                T_ret = kv._offset_retrieval[l]
+                scores = None
+                if T_ret > 0:
+                    K_all = torch.cat([K_all, kv.key_cache_retrieval[l][:, :T_ret]], 1)
+                    V_all = torch.cat([V_all, kv.value_cache_retrieval[l][:, :T_ret]], 1)
+                scores = torch.matmul(q, K_all.transpose(1, 2)) * (D ** -0.5)
+                if T_ret > 0:
+                    scores[:, :, T:] += kv._bias_retrieval[l][:, None, :T_ret]
+                attn = torch.softmax(scores, dim=-1)
+                colsum = attn.sum(dim=1)                    # [H, T + T_ret]
+                _ = torch.matmul(attn, V_all)
+                kv._last_query_offset[l] = Tq
+                kv._update_scores(colsum[None, :, None, :T], l)
+                del scores, attn
+            kv.append_positions(torch.from_numpy(pts), torch.from_numpy(mask))
+            if retrieval_due(self.chunk):
+                for l in range(self.L):
+                    kv.retrieve_kv(l, return_buf=True)
+            kv.prune_kv()
+        self.chunk += 1
+        return time.perf_counter() - t0
+
+
+class PortCpuStream:
+    """Same sample through the numpy restatement of that path (oracle/), used when the staged
+    reference sources (oracle/_ref) are absent."""
+
+    kind = "port"
+
+    def __init__(self, n_layers, n_heads, seed=0):
+        self.n_layers, self.n_heads, self.state, self.seed = n_layers, n_heads, None, seed
+        self.threads = os.cpu_count() or 1
+
+    def step(self):
+        dt, self.state = cpu_step_sample(self.n_layers, self.n_heads, self.state, seed=self.seed)
+        return dt
+
+
+def cpu_stream():
+    n_layers, n_heads = CPU_SAMPLE
+    return ReferenceCpuStream(n_layers, n_heads) if _reference_available() else PortCpuStream(n_layers, n_heads)
+
+
 def cpu_step_sample(n_layers, n_heads, state=None, seed=0):
     """One chunk of the same workload through the CPU oracle on a subset of (layers, heads);
     returns seconds and the state for the next chunk."""
@@ -634,58 +847,67 @@ def cpu_step_sample(n_layers, n_heads, state=None, seed=0):
     return dt, state
 
 
+def _cpu_record(st, seconds, n_steps):
+    """Fields common to `cpu_baseline` and the reference arm: what was measured and how it is scaled."""
+    n_layers, n_heads = CPU_SAMPLE
+    rows, all_rows = n_layers * n_heads, CFG["layers"] * CFG["heads"]
+    scale = all_rows / rows
+    fps = CFG["chunk"] * n_steps / (seconds * scale)
+    what = ("the reference's own manager (stac/stac_voxel.py, voxel_backend=python, allocator=segment, fp32, CPU) "
+            "with the fp32 torch attention of its self-check" if st.kind == "reference"
+            else "numpy restatement of the reference's Python path (oracle/); oracle/_ref was not staged")
+    return {"value": round(fps, 5), "unit": "frames/s", "cores": st.threads, "host_cpus": os.cpu_count(),
+            "kind": st.kind, "sample_rows": rows, "all_rows": all_rows, "scale_factor": scale,
+            "sample_seconds_measured": round(seconds, 3), "sample_steps": n_steps,
+            "sample": f"{n_steps} steady-state chunks of {n_layers} layer x {n_heads} heads ({rows} of the {all_rows} "
+                      f"(layer, head) rows, which are independent); measured {seconds:.2f} s, scaled x{scale:.0f} "
+                      f"to the full stream; {what}; torch/BLAS threads = {st.threads}"}
+
+
 def cpu_baseline(sample_seconds=15.0):
-    """The oracle (a port of the reference's CPU torch path) on this host, on a bounded sample:
-    1 of 24 layers and 2 of 16 heads of the same stream, steady-state chunks; throughput is
-    scaled by the sampled fraction of (layer, head) rows."""
-    n_layers, n_heads = 1, 2
-    state = None
+    """The reference's CPU path on this host on a bounded sample of the same stream (see
+    ReferenceCpuStream); throughput is scaled by the sampled fraction of (layer, head) rows."""
+    st = cpu_stream()
     for _ in range(5):            # reach the pruning regime (untimed)
-        _, state = cpu_step_sample(n_layers, n_heads, state)
+        st.step()
     t, n = 0.0, 0
     while t < sample_seconds and n < 8:
-        dt, state = cpu_step_sample(n_layers, n_heads, state)
-        t += dt
+        t += st.step()
         n += 1
-    frac = (n_layers * n_heads) / (CFG["layers"] * CFG["heads"])
-    fps = CFG["chunk"] * n / t * frac
-    return {"value": round(fps, 5), "unit": "frames/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{n} steady-state chunks of {n_layers} layer x {n_heads} heads "
-                      f"({frac:.4f} of the 384 rows), scaled to the full stream; numpy BLAS threads = all cores"}
+    return _cpu_record(st, t, n)
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    K, W = args.steps, max(args.warmup, 1)
-    n_layers, n_heads = 1, 2
-    state = None
-    for _ in range(4 + W):
-        _, state = cpu_step_sample(n_layers, n_heads, state)
+    K, W = args.steps, max(args.warmup, 3)
+    st = cpu_stream()
+    for _ in range(4 + min(W, 3)):
+        st.step()
     t = 0.0
     for _ in range(K):
-        dt, state = cpu_step_sample(n_layers, n_heads, state)
-        t += dt
-    frac = (n_layers * n_heads) / (CFG["layers"] * CFG["heads"])
-    fps = CFG["chunk"] * K / t * frac
-    sample = (f"each step = one steady-state chunk of {n_layers} layer x {n_heads} heads ({frac:.4f} of the rows), "
-              "throughput scaled to the full stream")
-    line = {"impl": "reference", "metric": METRIC, "value": round(fps, 5), "unit": "frames/s",
-            "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": K, "warmup": W,
-            "ms_per_step": round(t / K * 1e3 / frac, 2), "higher_is_better": True, "scaling": "weak",
+        t += st.step()
+    rec = _cpu_record(st, t, K)
+    shard_heads = args.shard == "heads" and world > 1
+    line = {"impl": "reference", "metric": METRIC, "value": rec["value"], "unit": "frames/s",
+            "n_gpus": world, "steps": K, "warmup": W,
+            # one step of the FULL workload at this rate (the sampled rows' seconds x scale_factor)
+            "ms_per_step": round(t / K * 1e3 * rec["scale_factor"], 2),
+            "ms_per_step_measured_on_sample": round(t / K * 1e3, 2),
+            "higher_is_better": True, "scaling": "strong" if shard_heads else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "frames_per_step": CFG["chunk"]},
-            "cpu_baseline": {"value": round(fps, 5), "unit": "frames/s", "cores": os.cpu_count(), "kind": "port",
-                             "sample": sample},
-            "e2e": {"value": round(fps, 5), "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "config": bench_config(world, shard_heads, K, W),
+            "cpu_baseline": rec,
+            "e2e": {"value": rec["value"], "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -693,17 +915,21 @@ if __name__ == "__main__":
                     help="N > 1: one independent stream per GPU (default, weak scaling) or ONE stream whose heads "
                          "and voxel memory are sharded over the GPUs (strong scaling)")
     ap.add_argument("--microbench", default=None, choices=["attn", "merge", "pointmap"],
-                    help="kernel microbenchmarks used for profiling (not the headline line)")
+                    help="kernel microbenchmarks used for profiling (not the headline line); `merge` is the "
+                         "voxel pool stress configuration (512 steps unless --steps is given)")
+    ap.add_argument("--pool-slots", type=int, default=1_000_000, help="pool stress: slots of each bounded pool")
     ap.add_argument("--lk", type=int, default=10376, help="attention microbench: number of keys")
     ap.add_argument("--m", type=int, default=None, help="microbench: query rows (attn) / evicted tokens per head (merge)")
     ap.add_argument("--pivots", type=int, default=0, help="attention microbench: keys carrying a bias")
     a = ap.parse_args()
+    if a.steps is None:
+        a.steps = 512 if a.microbench == "merge" else 8
     if a.microbench == "attn":
         a.m = a.m or 1041
         run_microbench_attn(a)
     elif a.microbench == "merge":
         a.m = a.m or 8328
-        run_microbench_merge(a)
+        run_config3(a)
     elif a.microbench == "pointmap":
         run_microbench_pointmap(a)
     elif a.impl == "reference":

@@ -152,6 +152,24 @@ int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t 
                    int64_t cache_head_stride, int64_t* token_idx, int64_t idx_head_stride, int H, int T_new,
                    int old_T, int64_t first_token_id, int head_dim, int elem_bytes, stac_stream_t stream);
 
+/* The epilogue of SparseAttention's QKV projection fused with append_kv
+ * (causalvggt/layers/attention.py:119-128 and :141; LayerNorm = q_norm / k_norm over the head
+ * dimension, causalvggt/layers/rope.py:148-188 for the 2-D rotary embedding).  qkv is the bf16
+ * projection output [T_new][3][H][64] (tokens qkv_token_stride elements apart).  q and k get
+ * LayerNorm in fp32 (weights / biases f32 [64]; pass NULL, NULL to skip) and the rotary embedding
+ * from the caller's tables cos_table / sin_table f32 [n_pos][16] (the reference's frequency
+ * cache for feature dimension 32: angle = position * 100^(-j/16); NULL to skip) at the integer
+ * positions pos i64 [T_new][2] = (y, x); results are rounded to bf16.  q goes to q_out
+ * [T_new][H][64] (rows q_out_row_stride apart), k and v to positions [old_T, old_T + T_new) of the
+ * cache [H][cache_head_stride] and the token ids first_token_id + t to token_idx, as
+ * stac_append_kv does.  head_dim is 64. */
+int stac_qkv_epilogue_append(const void* qkv, int64_t qkv_token_stride, const float* q_norm_w, const float* q_norm_b,
+                             const float* k_norm_w, const float* k_norm_b, float eps, const int64_t* pos,
+                             const float* cos_table, const float* sin_table, int n_pos, void* q_out,
+                             int64_t q_out_row_stride, void* k_cache, void* v_cache, int64_t cache_head_stride,
+                             int64_t* token_idx, int64_t idx_head_stride, int H, int T_new, int old_T,
+                             int64_t first_token_id, stac_stream_t stream);
+
 /* HeavyHittersKV._update_scores (stac/h2o.py:177-216) for one layer: s = colsum * T_live / Tq;
  * positions >= old_T take s, older ones score * temperature + s; counts += 1. */
 int stac_scores_update(const float* colsum, int64_t colsum_head_stride, float* scores, float* counts,
@@ -192,6 +210,7 @@ enum stac_meta_index {       /* int32 counters in device memory, pool->meta[STAC
   STAC_META_BUF_USED = 4,    /* tokens currently buffered */
   STAC_META_PIV_USED = 5,    /* pivots currently stored */
   STAC_META_DROPPED = 6,     /* tokens dropped because a bounded pool was full (cumulative) */
+  STAC_META_VOXELS = 7,      /* voxels in the table at the last insert (when pool->voxel_count is given) */
   STAC_META_SIZE = 8
 };
 
@@ -211,6 +230,10 @@ typedef struct stac_pool {
   void* over_K_out; void* over_V_out; float* over_S_out; int* over_hv_out; int* over_start_out;
   int over_cap;
   int* meta;
+  /* optional device scalar with the current number of voxels: an insert copies it to
+   * meta[STAC_META_VOXELS], so that a host which passes only an upper bound as voxel_used (to
+   * avoid reading the count back before the call) still learns the exact figure later */
+  const int* voxel_count;
 } stac_pool;
 
 typedef struct stac_evicted {

@@ -29,6 +29,7 @@ class StacPool(ctypes.Structure):
         ("over_hv_out", c_void_p), ("over_start_out", c_void_p),
         ("over_cap", c_int),
         ("meta", c_void_p),
+        ("voxel_count", c_void_p),
     ]
 
 
@@ -44,7 +45,8 @@ class StacEvicted(ctypes.Structure):
     ]
 
 
-META_BUF_TOP, META_BUF_FREE_LEN, META_PIV_TOP, META_OVER_COUNT, META_BUF_USED, META_PIV_USED, META_DROPPED = range(7)
+(META_BUF_TOP, META_BUF_FREE_LEN, META_PIV_TOP, META_OVER_COUNT, META_BUF_USED, META_PIV_USED, META_DROPPED,
+ META_VOXELS) = range(8)
 META_SIZE = 8
 VOXEL_MAX_POINTS = 16384
 
@@ -71,6 +73,9 @@ SIGNATURES = {
                                      c_i64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "stac_append_kv": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_void_p, c_void_p, c_i64, c_void_p,
                                c_i64, c_int, c_int, c_int, c_i64, c_int, c_int, c_void_p]),
+    "stac_qkv_epilogue_append": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_f32, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_void_p, c_i64, c_void_p, c_void_p, c_i64,
+                                         c_void_p, c_i64, c_int, c_int, c_int, c_i64, c_void_p]),
     "stac_scores_update": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_int, c_int, c_int, c_int, c_f32,
                                    c_void_p]),
     "stac_h2o_select": (c_int, [c_void_p, c_i64, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
@@ -90,7 +95,7 @@ SIGNATURES = {
 KERNELS_PER_CALL = {
     "stac_attn_colsum": 3, "stac_attn_colsum_noalloc": 3, "stac_selftest_bounded_wait": 1,
     "stac_voxel_hash_clear": 1, "stac_voxel_rehash": 2, "stac_voxel_upsert": 3, "stac_voxel_neighbors": 2, "stac_pointmap_to_positions": 1,
-    "stac_append_kv": 1, "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 16, "stac_retrieve": 2,
+    "stac_append_kv": 1, "stac_qkv_epilogue_append": 1, "stac_scores_update": 1, "stac_h2o_select": 1, "stac_compact": 2, "stac_merge_insert": 16, "stac_retrieve": 2,
 }
 CALLS = {}
 

@@ -54,7 +54,7 @@ const char* stac_status_string(int status) {
   }
 }
 
-int stac_abi_version(void) { return 1; }
+int stac_abi_version(void) { return 2; }
 
 size_t stac_attn_workspace_bytes(int M, int H) {
   if (M <= 0 || H <= 0) return 0;

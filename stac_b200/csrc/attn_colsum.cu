@@ -34,10 +34,18 @@ static_assert(128 * 40 + 256 * 232 <= kFwdThreads * ((65536 / kFwdThreads) / 8 *
 constexpr int kColGroup = 3;           // key tiles per item = exponent warpgroups of the column-sum kernel
 constexpr int kColStages = kColGroup == 4 ? 3 : 4;
 constexpr int kColThreads = 128 + kColGroup * 128;   // warpgroup 0 control (warp 0 TMA, warp 1 MMA issue), then exponent
-#ifndef STAC_COL_POLY_MASK
-#define STAC_COL_POLY_MASK 0x8888
+#ifndef STAC_COL_PAIR_MASK
+#define STAC_COL_PAIR_MASK 0x88
 #endif
-constexpr unsigned kColPolyMask = STAC_COL_POLY_MASK;   // which of 16 consecutive exponentials of the column-sum kernel run on the FMA pipes
+constexpr unsigned kColPairMask = STAC_COL_PAIR_MASK;   // which of 8 consecutive PAIRS of exponentials of the column-sum kernel run on the FMA pipes
+#ifndef STAC_COL_FOLD_LSE
+#define STAC_COL_FOLD_LSE 1
+#endif
+// 1: the row term -lse2[m] of the exponent is added to the score tile by the tensor core (a fifth
+// K = 16 step whose operands are a tile of ones and the row values split into three bf16), so the
+// exponent warps read nothing from shared memory; 0: they read it per score (LDS.128 per four).
+constexpr bool kColFoldLse = STAC_COL_FOLD_LSE != 0;
+constexpr int kColXBytes = 128 * 32;   // 128 rows x 16 bf16, no swizzle: [16 row groups][2 K chunks][8 rows][16 B]
 constexpr int kColCtlRegs = 56;
 constexpr int kColExpRegs = kColGroup == 4 ? 104 : 152;
 // setmaxnreg only moves registers inside the CTA's allocation, which is fixed at launch to
@@ -429,10 +437,10 @@ constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 constexpr int kPartFloats = kBM * kD + 2 * kBM; // one partial result: O[128][64], row sums, row references
 constexpr int kFastMaxCtas = 160;               // partial-result slots are provided for this many CTAs
 constexpr int kFastMinSplitTiles = 8;           // shorter key ranges run one CTA per item
-#ifndef STAC_FAST_POLY_MASK
-#define STAC_FAST_POLY_MASK 0x80808080u
+#ifndef STAC_FAST_PAIR_MASK
+#define STAC_FAST_PAIR_MASK 0x8080u
 #endif
-constexpr unsigned kFastPolyMask = STAC_FAST_POLY_MASK;   // which of 32 consecutive exponentials run on the FMA pipes
+constexpr unsigned kFastPairMask = STAC_FAST_PAIR_MASK;   // which of 16 consecutive PAIRS of exponentials run on the FMA pipes
 constexpr int kFastCtlRegs = 56, kFastSoftmaxRegs = 152;   // setmaxnreg targets; must fit the launch allocation
 static_assert(128 * kFastCtlRegs + 384 * kFastSoftmaxRegs <= kFastThreads * ((65536 / kFastThreads) / 8 * 8),
               "fast forward kernel: setmaxnreg targets exceed the CTA's register allocation");
@@ -491,34 +499,40 @@ struct FwdWalk {
   }
 };
 
-// kN scores -> kN probabilities relative to the row reference, packed as bf16 pairs.  The
-// elements whose bit is set in kFastPolyMask take their exponential on the FMA pipes (cubic,
+// kN scores -> kN probabilities relative to the row reference, packed as bf16 pairs.  Scores
+// are handled two at a time with the packed fp32 instructions (scale-and-subtract, row sums).
+// The pairs whose bit is set in kFastPairMask take their exponentials on the FMA pipes (cubic,
 // 8.6e-5 relative, far below the bf16 rounding of P) to relieve the exponential unit.
-template <int kE>
-__device__ __forceinline__ float fast_exp_one(float x) {
-  return ((kFastPolyMask >> (kE & 31)) & 1u) ? poly_exp2(x) : fast_exp2(x);
+template <int kJ>
+__device__ __forceinline__ uint64_t fast_exp_pair(uint64_t x2) {
+  if ((kFastPairMask >> (kJ & 15)) & 1u) return poly_exp2_x2(x2);
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  return pack_f32x2(fast_exp2(x0), fast_exp2(x1));
 }
 template <bool kBias, int kN, int kI = 0>
 __device__ __forceinline__ void fast_exp_chunk(const uint32_t (&s)[32], uint32_t (&pk)[16], const float* bias2,
-                                               float c2, float m_ref, float& l0, float& l1) {
+                                               uint64_t c2c2, uint64_t negm2, uint64_t& l0, uint64_t& l1) {
   if constexpr (kI < kN) {
-    float e0, e1, e2, e3;
+    uint64_t x0 = pack_f32x2(__uint_as_float(s[kI + 0]), __uint_as_float(s[kI + 1]));
+    uint64_t x1 = pack_f32x2(__uint_as_float(s[kI + 2]), __uint_as_float(s[kI + 3]));
     if (kBias) {
-      e0 = fast_exp_one<kI + 0>(fmaf(__uint_as_float(s[kI + 0]), c2, bias2[kI + 0]) - m_ref);
-      e1 = fast_exp_one<kI + 1>(fmaf(__uint_as_float(s[kI + 1]), c2, bias2[kI + 1]) - m_ref);
-      e2 = fast_exp_one<kI + 2>(fmaf(__uint_as_float(s[kI + 2]), c2, bias2[kI + 2]) - m_ref);
-      e3 = fast_exp_one<kI + 3>(fmaf(__uint_as_float(s[kI + 3]), c2, bias2[kI + 3]) - m_ref);
+      const float4 b = *reinterpret_cast<const float4*>(bias2 + kI);
+      x0 = add_f32x2(fma_f32x2(x0, c2c2, pack_f32x2(b.x, b.y)), negm2);
+      x1 = add_f32x2(fma_f32x2(x1, c2c2, pack_f32x2(b.z, b.w)), negm2);
     } else {
-      e0 = fast_exp_one<kI + 0>(fmaf(__uint_as_float(s[kI + 0]), c2, -m_ref));
-      e1 = fast_exp_one<kI + 1>(fmaf(__uint_as_float(s[kI + 1]), c2, -m_ref));
-      e2 = fast_exp_one<kI + 2>(fmaf(__uint_as_float(s[kI + 2]), c2, -m_ref));
-      e3 = fast_exp_one<kI + 3>(fmaf(__uint_as_float(s[kI + 3]), c2, -m_ref));
+      x0 = fma_f32x2(x0, c2c2, negm2);
+      x1 = fma_f32x2(x1, c2c2, negm2);
     }
-    l0 += e0 + e1;
-    l1 += e2 + e3;
-    pk[kI / 2] = pack_bf16x2(e0, e1);
-    pk[kI / 2 + 1] = pack_bf16x2(e2, e3);
-    fast_exp_chunk<kBias, kN, kI + 4>(s, pk, bias2, c2, m_ref, l0, l1);
+    const uint64_t e0 = fast_exp_pair<kI / 2>(x0), e1 = fast_exp_pair<kI / 2 + 1>(x1);
+    l0 = add_f32x2(l0, e0);
+    l1 = add_f32x2(l1, e1);
+    float a0, a1, a2, a3;
+    unpack_f32x2(e0, a0, a1);
+    unpack_f32x2(e1, a2, a3);
+    pk[kI / 2] = pack_bf16x2(a0, a1);
+    pk[kI / 2 + 1] = pack_bf16x2(a2, a3);
+    fast_exp_chunk<kBias, kN, kI + 4>(s, pk, bias2, c2c2, negm2, l0, l1);
   }
 }
 
@@ -709,6 +723,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int row = wq * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const float c2 = p.scale_log2;
+    const uint64_t c2c2 = pack_f32x2(c2, c2);
     const float* bias2 = sm.bias2[g];
     uint32_t ra[32], rb[32], pk[16];
     bool overflow = false;
@@ -720,7 +735,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int len = t1 - t0;
       const int sb = seg & 1;
       float m_ref = 0.f;
-      float l0 = 0.f, l1 = 0.f;
+      uint64_t l0 = 0ull, l1 = 0ull;    // four partial row sums, two per register pair
+      uint64_t negm2 = 0ull;            // (-m_ref, -m_ref)
       bool have_ref = false;
       bool any_live = false;  // some key tile of this warpgroup in this segment had a key that is not masked
       bool fetching = false;  // the first 32 scores of the next tile are already on their way into ra
@@ -796,22 +812,23 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_wait(&sm.ref_ready[sb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
             m_ref = sm.m_ref[sb][row];
           }
+          negm2 = pack_f32x2(-m_ref, -m_ref);
         }
         // keys 0..31 are on their way into ra
         tmem_ld_wait();
         tmem_ld32(s_addr + 32, rb);
-        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
-        else fast_exp_chunk<false, 32>(ra, pk, bias2, c2, m_ref, l0, l1);
+        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
+        else fast_exp_chunk<false, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
         tmem_st16(s_addr, pk);
         tmem_ld_wait();
         tmem_ld32(s_addr + 64, ra);
-        if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
-        else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2, m_ref, l0, l1);
+        if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2c2, negm2, l0, l1);
+        else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2c2, negm2, l0, l1);
         tmem_st16(s_addr + 16, pk);
         tmem_ld_wait();
         tmem_ld16(s_addr + 96, rb);
-        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
-        else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2, m_ref, l0, l1);
+        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
+        else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
         tmem_st16(s_addr + 32, pk);
         tmem_ld_wait();
         // this warpgroup's next tile of the segment is normally scored by now: start fetching it
@@ -825,8 +842,8 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tmem_ld32(tmem + lane_base + b2 * kFT, ra);
           fetching = true;
         }
-        if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
-        else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2, m_ref, l0, l1);
+        if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2c2, negm2, l0, l1);
+        else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2c2, negm2, l0, l1);
         tmem_st8(s_addr + 48, pk);
         if (more && !fetching && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
           tc_fence_after();                  // second chance, a chunk later
@@ -838,7 +855,10 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive(&sm.p_full[b]);
       }
       // ---- end of the segment
-      const float lsum = l0 + l1;
+      float la, lb, lc, ld;
+      unpack_f32x2(l0, la, lb);
+      unpack_f32x2(l1, lc, ld);
+      const float lsum = (la + lb) + (lc + ld);
       overflow = overflow || !(lsum <= kFastRowSumLimit);   // also true for NaN
       if (g != 0) {
         sm.lpart[sb][g - 1][row] = lsum;
@@ -994,8 +1014,11 @@ struct ColSmem {
   uint64_t q_empty[kColStages];
   uint64_t s_full[2];
   uint64_t s_free[2];
+  uint64_t x_full[kColStages];            // the row-term operand of a query stage is written
   uint32_t tmem_base;
-  alignas(16) float lse2[4];  // flexible: n_q_tiles * 128 floats follow (negated, one head)
+  alignas(16) uint8_t ax[kColXBytes];     // ones in K columns 0..2, same for every key
+  alignas(16) uint8_t bx[kColStages][kColXBytes];   // per query row: -lse2 / c2 as hi, mid, lo bf16
+  alignas(16) float lse2[4];  // (without the fold) flexible: n_q_tiles * 128 floats follow (negated, one head)
 };
 
 struct ColParams {
@@ -1043,46 +1066,35 @@ struct ColWalk {
   }
 };
 
-// 32 scores of one key against 32 query rows: sum of exp2(score * c2 - lse2[row]).
-__device__ __forceinline__ void col_exp_chunk(const uint32_t (&s)[32], const float4* nl4, float c2, float& a0,
-                                              float& a1, float& a2, float& a3) {
-#pragma unroll
-  for (int q4 = 0; q4 < 8; ++q4) {
-    const float4 nl = nl4[q4];
-    a0 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 0]), c2, nl.x));
-    a1 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 1]), c2, nl.y));
-    a2 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 2]), c2, nl.z));
-    a3 += fast_exp2(fmaf(__uint_as_float(s[q4 * 4 + 3]), c2, nl.w));
+// 16 scores of one key against 16 query rows: sum of exp2(score * c2 - lse2[row]), two rows at
+// a time with the packed fp32 instructions.  The pairs whose bit is set in kColPairMask take
+// their exponentials on the FMA pipes (cubic, 8.6e-5 relative): the exponential unit is the
+// bottleneck of this kernel.
+template <int kJ>
+__device__ __forceinline__ uint64_t col_exp_pair(uint64_t s2, uint64_t c2c2, float n0, float n1) {
+  const uint64_t x2 = kColFoldLse ? mul_f32x2(s2, c2c2) : fma_f32x2(s2, c2c2, pack_f32x2(n0, n1));
+  if ((kColPairMask >> kJ) & 1u) return poly_exp2_x2(x2);
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  return pack_f32x2(fast_exp2(x0), fast_exp2(x1));
+}
+__device__ __forceinline__ void col_exp_chunk16(const uint32_t (&s)[32], const float4* nl4, uint64_t c2c2, uint64_t& a01,
+                                                uint64_t& a23) {
+  float4 n0, n1, n2, n3;
+  if (kColFoldLse) {
+    n0 = n1 = n2 = n3 = make_float4(0.f, 0.f, 0.f, 0.f);
+  } else {
+    n0 = nl4[0]; n1 = nl4[1]; n2 = nl4[2]; n3 = nl4[3];
   }
-}
-
-// 16 scores of one key against 16 query rows: sum of exp2(score * c2 - lse2[row]).  The rows
-// whose bit is set in kColPolyMask take their exponential on the FMA pipes (cubic, 8.6e-5
-// relative): the exponential unit is the bottleneck of this kernel and its issue slots are half
-// empty.
-template <int kE>
-__device__ __forceinline__ float col_exp_one(float x) {
-  return ((kColPolyMask >> kE) & 1) ? poly_exp2(x) : fast_exp2(x);
-}
-__device__ __forceinline__ void col_exp_chunk16(const uint32_t (&s)[32], const float4* nl4, float c2, float& a0,
-                                                float& a1, float& a2, float& a3) {
-  const float4 n0 = nl4[0], n1 = nl4[1], n2 = nl4[2], n3 = nl4[3];
-  a0 += col_exp_one<0>(fmaf(__uint_as_float(s[0]), c2, n0.x));
-  a1 += col_exp_one<1>(fmaf(__uint_as_float(s[1]), c2, n0.y));
-  a2 += col_exp_one<2>(fmaf(__uint_as_float(s[2]), c2, n0.z));
-  a3 += col_exp_one<3>(fmaf(__uint_as_float(s[3]), c2, n0.w));
-  a0 += col_exp_one<4>(fmaf(__uint_as_float(s[4]), c2, n1.x));
-  a1 += col_exp_one<5>(fmaf(__uint_as_float(s[5]), c2, n1.y));
-  a2 += col_exp_one<6>(fmaf(__uint_as_float(s[6]), c2, n1.z));
-  a3 += col_exp_one<7>(fmaf(__uint_as_float(s[7]), c2, n1.w));
-  a0 += col_exp_one<8>(fmaf(__uint_as_float(s[8]), c2, n2.x));
-  a1 += col_exp_one<9>(fmaf(__uint_as_float(s[9]), c2, n2.y));
-  a2 += col_exp_one<10>(fmaf(__uint_as_float(s[10]), c2, n2.z));
-  a3 += col_exp_one<11>(fmaf(__uint_as_float(s[11]), c2, n2.w));
-  a0 += col_exp_one<12>(fmaf(__uint_as_float(s[12]), c2, n3.x));
-  a1 += col_exp_one<13>(fmaf(__uint_as_float(s[13]), c2, n3.y));
-  a2 += col_exp_one<14>(fmaf(__uint_as_float(s[14]), c2, n3.z));
-  a3 += col_exp_one<15>(fmaf(__uint_as_float(s[15]), c2, n3.w));
+  auto sp = [&](int i) { return pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])); };
+  a01 = add_f32x2(a01, col_exp_pair<0>(sp(0), c2c2, n0.x, n0.y));
+  a23 = add_f32x2(a23, col_exp_pair<1>(sp(2), c2c2, n0.z, n0.w));
+  a01 = add_f32x2(a01, col_exp_pair<2>(sp(4), c2c2, n1.x, n1.y));
+  a23 = add_f32x2(a23, col_exp_pair<3>(sp(6), c2c2, n1.z, n1.w));
+  a01 = add_f32x2(a01, col_exp_pair<4>(sp(8), c2c2, n2.x, n2.y));
+  a23 = add_f32x2(a23, col_exp_pair<5>(sp(10), c2c2, n2.z, n2.w));
+  a01 = add_f32x2(a01, col_exp_pair<6>(sp(12), c2c2, n3.x, n3.y));
+  a23 = add_f32x2(a23, col_exp_pair<7>(sp(14), c2c2, n3.z, n3.w));
 }
 
 // All half tiles of one item for one key (thread): returns the sum over the item's query rows.
@@ -1094,13 +1106,15 @@ template <bool kFast>
 __device__ __forceinline__ float col_item_sum(ColSmem& sm, const ColParams& p, uint32_t t_base, const float* nl_item,
                                               int n_half, int& ui, float c2, float b2_in) {
   uint32_t ra[32], rb[32];   // 16 registers of each are used
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  float a0 = 0.f;
+  uint64_t a01 = 0ull, a23 = 0ull;
+  const uint64_t c2c2 = pack_f32x2(c2, c2);
   auto consume = [&](const uint32_t (&r)[32], const float* nl) {
     if (kFast) {
-      col_exp_chunk16(r, reinterpret_cast<const float4*>(nl), c2, a0, a1, a2, a3);
+      col_exp_chunk16(r, reinterpret_cast<const float4*>(nl), c2c2, a01, a23);
     } else {
 #pragma unroll
-      for (int q = 0; q < 16; ++q) a0 += fast_exp2(fmaf(__uint_as_float(r[q]), c2, b2_in + nl[q]));
+      for (int q = 0; q < 16; ++q) a0 += fast_exp2(fmaf(__uint_as_float(r[q]), c2, kColFoldLse ? b2_in : b2_in + nl[q]));
     }
   };
   // first half tile of the item: nothing is in flight yet
@@ -1134,7 +1148,10 @@ __device__ __forceinline__ float col_item_sum(ColSmem& sm, const ColParams& p, u
     tc_fence_before();
     mbar_arrive(&sm.s_free[g]);
   }
-  return (a0 + a1) + (a2 + a3);
+  float b0, b1, b2, b3;
+  unpack_f32x2(a01, b0, b1);
+  unpack_f32x2(a23, b2, b3);
+  return a0 + ((b0 + b1) + (b2 + b3));
 }
 
 __global__ void __launch_bounds__(kColThreads, 1)
@@ -1156,8 +1173,17 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int s = 0; s < kColStages; ++s) {
       mbar_init(&sm.q_full[s], 1);
       mbar_init(&sm.q_empty[s], 1);
+      mbar_init(&sm.x_full[s], 1);
     }
     mbar_fence_init();
+  }
+  if (kColFoldLse && threadIdx.x >= 128 && threadIdx.x < 256) {
+    // the constant operand: row r = (1, 1, 1, 0, ..., 0) in bf16
+    const int r = threadIdx.x - 128;
+    uint8_t* dst = sm.ax + (r >> 3) * 256 + (r & 7) * 16;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u);
+    *reinterpret_cast<uint4*>(dst + 128) = make_uint4(0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
   }
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, 512);
@@ -1194,10 +1220,50 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (++s == kColStages) { s = 0; ++s_round; }
         }
       }
+    } else if (kColFoldLse && warp == 2) {
+      // ------------------------------------------------------------------ row-term producer
+      // For every query tile: x[m] = -lse2[m] / c2 split into three bf16 (24 bits together), so
+      // that ones . (hi, mid, lo) added to the scores by the tensor core makes
+      // (s + x) * c2 = s * c2 - lse2.  Rows past M_sub get a huge negative term: their
+      // exponentials are exactly zero.
+      ColWalk walk(p);
+      const float inv_c2 = 1.f / p.scale_log2;
+      int item, i0, i1;
+      int s = 0, s_round = 0;
+      while (walk.next(item, i0, i1)) {
+        const int h = item / p.n_groups;
+        for (int i = i0; i < i1; ++i) {
+          if (s_round > 0) mbar_wait(&sm.q_empty[s], (s_round - 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int row = lane * 4 + rr;
+            const int m = i * kBM + row;
+            float x = -1e30f;
+            if (m < p.M_sub)
+              x = -p.lse2[static_cast<long long>(h) * p.lse2_stride + static_cast<long long>(m) * p.row_stride] * inv_c2;
+            if (!(fabsf(x) < 1e30f)) x = -1e30f;   // lse2 = -inf (a row without live keys) or NaN: contributes nothing
+            const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+            const float r1 = x - __bfloat162float(hi);
+            const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+            uint8_t* dst = sm.bx[s] + (row >> 3) * 256 + (row & 7) * 16;
+            const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(hi)) |
+                                (static_cast<uint32_t>(__bfloat16_as_ushort(mid)) << 16);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w0, static_cast<uint32_t>(__bfloat16_as_ushort(lo)), 0u, 0u);
+            *reinterpret_cast<uint4*>(dst + 128) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.x_full[s]);
+          if (++s == kColStages) { s = 0; ++s_round; }
+        }
+      }
     } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
       // (all lanes run the loop so that descriptors are warp-uniform; one elected lane issues)
       constexpr uint32_t idesc = umma_idesc_bf16(kBN, kColHalf, 0);
+      const uint64_t ax_desc = smem_desc_nosw(smem_u32(sm.ax), 128, 256);
+      const uint64_t bx_desc0 = smem_desc_nosw(smem_u32(sm.bx[0]), 128, 256);
       ColWalk walk(p);
       const uint64_t k_desc0 = smem_desc_sw128(smem_u32(sm.k[0][0]));
       const uint64_t q_desc0 = smem_desc_sw128(smem_u32(sm.q[0]));
@@ -1209,6 +1275,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(kb * kColGroup * (kTileBytes >> 4));
         for (int i = i0; i < i1; ++i) {
           mbar_wait(&sm.q_full[s], s_round & 1, p.err, DEV_TIMEOUT_TMA);
+          if (kColFoldLse) mbar_wait(&sm.x_full[s], s_round & 1, p.err, DEV_TIMEOUT_CONSUMER);
 #pragma unroll
           for (int half = 0; half < 2; ++half, ++ui) {
             const int g = ui & 1, it = ui >> 1;
@@ -1225,6 +1292,10 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 umma_ss(d + t * 128, kd + 2, q_desc + 2, idesc, 1u);
                 umma_ss(d + t * 128, kd + 4, q_desc + 4, idesc, 1u);
                 umma_ss(d + t * 128, kd + 6, q_desc + 6, idesc, 1u);
+                // the 64 rows of this half: eight row groups of 256 bytes further in the operand
+                if (kColFoldLse)
+                  umma_ss(d + t * 128, ax_desc, bx_desc0 + static_cast<uint64_t>((s * kColXBytes + half * 2048) >> 4),
+                          idesc, 1u);
               }
               umma_commit(&sm.s_full[g]);
               if (half == 1) {
@@ -1255,7 +1326,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // negated row log-sum-exps of the head's query rows, reloaded only when the head changes
       // (a CTA's items are consecutive, so that is once or twice per launch)
       float* nl_s = sm.lse2;
-      if (h != cur_h) {
+      if (!kColFoldLse && h != cur_h) {
         cur_h = h;
         named_bar_sync(1, kColExpThreads);   // everyone is done with the previous head's values
         for (int r = tid; r < nq * kBM; r += kColExpThreads) {
@@ -1386,7 +1457,7 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   float corr;
   attn_subsample_plan(a.M, a.subsample_ratio, &m_sub, &stride, &corr);
   const int nq = (m_sub + kBM - 1) / kBM;
-  const int col_smem = static_cast<int>(sizeof(ColSmem)) + nq * kBM * 4 + 1024;
+  const int col_smem = static_cast<int>(sizeof(ColSmem)) + (kColFoldLse ? 0 : nq * kBM * 4) + 1024;
   if (col_smem > 227 * 1024) return STAC_ERR_BAD_ARG;
   const int fast_smem = static_cast<int>(sizeof(FastSmem)) + 1024;
   if (attr_done.needs_setup(dev)) {

@@ -226,6 +226,19 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for a K-major operand stored WITHOUT swizzle: core matrices of
+// eight rows x 16 bytes (eight bf16) are contiguous (row r of a core matrix at r * 16 bytes);
+// `lbo` = bytes between the core matrices that are neighbours along K, `sbo` = bytes between
+// eight-row groups.  Used for the small operand pair that adds a per-row term to a score tile.
+__device__ __forceinline__ uint64_t smem_desc_nosw(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;            // descriptor version
+  return d;                                       // layout bits [61,64) = 0: no swizzle
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 //   bits [4,6) D format (1 = f32)  [7,10) A format (1 = bf16)  [10,13) B format (1 = bf16)
 //   bit 15 A major (0 = K)  bit 16 B major (0 = K, 1 = MN)  [17,23) N >> 3  [24,29) M >> 4
@@ -254,6 +267,58 @@ __device__ __forceinline__ float poly_exp2(float x) {
   p = fmaf(p, f, 0.6951165795326233f);
   p = fmaf(p, f, 1.f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// Two fp32 values in one 64-bit register pair, for the packed fp32 instructions of sm_100
+// (fma / add on both halves in one issue slot; the FMA pipe does the same work as two scalar
+// instructions, what is saved is instruction issue).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_rm_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// poly_exp2 on two values at once: the range reduction and the cubic use packed instructions
+// (six for the pair), only the clamp and the exponent insertion stay per value.
+__device__ __forceinline__ uint64_t poly_exp2_x2(uint64_t x2) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x2 = pack_f32x2(fmaxf(x0, -127.f), fmaxf(x1, -127.f));
+  const uint64_t t2 = add_rm_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t u2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(u2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t p2 = fma_f32x2(pack_f32x2(0.07706617563962936f, 0.07706617563962936f), f2,
+                          pack_f32x2(0.22764593362808228f, 0.22764593362808228f));
+  p2 = fma_f32x2(p2, f2, pack_f32x2(0.6951165795326233f, 0.6951165795326233f));
+  p2 = fma_f32x2(p2, f2, pack_f32x2(1.f, 1.f));
+  float p0, p1, t0, t1;
+  unpack_f32x2(p2, p0, p1);
+  unpack_f32x2(t2, t0, t1);
+  return pack_f32x2(__int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23)),
+                    __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23)));
 }
 
 // three-input maximum (one instruction on sm_100)

@@ -199,10 +199,99 @@ __global__ void append_kv_kernel(const uint4* __restrict__ k, const uint4* __res
   if (part == 0) token_idx[h * idx_head_stride + old_T + t] = first_id + t;
 }
 
+// The epilogue of the attention layer's QKV projection fused with append_kv
+// (causalvggt/layers/attention.py:119-128 and :141): one warp per (token, head) takes the three
+// 64-value rows q, k, v of the projection output, applies LayerNorm over the head dimension to
+// q and k (fp32: mean, biased variance, eps, affine), the 2-D rotary embedding (dims 0..31 turn
+// with the token's y position, dims 32..63 with its x position; 16 frequencies each, rotate-half
+// form, cos / sin read from the caller's tables), rounds to bf16 and writes q to the query
+// tensor and k, v straight into the cache tail together with the token id.  Lane l holds dims l
+// and 32 + l; the rotation partner of dim l inside its half is dim l ^ 16, i.e. lane l ^ 16.
+__global__ void __launch_bounds__(256) qkv_epilogue_kernel(
+    const __nv_bfloat16* __restrict__ qkv, long long token_stride, int H, const float* __restrict__ q_w,
+    const float* __restrict__ q_b, const float* __restrict__ k_w, const float* __restrict__ k_b, float eps,
+    const long long* __restrict__ pos, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+    int n_pos, __nv_bfloat16* __restrict__ q_out, long long q_row_stride, __nv_bfloat16* __restrict__ k_cache,
+    __nv_bfloat16* __restrict__ v_cache, long long cache_head_stride, long long* __restrict__ token_idx,
+    long long idx_head_stride, int T_new, int old_T, long long first_id) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (w >= static_cast<long long>(T_new) * H) return;
+  const int t = static_cast<int>(w / H), h = static_cast<int>(w - static_cast<long long>(t) * H);
+  const __nv_bfloat16* src = qkv + t * token_stride + h * 64;
+  float c_y = 1.f, s_y = 0.f, c_x = 1.f, s_x = 0.f;
+  if (cos_tab != nullptr) {
+    long long py = pos[2 * t], px = pos[2 * t + 1];
+    py = py < 0 ? 0 : (py >= n_pos ? n_pos - 1 : py);
+    px = px < 0 ? 0 : (px >= n_pos ? n_pos - 1 : px);
+    const int f = lane & 15;
+    c_y = cos_tab[py * 16 + f]; s_y = sin_tab[py * 16 + f];
+    c_x = cos_tab[px * 16 + f]; s_x = sin_tab[px * 16 + f];
+  }
+  const float sign = (lane < 16) ? -1.f : 1.f;     // rotate-half: (-x2, x1)
+  auto norm_rope = [&](int which, const float* wgt, const float* bia, float& a, float& b) {
+    a = __bfloat162float(src[which * H * 64 + lane]);
+    b = __bfloat162float(src[which * H * 64 + 32 + lane]);
+    if (wgt != nullptr) {
+      float sum = a + b;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float mean = sum * (1.f / 64.f);
+      const float da = a - mean, db = b - mean;
+      float sq = da * da + db * db;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      const float rstd = rsqrtf(sq * (1.f / 64.f) + eps);
+      a = da * rstd * wgt[lane] + bia[lane];
+      b = db * rstd * wgt[32 + lane] + bia[32 + lane];
+    }
+    if (cos_tab != nullptr) {
+      const float pa = __shfl_xor_sync(0xffffffffu, a, 16), pb = __shfl_xor_sync(0xffffffffu, b, 16);
+      a = a * c_y + sign * pa * s_y;
+      b = b * c_x + sign * pb * s_x;
+    }
+  };
+  float qa, qb, ka, kb;
+  norm_rope(0, q_w, q_b, qa, qb);
+  norm_rope(1, k_w, k_b, ka, kb);
+  __nv_bfloat16* qd = q_out + t * q_row_stride + h * 64;
+  qd[lane] = __float2bfloat16_rn(qa);
+  qd[32 + lane] = __float2bfloat16_rn(qb);
+  const long long dst = h * cache_head_stride + static_cast<long long>(old_T + t) * 64;
+  k_cache[dst + lane] = __float2bfloat16_rn(ka);
+  k_cache[dst + 32 + lane] = __float2bfloat16_rn(kb);
+  v_cache[dst + lane] = src[2 * H * 64 + lane];
+  v_cache[dst + 32 + lane] = src[2 * H * 64 + 32 + lane];
+  if (lane == 0) token_idx[h * idx_head_stride + old_T + t] = first_id + t;
+}
+
 }  // namespace
 }  // namespace stac
 
 extern "C" {
+
+int stac_qkv_epilogue_append(const void* qkv, int64_t qkv_token_stride, const float* q_norm_w, const float* q_norm_b,
+                             const float* k_norm_w, const float* k_norm_b, float eps, const int64_t* pos,
+                             const float* cos_table, const float* sin_table, int n_pos, void* q_out,
+                             int64_t q_out_row_stride, void* k_cache, void* v_cache, int64_t cache_head_stride,
+                             int64_t* token_idx, int64_t idx_head_stride, int H, int T_new, int old_T,
+                             int64_t first_token_id, stac_stream_t stream) {
+  if (qkv == nullptr || q_out == nullptr || k_cache == nullptr || v_cache == nullptr || token_idx == nullptr ||
+      H <= 0 || T_new < 0 || old_T < 0)
+    return STAC_ERR_BAD_ARG;
+  if ((q_norm_w == nullptr) != (q_norm_b == nullptr) || (k_norm_w == nullptr) != (k_norm_b == nullptr))
+    return STAC_ERR_BAD_ARG;
+  if (cos_table != nullptr && (sin_table == nullptr || pos == nullptr || n_pos <= 0)) return STAC_ERR_BAD_ARG;
+  if (T_new == 0) return STAC_OK;
+  const long long warps = static_cast<long long>(T_new) * H;
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+  stac::qkv_epilogue_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), qkv_token_stride, H, q_norm_w, q_norm_b, k_norm_w, k_norm_b, eps,
+      reinterpret_cast<const long long*>(pos), cos_table, sin_table, n_pos, static_cast<__nv_bfloat16*>(q_out),
+      q_out_row_stride, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), cache_head_stride,
+      reinterpret_cast<long long*>(token_idx), idx_head_stride, T_new, old_T, first_token_id);
+  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+}
 
 int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
                    int64_t v_row_stride, void* k_cache, void* v_cache, int64_t cache_head_stride, int64_t* token_idx,

@@ -18,12 +18,15 @@
 //   sort_tokens_kernel   one CTA per pool head: list the head's valid evicted tokens followed
 //                        by its carried overflow tokens, stable LSD radix sort by voxel id,
 //                        emit the unique rows (CSR).
-//   rows_phase_a1_kernel one thread per row: rows without pivots need only scores (all tokens are
-//                        selected and ranked against the buffered scores); rows with pivots or
-//                        many tokens are queued for
-//   rows_phase_a2_kernel one warp per queued row: merge tokens into existing pivots (cosine >=
-//                        sim), select the rest, rank existing buffer tokens + selected tokens by
-//                        (score desc, arrival order), count new segments / overflow / full.
+//   tokens_sim_kernel    token-parallel (eight lanes per token, 16-byte loads): cosine of every
+//                        token with the pivots of its row, best pivot; rows in which a token
+//                        reaches the merge threshold are queued for
+//   rows_merge_kernel    one warp per queued row: fold those tokens into their pivots in token
+//                        order (exp(sim) weights), publish the new pivot weights.
+//   rows_rank_kernel     one thread per row: score gate of the row's pivots, selection, ranking of
+//                        the buffered tokens + selected tokens by (score desc, arrival order),
+//                        counts of new segments / overflow / full; rows with many tokens are
+//                        queued for rows_rank_long_kernel (one warp per row, same result).
 //   scan_heads_kernel /  exclusive scans of those counts, allocation plan (k ids from the top
 //   scan_plan_kernel     of the free list, the rest fresh), capacity checks.
 //   rows_phase_b1a_kernel one thread per row: hand out segment ids, publish occupancy, queue rows
@@ -32,7 +35,7 @@
 //                        (or to the overflow list), last column first, in place.
 //   tokens_place_kernel  token-parallel 16-byte-vector copy of every selected token to its
 //                        column's segment or overflow slot.
-//   rows_phase_b2_kernel one warp per full row: turn the buffer into a pivot, insert it (folding
+//   rows_phase_b2_kernel eight lanes per full row: turn the buffer into a pivot, insert it (folding
 //                        the lowest-weight pivot into its nearest neighbour when the row is
 //                        saturated), stage the freed segment ids.
 //   finalize_kernel      append staged ids to the free list, publish counters.
@@ -68,12 +71,6 @@ template <> struct Elem<__nv_bfloat16> {
   static constexpr bool kIsBf16 = true;
 };
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
-  return v;
-}
-
 struct MergeParams {
   // geometry
   int heads, D, P, B, voxel_cap, voxel_used;
@@ -100,6 +97,7 @@ struct MergeParams {
   int* over_start_out;
   int over_cap;
   int* meta;  // device ints, see STAC_META_*
+  const int* voxel_count;  // device scalar or nullptr
   // scratch
   int ncap;            // per-head capacity of the token lists
   unsigned int* keys_a; unsigned int* keys_b;  // [heads][ncap]
@@ -122,12 +120,16 @@ struct MergeParams {
   int2* full_list;     // [heads*ncap] rows whose buffer filled up in this call
   int2* move_list;     // [heads*ncap] rows in which buffered tokens change column
   int* tok_row;        // [heads][ncap] row index of each sorted token
+  int* tok_best;       // [heads][ncap] index of the most similar pivot of the token's row
+  int* row_flag;       // [heads][ncap] zero on entry: set once a token of the row merges into a pivot
+  int2* merge_list;    // [heads*ncap] rows (head, row index) with at least one merging token
   int passes;          // radix passes (8 bits each)
   int* err;
 };
 
 enum { kPlanK = 0, kPlanFreeLen, kPlanBufTop, kPlanPivTop, kPlanTotalAdd, kPlanTotalFull, kPlanTotalOver,
-       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanMoveCount, kPlanShort, kPlanAvailBuf, kPlanAvailPiv, kPlanSize = 16 };
+       kPlanAnyValid, kPlanAbort, kPlanDeferCount, kPlanFullCount, kPlanMoveCount, kPlanShort, kPlanAvailBuf, kPlanAvailPiv,
+       kPlanMergeCount, kPlanSize = 16 };
 
 // Block-wide exclusive scan, 1024 threads.
 __device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
@@ -283,6 +285,7 @@ __global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams 
       rvx[r] = static_cast<int>(key);
       rst[r] = i;
     }
+    if (i < n) p.tok_row[static_cast<long long>(h) * p.ncap + i] = r + head_flag - 1;
     __syncthreads();
     if (threadIdx.x == 0) sh_carry += sh_total;
     __syncthreads();
@@ -332,145 +335,244 @@ struct TokenReader {
   }
 };
 
-template <int EPL>
-__device__ __forceinline__ float norm_inv_denom(const float (&x)[EPL]) {
-  float s = 0.f;
-#pragma unroll
-  for (int e = 0; e < EPL; ++e) s += x[e] * x[e];
-  return fmaxf(sqrtf(warp_sum(s)), 1e-6f);
+// ------------------------------------------------------------------------------------ phase A
+// Eight consecutive lanes work on one token: each holds eight of its 64 values (16 bytes of a
+// bf16 row, 32 of an fp32 row).
+template <typename T> struct Row8;
+template <> struct Row8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* row, int sub, float (&x)[8]) {
+    const uint4 u = reinterpret_cast<const uint4*>(row)[sub];
+    x[0] = __uint_as_float(u.x << 16); x[1] = __uint_as_float(u.x & 0xffff0000u);
+    x[2] = __uint_as_float(u.y << 16); x[3] = __uint_as_float(u.y & 0xffff0000u);
+    x[4] = __uint_as_float(u.z << 16); x[5] = __uint_as_float(u.z & 0xffff0000u);
+    x[6] = __uint_as_float(u.w << 16); x[7] = __uint_as_float(u.w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* row, int sub, const float (&x)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(x[0], x[1]); u.y = pack_bf16x2(x[2], x[3]);
+    u.z = pack_bf16x2(x[4], x[5]); u.w = pack_bf16x2(x[6], x[7]);
+    reinterpret_cast<uint4*>(row)[sub] = u;
+  }
+};
+template <> struct Row8<float> {
+  static __device__ __forceinline__ void load(const float* row, int sub, float (&x)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(row)[2 * sub], b = reinterpret_cast<const float4*>(row)[2 * sub + 1];
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* row, int sub, const float (&x)[8]) {
+    reinterpret_cast<float4*>(row)[2 * sub] = make_float4(x[0], x[1], x[2], x[3]);
+    reinterpret_cast<float4*>(row)[2 * sub + 1] = make_float4(x[4], x[5], x[6], x[7]);
+  }
+};
+
+// sum over the eight lanes of a group (every lane gets it; same order in every group)
+__device__ __forceinline__ float group8_sum(float v, unsigned gmask) {
+  v += __shfl_xor_sync(gmask, v, 4);
+  v += __shfl_xor_sync(gmask, v, 2);
+  v += __shfl_xor_sync(gmask, v, 1);
+  return v;
 }
 
-// ------------------------------------------------------------------------------------ phase A
+template <typename T>
+__device__ __forceinline__ const T* token_row_ptr(const MergeParams& p, int h, int code, bool want_v) {
+  if (code >= 0) {
+    const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+    return static_cast<const T*>(want_v ? p.v_src : p.k_src) + h * p.src_head_stride + pos * p.src_row_stride;
+  }
+  return static_cast<const T*>(want_v ? p.over_V_in : p.over_K_in) + static_cast<long long>(~code) * p.D;
+}
+
+__device__ __forceinline__ float token_score(const MergeParams& p, int h, int code) {
+  if (code >= 0) {
+    const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
+    return p.s_src[h * p.meta_head_stride + pos];
+  }
+  return p.over_S_in[~code];
+}
+
+// Tokens against the pivots of their row (stac/merger.py:586-660): cosine with every pivot key
+// (both L2-normalised, norms clamped at 1e-6), clamped to [-1, 1]; the first largest wins.  All
+// similarities are taken against the pivots as they are BEFORE this call's merges, as the
+// reference's vectorised code does.
+template <typename T>
+__global__ void __launch_bounds__(256) tokens_sim_kernel(const MergeParams p) {
+  const int h = blockIdx.y;
+  if (p.plan[kPlanAnyValid] == 0) return;
+  const int lane = threadIdx.x & 31, sub = threadIdx.x & 7;
+  const unsigned gmask = 0xffu << (lane & 24);
+  const int i = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3);
+  if (i >= p.n_tok[h]) return;
+  const long long hb = static_cast<long long>(h) * p.ncap;
+  const int code = (((p.passes & 1) ? p.vals_b : p.vals_a) + hb)[i];
+  const int ri = p.tok_row[hb + i];
+  const int vx = p.row_vx[hb + ri];
+  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+  const int npiv = p.piv_row_cnt[r];
+  if (sub == 0) p.tok_score[hb + i] = token_score(p, h, code);
+  if (npiv == 0) {
+    if (sub == 0) {
+      p.tok_sim[hb + i] = -INFINITY;
+      p.tok_best[hb + i] = 0;
+    }
+    return;
+  }
+  float k[8];
+  Row8<T>::load(token_row_ptr<T>(p, h, code, false), sub, k);
+  float kk = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) kk = fmaf(k[e], k[e], kk);
+  float dot[kMaxP], pp[kMaxP];
+#pragma unroll
+  for (int q = 0; q < kMaxP; ++q) {
+    dot[q] = pp[q] = 0.f;
+    if (q < npiv) {
+      const int seg = p.piv_row_seg[r * p.P + q];
+      float pk[8];
+      Row8<T>::load(static_cast<const T*>(p.piv_K) + static_cast<long long>(seg) * p.D, sub, pk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        dot[q] = fmaf(k[e], pk[e], dot[q]);
+        pp[q] = fmaf(pk[e], pk[e], pp[q]);
+      }
+    }
+  }
+  const float den_k = fmaxf(sqrtf(group8_sum(kk, gmask)), 1e-6f);
+  float best_sim = -INFINITY;
+  int best = 0;
+#pragma unroll
+  for (int q = 0; q < kMaxP; ++q) {
+    if (q < npiv) {
+      const float d = group8_sum(dot[q], gmask);
+      const float den_p = fmaxf(sqrtf(group8_sum(pp[q], gmask)), 1e-6f);
+      const float sim = fminf(1.f, fmaxf(-1.f, __fdiv_rn(d, __fmul_rn(den_k, den_p))));
+      if (sim > best_sim) {
+        best_sim = sim;
+        best = q;
+      }
+    }
+  }
+  if (sub == 0) {
+    p.tok_sim[hb + i] = best_sim;
+    p.tok_best[hb + i] = best;
+    if (best_sim >= p.sim_thresh && atomicExch(&p.row_flag[hb + ri], 1) == 0)
+      p.merge_list[atomicAdd(&p.plan[kPlanMergeCount], 1)] = make_int2(h, ri);
+  }
+}
+
+// Rows with merging tokens (one warp each, lane = two of the 64 values): the tokens whose best
+// similarity reaches the threshold are folded into that pivot in token order with weights
+// exp(sim): K <- (W K + sum a k) / (W + sum a), same for V, W += sum a, S += sum of the (clamped)
+// scores, C += count; the result is stored in the pool dtype (stac/merger.py:660-760).
 template <typename T, int EPL>
-__device__ __forceinline__ void phase_a_row(const MergeParams& p, const int h, const int ri, const int lane) {
+__global__ void __launch_bounds__(256) rows_merge_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  if (p.plan[kPlanAnyValid] == 0) return;
+  const int n = p.plan[kPlanMergeCount];
+  for (int w = blockIdx.x * warps_per_block + (threadIdx.x >> 5); w < n; w += gridDim.x * warps_per_block) {
+    const int2 hr = p.merge_list[w];
+    const int h = hr.x, ri = hr.y;
+    const long long hb = static_cast<long long>(h) * p.ncap;
+    const int vx = p.row_vx[hb + ri];
+    const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
+    const int s0 = rst[ri], s1 = rst[ri + 1];
+    const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
+    const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+    const int npiv = p.piv_row_cnt[r];
+    TokenReader<T, EPL> rd(p, h, lane);
+    float accK[kMaxP][EPL], accV[kMaxP][EPL], accA[kMaxP], accS[kMaxP], accC[kMaxP];
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      accA[q] = accS[q] = accC[q] = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) accK[q][e] = accV[q][e] = 0.f;
+    }
+    for (int i = s0; i < s1; ++i) {
+      const float sim = p.tok_sim[hb + i];
+      if (!(sim >= p.sim_thresh)) continue;
+      const int best = p.tok_best[hb + i];
+      const int code = codes[i];
+      const float a = expf(sim);
+      const float s_t = fmaxf(p.tok_score[hb + i], 1e-6f);
+      float k[EPL], v[EPL];
+      rd.load_k(code, k);
+      rd.load_v(code, v);
+#pragma unroll
+      for (int q = 0; q < kMaxP; ++q) {
+        if (q == best) {
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) {
+            accK[q][e] = __fadd_rn(accK[q][e], __fmul_rn(a, k[e]));
+            accV[q][e] = __fadd_rn(accV[q][e], __fmul_rn(a, v[e]));
+          }
+          accA[q] = __fadd_rn(accA[q], a);
+          accS[q] = __fadd_rn(accS[q], s_t);
+          accC[q] = __fadd_rn(accC[q], 1.f);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kMaxP; ++q) {
+      if (q < npiv && accA[q] > 0.f) {
+        const int seg = p.piv_row_seg[r * p.P + q];
+        T* kb = static_cast<T*>(p.piv_K) + static_cast<long long>(seg) * p.D;
+        T* vb = static_cast<T*>(p.piv_V) + static_cast<long long>(seg) * p.D;
+        const float W = p.piv_W[seg];
+        const float denom = fmaxf(__fadd_rn(W, accA[q]), 1e-8f);
+        const float fo = __fdiv_rn(W, denom), fn = __fdiv_rn(1.0f, denom);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          const float ko = Elem<T>::load(kb + lane * EPL + e), vo = Elem<T>::load(vb + lane * EPL + e);
+          Elem<T>::store(kb + lane * EPL + e, __fadd_rn(__fmul_rn(fo, ko), __fmul_rn(fn, accK[q][e])));
+          Elem<T>::store(vb + lane * EPL + e, __fadd_rn(__fmul_rn(fo, vo), __fmul_rn(fn, accV[q][e])));
+        }
+        if (lane == 0) {
+          p.piv_W[seg] = denom;
+          p.piv_S[seg] = __fadd_rn(p.piv_S[seg], accS[q]);
+          p.piv_C[seg] = __fadd_rn(p.piv_C[seg], accC[q]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// Score gate of a row with pivots (after this call's merges): mean score per merged token of
+// the row's pivots times score_thresh (stac/merger.py:735-745).
+__device__ __forceinline__ float row_gate(const MergeParams& p, long long r, int npiv) {
+  float sumS = 0.f, sumC = 0.f;
+  for (int q = 0; q < npiv; ++q) {
+    const int seg = p.piv_row_seg[r * p.P + q];
+    sumS = __fadd_rn(sumS, p.piv_S[seg]);
+    sumC = __fadd_rn(sumC, p.piv_C[seg]);
+  }
+  return __fmul_rn(__fdiv_rn(sumS, fmaxf(sumC, 1e-6f)), p.score_thresh);
+}
+
+// Selection and ranking of one row by one warp (rows with many tokens).  A token of a row with
+// pivots is selected for the buffer if it did not come close to a pivot (sim < replace) and its
+// score passes the gate; every token of a row without pivots is selected.  Candidates = buffered
+// tokens (in column order) then selected tokens (in list order), ranked by (score desc,
+// candidate order); rank < B = new column, the rest overflows (stac/allocator.py:559-723).
+__device__ __forceinline__ void rank_row_warp(const MergeParams& p, const int h, const int ri, const int lane) {
   const long long hb = static_cast<long long>(h) * p.ncap;
   const int vx = p.row_vx[hb + ri];
   const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
   const int s0 = rst[ri], s1 = rst[ri + 1];
-  const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
   const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
   const int npiv = p.piv_row_cnt[r];
   const int nbuf = p.buf_row_cnt[r];
-  TokenReader<T, EPL> rd(p, h, lane);
   float* tsim = p.tok_sim + hb;
   float* tscore = p.tok_score + hb;
   int* tdest = p.tok_dest + hb;
-
   if (npiv > 0) {
-    // ---- tokens against the row's pivots (stac/merger.py:586-760)
-    float kp[kMaxP][EPL], vp[kMaxP][EPL], kpn[kMaxP][EPL];
-    float Wp[kMaxP], Sp[kMaxP], Cp[kMaxP];
-    int seg[kMaxP];
-    float accK[kMaxP][EPL], accV[kMaxP][EPL], accA[kMaxP], accS[kMaxP], accC[kMaxP];
-#pragma unroll
-    for (int q = 0; q < kMaxP; ++q) {
-      seg[q] = -1;
-      Wp[q] = Sp[q] = Cp[q] = 0.f;
-      accA[q] = accS[q] = accC[q] = 0.f;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) kp[q][e] = vp[q][e] = kpn[q][e] = accK[q][e] = accV[q][e] = 0.f;
-      if (q < npiv) {
-        seg[q] = p.piv_row_seg[r * p.P + q];
-        const T* kb = static_cast<const T*>(p.piv_K) + static_cast<long long>(seg[q]) * p.D;
-        const T* vb = static_cast<const T*>(p.piv_V) + static_cast<long long>(seg[q]) * p.D;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          kp[q][e] = Elem<T>::load(kb + lane * EPL + e);
-          vp[q][e] = Elem<T>::load(vb + lane * EPL + e);
-        }
-        Wp[q] = p.piv_W[seg[q]];
-        Sp[q] = p.piv_S[seg[q]];
-        Cp[q] = p.piv_C[seg[q]];
-        const float den = norm_inv_denom<EPL>(kp[q]);
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) kpn[q][e] = __fdiv_rn(kp[q][e], den);
-      }
-    }
-    for (int i = s0; i < s1; ++i) {
-      const int code = codes[i];
-      float k[EPL];
-      rd.load_k(code, k);
-      const float s_raw = rd.load_s(code);
-      const float s_t = fmaxf(s_raw, 1e-6f);
-      const float den = norm_inv_denom<EPL>(k);
-      float best_sim = -INFINITY;
-      int best = 0;
-#pragma unroll
-      for (int q = 0; q < kMaxP; ++q) {
-        if (q < npiv) {
-          float d = 0.f;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) d += __fdiv_rn(k[e], den) * kpn[q][e];
-          d = fminf(1.f, fmaxf(-1.f, warp_sum(d)));
-          if (d > best_sim) {
-            best_sim = d;
-            best = q;
-          }
-        }
-      }
-      if (lane == 0) {
-        tsim[i] = best_sim;
-        tscore[i] = s_raw;
-      }
-      if (best_sim >= p.sim_thresh) {
-        const float a = expf(best_sim);
-        float v[EPL];
-        rd.load_v(code, v);
-#pragma unroll
-        for (int q = 0; q < kMaxP; ++q) {
-          if (q == best) {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) {
-              accK[q][e] = __fadd_rn(accK[q][e], __fmul_rn(a, k[e]));
-              accV[q][e] = __fadd_rn(accV[q][e], __fmul_rn(a, v[e]));
-            }
-            accA[q] = __fadd_rn(accA[q], a);
-            accS[q] = __fadd_rn(accS[q], s_t);
-            accC[q] = __fadd_rn(accC[q], 1.f);
-          }
-        }
-      }
-    }
-    float sumS = 0.f, sumC = 0.f;
-#pragma unroll
-    for (int q = 0; q < kMaxP; ++q) {
-      if (q < npiv) {
-        if (accA[q] > 0.f) {
-          const float denom = fmaxf(__fadd_rn(Wp[q], accA[q]), 1e-8f);
-          const float fo = __fdiv_rn(Wp[q], denom), fn = __fdiv_rn(1.0f, denom);
-          T* kb = static_cast<T*>(p.piv_K) + static_cast<long long>(seg[q]) * p.D;
-          T* vb = static_cast<T*>(p.piv_V) + static_cast<long long>(seg[q]) * p.D;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) {
-            Elem<T>::store(kb + lane * EPL + e, __fadd_rn(__fmul_rn(fo, kp[q][e]), __fmul_rn(fn, accK[q][e])));
-            Elem<T>::store(vb + lane * EPL + e, __fadd_rn(__fmul_rn(fo, vp[q][e]), __fmul_rn(fn, accV[q][e])));
-          }
-          Wp[q] = denom;
-          Sp[q] = __fadd_rn(Sp[q], accS[q]);
-          Cp[q] = __fadd_rn(Cp[q], accC[q]);
-          if (lane == 0) {
-            p.piv_W[seg[q]] = Wp[q];
-            p.piv_S[seg[q]] = Sp[q];
-            p.piv_C[seg[q]] = Cp[q];
-          }
-        }
-        sumS = __fadd_rn(sumS, Sp[q]);
-        sumC = __fadd_rn(sumC, Cp[q]);
-      }
-    }
-    const float gate = __fmul_rn(__fdiv_rn(sumS, fmaxf(sumC, 1e-6f)), p.score_thresh);
-    __syncwarp();
+    const float gate = row_gate(p, r, npiv);
     for (int i = s0 + lane; i < s1; i += 32) {
       const bool sel = (tsim[i] < p.replace_thresh) && (fmaxf(tscore[i], 1e-6f) > gate);
       tdest[i] = sel ? 0 : -1;
-      p.tok_row[hb + i] = ri;
     }
   } else {
-    for (int i = s0 + lane; i < s1; i += 32) {
-      tscore[i] = rd.load_s(codes[i]);
-      tdest[i] = 0;
-      p.tok_row[hb + i] = ri;
-    }
+    for (int i = s0 + lane; i < s1; i += 32) tdest[i] = 0;
   }
   __syncwarp();
   // ---- rank existing buffer tokens and selected tokens by (score desc, arrival order)
@@ -535,10 +637,9 @@ __device__ __forceinline__ void phase_a_row(const MergeParams& p, const int h, c
   }
 }
 
-// Thread-per-row fast path of phase A: rows without pivots and with few tokens need only
-// scores (every token is selected, ranked against the buffered scores).  Rows that hold
-// pivots, or long rows, are queued for the warp-per-row path.
-__global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p) {
+// The same for short rows, one thread per row; rows with more than 32 tokens are queued for the
+// warp-per-row kernel.
+__global__ void __launch_bounds__(256) rows_rank_kernel(const MergeParams p) {
   const int h = blockIdx.y;
   const int ri = blockIdx.x * blockDim.x + threadIdx.x;
   if (p.plan[kPlanAnyValid] == 0) return;
@@ -547,48 +648,47 @@ __global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p)
   const int vx = p.row_vx[hb + ri];
   const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
   const int s0 = rst[ri], s1 = rst[ri + 1];
-  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
-  const int npiv = p.piv_row_cnt[r];
-  if (npiv > 0 || s1 - s0 > 32) {
-    const int pos = atomicAdd(&p.plan[kPlanDeferCount], 1);
-    p.defer_list[pos] = make_int2(h, ri);
+  if (s1 - s0 > 32) {
+    p.defer_list[atomicAdd(&p.plan[kPlanDeferCount], 1)] = make_int2(h, ri);
     return;
   }
-  const int* codes = ((p.passes & 1) ? p.vals_b : p.vals_a) + hb;
+  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+  const int npiv = p.piv_row_cnt[r];
   const int nbuf = p.buf_row_cnt[r];
-  float* tscore = p.tok_score + hb;
+  const float* tscore = p.tok_score + hb;
   int* tdest = p.tok_dest + hb;
+  unsigned sel_mask = 0u;      // bit j: token s0 + j goes to the buffer
+  if (npiv > 0) {
+    const float gate = row_gate(p, r, npiv);
+    for (int i = s0; i < s1; ++i)
+      if ((p.tok_sim[hb + i] < p.replace_thresh) && (fmaxf(tscore[i], 1e-6f) > gate)) sel_mask |= 1u << (i - s0);
+  } else {
+    sel_mask = (s1 - s0) == 32 ? 0xffffffffu : ((1u << (s1 - s0)) - 1u);
+  }
   float ex[kMaxB];
 #pragma unroll
   for (int c = 0; c < kMaxB; ++c) ex[c] = (c < nbuf) ? p.buf_S[p.buf_row_seg[r * p.B + c]] : 0.f;
-  for (int i = s0; i < s1; ++i) {
-    const int code = codes[i];
-    float sc;
-    if (code >= 0) {
-      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
-      sc = p.s_src[h * p.meta_head_stride + pos];
-    } else {
-      sc = p.over_S_in[~code];
-    }
-    tscore[i] = sc;
-    p.tok_row[hb + i] = ri;
-  }
-  const int n_sel = s1 - s0;
+  const int n_sel = __popc(sel_mask);
   int* od = p.old_dest + (hb + ri) * kMaxB;
 #pragma unroll
   for (int c = 0; c < kMaxB; ++c) {
     if (c < nbuf) {
       int rank = c;  // buffered tokens are stored in rank order
-      for (int i = s0; i < s1; ++i) rank += (tscore[i] > ex[c]) ? 1 : 0;
+      for (unsigned mm = sel_mask; mm; mm &= mm - 1) rank += (tscore[s0 + __ffs(mm) - 1] > ex[c]) ? 1 : 0;
       od[c] = rank;
     }
   }
   for (int i = s0; i < s1; ++i) {
+    if (!((sel_mask >> (i - s0)) & 1u)) {
+      tdest[i] = -1;
+      continue;
+    }
     const float mine = tscore[i];
     int rank = 0;
 #pragma unroll
     for (int c = 0; c < kMaxB; ++c) rank += (c < nbuf && ex[c] >= mine) ? 1 : 0;
-    for (int i2 = s0; i2 < s1; ++i2) {
+    for (unsigned mm = sel_mask; mm; mm &= mm - 1) {
+      const int i2 = s0 + __ffs(mm) - 1;
       const float s2 = tscore[i2];
       rank += (s2 > mine || (s2 == mine && i2 < i)) ? 1 : 0;
     }
@@ -596,23 +696,22 @@ __global__ void __launch_bounds__(256) rows_phase_a1_kernel(const MergeParams p)
   }
   const int n_cand = nbuf + n_sel;
   const int newcnt = min(p.B, n_cand);
-  const int full = (newcnt == p.B) ? 1 : 0;
+  const int full = (n_sel > 0 && newcnt == p.B) ? 1 : 0;
   int4 info;
   info.x = newcnt - nbuf;
   info.y = max(0, n_cand - p.B);
-  info.z = full | (full ? 2 : 0) | (nbuf << 4);   // no pivots here: a full buffer always needs a pivot segment
+  info.z = full | ((full && npiv < p.P) ? 2 : 0) | (nbuf << 4);
   info.w = n_sel;
   p.row_info[hb + ri] = info;
 }
 
-template <typename T, int EPL>
-__global__ void __launch_bounds__(256) rows_phase_a2_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(256) rows_rank_long_kernel(const MergeParams p) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int n = p.plan[kPlanDeferCount];
   for (int w = blockIdx.x * warps_per_block + (threadIdx.x >> 5); w < n; w += gridDim.x * warps_per_block) {
     const int2 hr = p.defer_list[w];
-    phase_a_row<T, EPL>(p, hr.x, hr.y, lane);
+    rank_row_warp(p, hr.x, hr.y, lane);
   }
 }
 
@@ -683,6 +782,7 @@ __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p,
     __syncthreads();
   }
   if (threadIdx.x == 0) {
+    if (pass == 0 && p.voxel_count != nullptr) p.meta[STAC_META_VOXELS] = max(p.meta[STAC_META_VOXELS], *p.voxel_count);
     const int any = p.plan[kPlanAnyValid];
     const int total_add = carry[0], total_over = carry[1], total_full = carry[2], total_piv = carry[3];
     const int free_len = p.meta[STAC_META_BUF_FREE_LEN];
@@ -852,14 +952,14 @@ __global__ void __launch_bounds__(256) rows_phase_b1m_kernel(const MergeParams p
 }
 
 // Phase B, step 3 (token-parallel): every selected token is copied to its column's segment or
-// to its overflow slot with 16-byte vectors; a group of 2 * vec lanes handles one token (first
-// half K, second half V).
-__global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p, const int vec, const int elem_bytes) {
+// to its overflow slot; eight lanes per token, each moving 16 (bf16) or 32 (fp32) bytes of K and
+// of V, all four loads in flight before the stores.
+template <typename T>
+__global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p) {
+  constexpr int kVec = static_cast<int>(sizeof(T)) * 8 / 16;   // 16-byte vectors per lane and row
   const int h = blockIdx.y;
-  const int group = 2 * vec;
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int i = static_cast<int>(gid / group);
-  const int sub = static_cast<int>(gid % group);
+  const int sub = threadIdx.x & 7;
+  const int i = static_cast<int>((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3);
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
   if (i >= p.n_tok[h]) return;
   const long long hb = static_cast<long long>(h) * p.ncap;
@@ -868,250 +968,257 @@ __global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p, 
   const int ri = p.tok_row[hb + i];
   const int code = (((p.passes & 1) ? p.vals_b : p.vals_a) + hb)[i];
   const int vx = p.row_vx[hb + ri];
-  const bool is_v = sub >= vec;
-  const int part = is_v ? sub - vec : sub;
-  const long long tok_bytes = static_cast<long long>(p.D) * elem_bytes;
-  const char* src;
-  float sc;
-  if (code >= 0) {
-    const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + code] : code;
-    src = static_cast<const char*>(is_v ? p.v_src : p.k_src) +
-          (h * p.src_head_stride + pos * p.src_row_stride) * elem_bytes;
-    sc = p.s_src[h * p.meta_head_stride + pos];
-  } else {
-    src = static_cast<const char*>(is_v ? p.over_V_in : p.over_K_in) + static_cast<long long>(~code) * tok_bytes;
-    sc = p.over_S_in[~code];
+  const uint4* src_k = reinterpret_cast<const uint4*>(token_row_ptr<T>(p, h, code, false)) + sub * kVec;
+  const uint4* src_v = reinterpret_cast<const uint4*>(token_row_ptr<T>(p, h, code, true)) + sub * kVec;
+  uint4 kv[kVec], vv[kVec];
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) {
+    kv[j] = src_k[j];
+    vv[j] = src_v[j];
   }
-  const uint4 val = reinterpret_cast<const uint4*>(src)[part];
+  const float sc = p.tok_score[hb + i];
+  T* dst_k;
+  T* dst_v;
   if (d < p.B) {
     const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
     const int sg = p.buf_row_seg[r * p.B + d];
-    char* dst = static_cast<char*>(is_v ? p.buf_V : p.buf_K) + static_cast<long long>(sg) * tok_bytes;
-    reinterpret_cast<uint4*>(dst)[part] = val;
+    dst_k = static_cast<T*>(p.buf_K) + static_cast<long long>(sg) * p.D;
+    dst_v = static_cast<T*>(p.buf_V) + static_cast<long long>(sg) * p.D;
     if (sub == 0) p.buf_S[sg] = sc;
   } else {
     const long long o = p.head_base[h].y + p.row_pref[hb + ri].y + (d - p.B);
-    char* dst = static_cast<char*>(is_v ? p.over_V_out : p.over_K_out) + o * tok_bytes;
-    reinterpret_cast<uint4*>(dst)[part] = val;
+    dst_k = static_cast<T*>(p.over_K_out) + o * p.D;
+    dst_v = static_cast<T*>(p.over_V_out) + o * p.D;
     if (sub == 0) {
       p.over_S_out[o] = sc;
       p.over_hv_out[2 * o] = h;
       p.over_hv_out[2 * o + 1] = vx;
     }
   }
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) {
+    reinterpret_cast<uint4*>(dst_k)[sub * kVec + j] = kv[j];
+    reinterpret_cast<uint4*>(dst_v)[sub * kVec + j] = vv[j];
+  }
 }
 
 // Full buffers -> one pivot each, inserted into the row's pivot slots; the buffer row is released.
-template <typename T, int EPL>
+// Eight lanes per row, each holding eight of the 64 values of every token (16-byte loads), so a
+// warp works on four rows at once.
+template <typename T>
 __global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p) {
-  const int lane = threadIdx.x & 31;
-  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, sub = threadIdx.x & 7;
+  const int gbase = lane & 24;                       // first lane of this group
+  const unsigned gmask = 0xffu << gbase;
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
   const int n_full = p.plan[kPlanFullCount];
-  for (int wi = blockIdx.x * warps_per_block + (threadIdx.x >> 5); wi < n_full; wi += gridDim.x * warps_per_block) {
-  const int2 hr = p.full_list[wi];
-  const int h = hr.x, ri = hr.y;
-  const long long hb = static_cast<long long>(h) * p.ncap;
-  const int vx = p.row_vx[hb + ri];
-  const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
-  const int4 pref = p.row_pref[hb + ri];
-  const int4 hbase = p.head_base[h];
-  const int full_off = hbase.z + pref.z, piv_off = hbase.w + pref.w;
-  const int B = p.B, D = p.D;
-  T* bK = static_cast<T*>(p.buf_K);
-  T* bV = static_cast<T*>(p.buf_V);
-  int my_seg = -1;
-  if (lane < B) my_seg = p.buf_row_seg[r * B + lane];
-  // ---- the buffer is full: B tokens -> one pivot (stac/merger.py:408-461)
-  float tk[kMaxB][EPL], tv[kMaxB][EPL];
-  float ts = 0.f;
-  if (lane < B) ts = fmaxf(p.buf_S[my_seg], 1e-6f);
+  const int groups = (gridDim.x * blockDim.x) >> 3;
+  for (int wi = (blockIdx.x * blockDim.x + threadIdx.x) >> 3; wi < n_full; wi += groups) {
+    const int2 hr = p.full_list[wi];
+    const int h = hr.x, ri = hr.y;
+    const long long hb = static_cast<long long>(h) * p.ncap;
+    const int vx = p.row_vx[hb + ri];
+    const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
+    const int4 pref = p.row_pref[hb + ri];
+    const int4 hbase = p.head_base[h];
+    const int full_off = hbase.z + pref.z, piv_off = hbase.w + pref.w;
+    const int B = p.B, D = p.D;
+    const T* bK = static_cast<const T*>(p.buf_K);
+    const T* bV = static_cast<const T*>(p.buf_V);
+    int my_seg = -1;
+    if (sub < B) my_seg = p.buf_row_seg[r * B + sub];
+    // ---- the buffer is full: B tokens -> one pivot (stac/merger.py:408-461)
+    float ts = 0.f;
+    if (sub < B) ts = fmaxf(p.buf_S[my_seg], 1e-6f);
+    float tk[kMaxB][8];
+    float den[kMaxB];
 #pragma unroll
-  for (int c = 0; c < kMaxB; ++c) {
-    const int sg = __shfl_sync(kFull, my_seg, c);
-    if (c < B) {
+    for (int c = 0; c < kMaxB; ++c) {
+      const int sg = __shfl_sync(gmask, my_seg, gbase + c);
+      den[c] = 1.f;
+      if (c < B) {
+        Row8<T>::load(bK + static_cast<long long>(sg) * D, sub, tk[c]);
+      } else {
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        tk[c][e] = Elem<T>::load(bK + static_cast<long long>(sg) * D + lane * EPL + e);
-        tv[c][e] = Elem<T>::load(bV + static_cast<long long>(sg) * D + lane * EPL + e);
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) tk[c][e] = tv[c][e] = 0.f;
-    }
-  }
-  int seed = 0;
-  float seed_s = -INFINITY, sumS = 0.f;
-  for (int c = 0; c < B; ++c) {
-    const float sc = __shfl_sync(kFull, ts, c);
-    if (sc > seed_s) {
-      seed_s = sc;
-      seed = c;
-    }
-    sumS = __fadd_rn(sumS, sc);
-  }
-  float kn_seed[EPL];
-#pragma unroll
-  for (int e = 0; e < EPL; ++e) kn_seed[e] = 0.f;
-#pragma unroll
-  for (int c = 0; c < kMaxB; ++c) {
-    if (c == seed) {
-      const float den = norm_inv_denom<EPL>(tk[c]);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) kn_seed[e] = __fdiv_rn(tk[c][e], den);
-    }
-  }
-  float w[kMaxB];
-  float Wsum = 0.f;
-#pragma unroll
-  for (int c = 0; c < kMaxB; ++c) {
-    w[c] = 0.f;
-    if (c < B) {
-      const float den = norm_inv_denom<EPL>(tk[c]);
-      float d = 0.f;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) d += __fdiv_rn(tk[c][e], den) * kn_seed[e];
-      d = fminf(1.f, fmaxf(-1.f, warp_sum(d)));
-      w[c] = expf(d);
-      Wsum = __fadd_rn(Wsum, w[c]);
-    }
-  }
-  float nk[EPL], nv[EPL];
-#pragma unroll
-  for (int e = 0; e < EPL; ++e) nk[e] = nv[e] = 0.f;
-  const float wden = __fadd_rn(Wsum, 1e-8f);
-#pragma unroll
-  for (int c = 0; c < kMaxB; ++c) {
-    if (c < B) {
-      const float cn = __fdiv_rn(w[c], wden);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        nk[e] = __fadd_rn(nk[e], __fmul_rn(cn, tk[c][e]));
-        nv[e] = __fadd_rn(nv[e], __fmul_rn(cn, tv[c][e]));
+        for (int e = 0; e < 8; ++e) tk[c][e] = 0.f;
       }
     }
-  }
-  // ---- insert the pivot (stac/merger.py:462-582)
-  T* pK = static_cast<T*>(p.piv_K);
-  T* pV = static_cast<T*>(p.piv_V);
-  const int npiv = p.piv_row_cnt[r];
-  int slot, pseg;
-  if (npiv < p.P) {
-    slot = npiv;
-    pseg = p.plan[kPlanPivTop] + piv_off;
-    if (lane == 0) {
-      p.piv_row_seg[r * p.P + slot] = pseg;
-      p.piv_row_cnt[r] = npiv + 1;
-    }
-  } else {
-    // saturated: fold the lowest-weight pivot into its most similar neighbour, reuse its slot
-    float pk[kMaxP][EPL], pkn[kMaxP][EPL];
-    float pw[kMaxP];
-    int ps[kMaxP];
-    int victim = 0;
-    float wmin = INFINITY;
 #pragma unroll
-    for (int q = 0; q < kMaxP; ++q) {
-      ps[q] = -1;
-      pw[q] = INFINITY;
+    for (int c = 0; c < kMaxB; ++c) {
+      if (c < B) {
+        float ss = 0.f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) pk[q][e] = pkn[q][e] = 0.f;
-      if (q < p.P) {
-        ps[q] = p.piv_row_seg[r * p.P + q];
-        pw[q] = p.piv_W[ps[q]];
-        if (pw[q] < wmin) {
-          wmin = pw[q];
-          victim = q;
-        }
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) pk[q][e] = Elem<T>::load(pK + static_cast<long long>(ps[q]) * D + lane * EPL + e);
-        // the reference normalises in the pool dtype here (stac/merger.py:493-495)
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) s += pk[q][e] * pk[q][e];
-        float nrm = Elem<T>::round(sqrtf(warp_sum(s)));
-        nrm = fmaxf(nrm, Elem<T>::round(1e-6f));
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) pkn[q][e] = Elem<T>::round(__fdiv_rn(pk[q][e], nrm));
+        for (int e = 0; e < 8; ++e) ss += tk[c][e] * tk[c][e];
+        den[c] = fmaxf(sqrtf(group8_sum(ss, gmask)), 1e-6f);
       }
     }
-    float vn[EPL];
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) vn[e] = 0.f;
-#pragma unroll
-    for (int q = 0; q < kMaxP; ++q)
-      if (q == victim) {
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) vn[e] = pkn[q][e];
+    int seed = 0;
+    float seed_s = -INFINITY, sumS = 0.f;
+    for (int c = 0; c < B; ++c) {
+      const float sc = __shfl_sync(gmask, ts, gbase + c);
+      if (sc > seed_s) {
+        seed_s = sc;
+        seed = c;
       }
-    int nb = 0;
-    float best = -INFINITY;
+      sumS = __fadd_rn(sumS, sc);
+    }
+    float kn_seed[8];
 #pragma unroll
-    for (int q = 0; q < kMaxP; ++q) {
-      if (q < p.P && q != victim) {
+    for (int e = 0; e < 8; ++e) kn_seed[e] = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxB; ++c) {
+      if (c == seed) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kn_seed[e] = __fdiv_rn(tk[c][e], den[c]);
+      }
+    }
+    float w[kMaxB];
+    float Wsum = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxB; ++c) {
+      w[c] = 0.f;
+      if (c < B) {
         float d = 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) d += pkn[q][e] * vn[e];
-        d = Elem<T>::round(warp_sum(d));
-        if (d > best) {
-          best = d;
-          nb = q;
+        for (int e = 0; e < 8; ++e) d += __fdiv_rn(tk[c][e], den[c]) * kn_seed[e];
+        d = fminf(1.f, fmaxf(-1.f, group8_sum(d, gmask)));
+        w[c] = expf(d);
+        Wsum = __fadd_rn(Wsum, w[c]);
+      }
+    }
+    float nk[8], nv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) nk[e] = nv[e] = 0.f;
+    const float wden = __fadd_rn(Wsum, 1e-8f);
+#pragma unroll
+    for (int c = 0; c < kMaxB; ++c) {
+      if (c < B) {
+        const float cn = __fdiv_rn(w[c], wden);
+        const int sg = __shfl_sync(gmask, my_seg, gbase + c);
+        float tv[8];
+        Row8<T>::load(bV + static_cast<long long>(sg) * D, sub, tv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          nk[e] = __fadd_rn(nk[e], __fmul_rn(cn, tk[c][e]));
+          nv[e] = __fadd_rn(nv[e], __fmul_rn(cn, tv[e]));
         }
       }
     }
-    if (p.P == 1) {  // no neighbour to fold into: the victim is simply replaced
-      nb = victim;
-    }
-    float scale;
-    if (Elem<T>::kIsBf16) scale = Elem<T>::round(expf(Elem<T>::round(best - 1.0f)));
-    else scale = expf(best - 1.0f);
-    int vseg = -1, nseg = -1;
-    float Wv = 0.f, Wn = 0.f;
-#pragma unroll
-    for (int q = 0; q < kMaxP; ++q) {
-      if (q == victim) { vseg = ps[q]; Wv = pw[q]; }
-      if (q == nb) { nseg = ps[q]; Wn = pw[q]; }
-    }
-    if (p.P > 1) {
-      const float Wj = __fmul_rn(Wv, scale);
-      const float denom = fmaxf(__fadd_rn(Wj, Wn), 1e-8f);
-      const float fj = __fdiv_rn(Wj, denom), fk = __fdiv_rn(Wn, denom);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const long long oj = static_cast<long long>(vseg) * D + lane * EPL + e;
-        const long long ok = static_cast<long long>(nseg) * D + lane * EPL + e;
-        const float kj = Elem<T>::load(pK + oj), kk = Elem<T>::load(pK + ok);
-        const float vj = Elem<T>::load(pV + oj), vk = Elem<T>::load(pV + ok);
-        Elem<T>::store(pK + ok, __fadd_rn(__fmul_rn(fj, kj), __fmul_rn(fk, kk)));
-        Elem<T>::store(pV + ok, __fadd_rn(__fmul_rn(fj, vj), __fmul_rn(fk, vk)));
+    // ---- insert the pivot (stac/merger.py:462-582)
+    T* pK = static_cast<T*>(p.piv_K);
+    T* pV = static_cast<T*>(p.piv_V);
+    const int npiv = p.piv_row_cnt[r];
+    int pseg;
+    if (npiv < p.P) {
+      pseg = p.plan[kPlanPivTop] + piv_off;
+      if (sub == 0) {
+        p.piv_row_seg[r * p.P + npiv] = pseg;
+        p.piv_row_cnt[r] = npiv + 1;
       }
-      if (lane == 0) {
-        p.piv_W[nseg] = denom;
-        p.piv_S[nseg] = __fadd_rn(p.piv_S[vseg], p.piv_S[nseg]);
-        p.piv_C[nseg] = __fadd_rn(p.piv_C[vseg], p.piv_C[nseg]);
-      }
-    }
-    __syncwarp();
-    slot = victim;
-    pseg = vseg;
-  }
+    } else {
+      // saturated: fold the lowest-weight pivot into its most similar neighbour, reuse its slot
+      float pkn[kMaxP][8];
+      float pw[kMaxP];
+      int ps[kMaxP];
+      int victim = 0;
+      float wmin = INFINITY;
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) {
-    Elem<T>::store(pK + static_cast<long long>(pseg) * D + lane * EPL + e, nk[e]);
-    Elem<T>::store(pV + static_cast<long long>(pseg) * D + lane * EPL + e, nv[e]);
-  }
-  if (lane == 0) {
-    p.piv_W[pseg] = Wsum;
-    p.piv_S[pseg] = sumS;
-    p.piv_C[pseg] = static_cast<float>(B);
-  }
-  // ---- release the buffer row: segment ids go to the staging area in column order
-  if (lane < B) {
-    p.free_stage[full_off * B + lane] = my_seg;
-    p.buf_row_seg[r * B + lane] = -1;
-  }
-  if (lane == 0) p.buf_row_cnt[r] = 0;
-  __syncwarp();
+      for (int q = 0; q < kMaxP; ++q) {
+        ps[q] = -1;
+        pw[q] = INFINITY;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pkn[q][e] = 0.f;
+        if (q < p.P) {
+          ps[q] = p.piv_row_seg[r * p.P + q];
+          pw[q] = p.piv_W[ps[q]];
+          if (pw[q] < wmin) {
+            wmin = pw[q];
+            victim = q;
+          }
+          float pk[8];
+          Row8<T>::load(pK + static_cast<long long>(ps[q]) * D, sub, pk);
+          // the reference normalises in the pool dtype here (stac/merger.py:493-495)
+          float ss = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss += pk[e] * pk[e];
+          float nrm = Elem<T>::round(sqrtf(group8_sum(ss, gmask)));
+          nrm = fmaxf(nrm, Elem<T>::round(1e-6f));
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pkn[q][e] = Elem<T>::round(__fdiv_rn(pk[e], nrm));
+        }
+      }
+      float vn[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) vn[e] = 0.f;
+#pragma unroll
+      for (int q = 0; q < kMaxP; ++q)
+        if (q == victim) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) vn[e] = pkn[q][e];
+        }
+      int nb = 0;
+      float best = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < kMaxP; ++q) {
+        if (q < p.P && q != victim) {
+          float d = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d += pkn[q][e] * vn[e];
+          d = Elem<T>::round(group8_sum(d, gmask));
+          if (d > best) {
+            best = d;
+            nb = q;
+          }
+        }
+      }
+      if (p.P == 1) nb = victim;   // no neighbour to fold into: the victim is simply replaced
+      float scale;
+      if (Elem<T>::kIsBf16) scale = Elem<T>::round(expf(Elem<T>::round(best - 1.0f)));
+      else scale = expf(best - 1.0f);
+      int vseg = -1, nseg = -1;
+      float Wv = 0.f, Wn = 0.f;
+#pragma unroll
+      for (int q = 0; q < kMaxP; ++q) {
+        if (q == victim) { vseg = ps[q]; Wv = pw[q]; }
+        if (q == nb) { nseg = ps[q]; Wn = pw[q]; }
+      }
+      if (p.P > 1) {
+        const float Wj = __fmul_rn(Wv, scale);
+        const float denom = fmaxf(__fadd_rn(Wj, Wn), 1e-8f);
+        const float fj = __fdiv_rn(Wj, denom), fk = __fdiv_rn(Wn, denom);
+        float kj[8], kk[8], vj[8], vk[8];
+        Row8<T>::load(pK + static_cast<long long>(vseg) * D, sub, kj);
+        Row8<T>::load(pK + static_cast<long long>(nseg) * D, sub, kk);
+        Row8<T>::load(pV + static_cast<long long>(vseg) * D, sub, vj);
+        Row8<T>::load(pV + static_cast<long long>(nseg) * D, sub, vk);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          kk[e] = __fadd_rn(__fmul_rn(fj, kj[e]), __fmul_rn(fk, kk[e]));
+          vk[e] = __fadd_rn(__fmul_rn(fj, vj[e]), __fmul_rn(fk, vk[e]));
+        }
+        Row8<T>::store(pK + static_cast<long long>(nseg) * D, sub, kk);
+        Row8<T>::store(pV + static_cast<long long>(nseg) * D, sub, vk);
+        if (sub == 0) {
+          p.piv_W[nseg] = denom;
+          p.piv_S[nseg] = __fadd_rn(p.piv_S[vseg], p.piv_S[nseg]);
+          p.piv_C[nseg] = __fadd_rn(p.piv_C[vseg], p.piv_C[nseg]);
+        }
+      }
+      pseg = vseg;
+    }
+    Row8<T>::store(pK + static_cast<long long>(pseg) * D, sub, nk);
+    Row8<T>::store(pV + static_cast<long long>(pseg) * D, sub, nv);
+    if (sub == 0) {
+      p.piv_W[pseg] = Wsum;
+      p.piv_S[pseg] = sumS;
+      p.piv_C[pseg] = static_cast<float>(B);
+    }
+    // ---- release the buffer row: segment ids go to the staging area in column order
+    if (sub < B) {
+      p.free_stage[full_off * B + sub] = my_seg;
+      p.buf_row_seg[r * B + sub] = -1;
+    }
+    if (sub == 0) p.buf_row_cnt[r] = 0;
   }
 }
 
@@ -1149,7 +1256,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct ScratchLayout {
   size_t keys_a, keys_b, vals_a, vals_b, n_tok, n_rows, row_vx, row_start, row_info, row_pref, old_dest, tok_dest,
-      tok_sim, tok_score, head_tot, head_base, plan, free_stage, defer_list, full_list, move_list, tok_row, total;
+      tok_sim, tok_score, head_tot, head_base, plan, free_stage, defer_list, full_list, move_list, tok_row, tok_best, row_flag, merge_list, total;
 };
 
 ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
@@ -1170,6 +1277,7 @@ ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
   L.plan = take(kPlanSize * 4); L.free_stage = take(static_cast<size_t>(buf_cap) * 4);
   L.defer_list = take(hn * 8); L.full_list = take(hn * 8);
   L.move_list = take(hn * 8); L.tok_row = take(hn * 4);
+  L.tok_best = take(hn * 4); L.row_flag = take(hn * 4); L.merge_list = take(hn * 8);
   L.total = off;
   return L;
 }
@@ -1177,12 +1285,16 @@ ScratchLayout scratch_layout(int heads, int ncap, int buf_cap) {
 template <typename T>
 int launch_merge(MergeParams& mp, cudaStream_t st) {
   if (cudaMemsetAsync(mp.plan, 0, kPlanSize * 4, st) != cudaSuccess) return STAC_ERR_CUDA;
+  if (cudaMemsetAsync(mp.row_flag, 0, static_cast<size_t>(mp.heads) * mp.ncap * 4, st) != cudaSuccess) return STAC_ERR_CUDA;
   sort_tokens_kernel<<<mp.heads, 1024, 0, st>>>(mp);
   const int warps = 8;
   dim3 grid_rows((mp.ncap + warps - 1) / warps, mp.heads);
   dim3 grid_a1((mp.ncap + 255) / 256, mp.heads);
-  rows_phase_a1_kernel<<<grid_a1, 256, 0, st>>>(mp);
-  rows_phase_a2_kernel<T, 2><<<148 * 4, 256, 0, st>>>(mp);
+  dim3 grid_sim(static_cast<unsigned>((static_cast<long long>(mp.ncap) * 8 + 255) / 256), mp.heads);
+  tokens_sim_kernel<T><<<grid_sim, 256, 0, st>>>(mp);
+  rows_merge_kernel<T, 2><<<148 * 4, 256, 0, st>>>(mp);
+  rows_rank_kernel<<<grid_a1, 256, 0, st>>>(mp);
+  rows_rank_long_kernel<<<148 * 4, 256, 0, st>>>(mp);
   scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp, 0);
   scan_plan_kernel<<<1, 1024, 0, st>>>(mp, 0);
   trim_rows_kernel<<<grid_a1, 256, 0, st>>>(mp);
@@ -1190,10 +1302,8 @@ int launch_merge(MergeParams& mp, cudaStream_t st) {
   scan_plan_kernel<<<1, 1024, 0, st>>>(mp, 1);
   rows_phase_b1a_kernel<<<grid_a1, 256, 0, st>>>(mp);
   rows_phase_b1m_kernel<T, 2><<<148 * 6, 256, 0, st>>>(mp);
-  const int vec = mp.D * static_cast<int>(sizeof(T)) / 16;
-  dim3 grid_tok(static_cast<unsigned>((static_cast<long long>(mp.ncap) * 2 * vec + 255) / 256), mp.heads);
-  tokens_place_kernel<<<grid_tok, 256, 0, st>>>(mp, vec, static_cast<int>(sizeof(T)));
-  rows_phase_b2_kernel<T, 2><<<148 * 8, 128, 0, st>>>(mp);
+  tokens_place_kernel<T><<<grid_sim, 256, 0, st>>>(mp);
+  rows_phase_b2_kernel<T><<<148 * 8, 128, 0, st>>>(mp);
   finalize_kernel<<<148 * 4, 256, 0, st>>>(mp);   // grid-stride over the freed ids (known on the device only)
   carry_overflow_kernel<T><<<148, 256, 0, st>>>(mp);
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
@@ -1240,6 +1350,7 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
   mp.over_K_out = pool->over_K_out; mp.over_V_out = pool->over_V_out; mp.over_S_out = pool->over_S_out;
   mp.over_hv_out = pool->over_hv_out; mp.over_start_out = pool->over_start_out; mp.over_cap = pool->over_cap;
   mp.meta = pool->meta;
+  mp.voxel_count = pool->voxel_count;
   mp.ncap = list_cap_per_head;
   char* base = static_cast<char*>(scratch);
   mp.keys_a = reinterpret_cast<unsigned int*>(base + L.keys_a);
@@ -1264,6 +1375,9 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
   mp.full_list = reinterpret_cast<int2*>(base + L.full_list);
   mp.move_list = reinterpret_cast<int2*>(base + L.move_list);
   mp.tok_row = reinterpret_cast<int*>(base + L.tok_row);
+  mp.tok_best = reinterpret_cast<int*>(base + L.tok_best);
+  mp.row_flag = reinterpret_cast<int*>(base + L.row_flag);
+  mp.merge_list = reinterpret_cast<int2*>(base + L.merge_list);
   int bits = 1;
   while ((1ll << bits) < pool->voxel_used) ++bits;
   mp.passes = (bits + 7) / 8;

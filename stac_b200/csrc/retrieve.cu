@@ -5,10 +5,11 @@
 // gather of all [H, Q*P] pivots, argsort by W, three more gathers, index_put compaction) and
 // MergerWrapper.retrieve_seg with its torch sort (merger-cuda/csrc/merger_wrapper.cu:3148-3221).
 //
-// retrieve_select_kernel  one CTA per head streams the (voxel, slot) candidates of the queried
-//                         voxels, keeps the best R in shared memory (threshold filter + bitonic
-//                         sort of 64-bit keys = weight bits | inverted candidate index, so equal
-//                         weights resolve to the earlier candidate) and writes their order.
+// retrieve_select_kernel  one CTA per head: radix select of the weight threshold over the
+//                         (voxel, slot) candidates of the queried voxels, the candidates at or
+//                         above it collected in shared memory and sorted (64-bit keys = weight
+//                         bits | inverted candidate index, so equal weights resolve to the
+//                         earlier candidate); writes their order.
 // retrieve_gather_kernel  copies K/V of the selected pivots with 16-byte vectors, writes mask
 //                         and bias, zero-fills the padding.
 #include "common.cuh"
@@ -17,8 +18,10 @@
 namespace stac {
 namespace {
 
-constexpr int kSelCap = 8192;   // shared-memory candidate buffer (64-bit keys)
-constexpr int kSelBatch = 1024; // voxels examined per iteration (one per thread)
+constexpr int kSelCap = 8192;     // shared-memory candidate buffer (64-bit keys)
+constexpr int kSelThreads = 512;
+constexpr int kSelBins = 4096;    // 12-bit digits of the weight key, most significant first
+constexpr int kSelUnroll = 2;     // queried voxels per thread in flight
 
 __device__ __forceinline__ unsigned int wkey(float f) {
   const unsigned int u = __float_as_uint(f);
@@ -62,81 +65,185 @@ struct RetrieveParams {
   int* out_idx;             // [heads][R][2] (voxel, slot) or nullptr
 };
 
-__global__ void __launch_bounds__(1024, 1) retrieve_select_kernel(const RetrieveParams p) {
-  extern __shared__ unsigned long long cand[];  // kSelCap keys
-  __shared__ int warp_sums[32];
-  __shared__ int sh_count;
-  __shared__ unsigned int sh_thr;
+// Calls f(weight key, candidate index) for every pivot of the queried voxels of head h: one
+// pass over the candidates, kSelUnroll voxels per thread in flight.  Every thread of the CTA
+// must call it (no barrier inside).
+template <typename F>
+__device__ __forceinline__ void for_each_candidate(const RetrieveParams& p, int h, int Q, F f) {
+  for (int base = 0; base < Q; base += kSelThreads * kSelUnroll) {
+    int n[kSelUnroll];
+    long long r[kSelUnroll];
+#pragma unroll
+    for (int u = 0; u < kSelUnroll; ++u) {
+      const int q = base + u * kSelThreads + threadIdx.x;
+      n[u] = 0;
+      r[u] = 0;
+      if (q < Q) {
+        const int v = p.query_ids[q];
+        if (v >= 0 && v < p.voxel_used) {
+          r[u] = static_cast<long long>(h) * p.voxel_cap + v;
+          n[u] = min(p.piv_row_cnt[r[u]], 4);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kSelUnroll; ++u) {
+      const int q = base + u * kSelThreads + threadIdx.x;
+      int seg[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) seg[s] = s < n[u] ? p.piv_row_seg[r[u] * p.P + s] : 0;
+      float w[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) w[s] = s < n[u] ? p.piv_W[seg[s]] : 0.f;
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        if (s < n[u]) f(wkey(w[s]), static_cast<unsigned int>(q * p.P + s));
+    }
+  }
+}
+
+// Top R candidates of one head by (weight desc, candidate index asc).  A radix select on the
+// weight key finds the threshold digit by digit (12 + 12 + 8 bits, one pass over the candidates
+// per digit) and stops as soon as the candidates at or above the current prefix fit the
+// shared-memory buffer, which is then sorted; with the usual spread of weights that is after the
+// first digit, i.e. two passes.  Only when more than kSelCap - R candidates share one exact
+// weight is the last group taken in candidate order by an ordered pass.
+__global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const RetrieveParams p) {
+  extern __shared__ unsigned long long cand[];  // kSelCap keys, then kSelBins counters
+  int* hist = reinterpret_cast<int*>(cand + kSelCap);
+  __shared__ int warp_sums[kSelThreads / 32];
+  __shared__ int sh_count, sh_bin, sh_above, sh_ties;
   const int h = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int Q = *p.query_count;
   const int R = p.R;
-  if (threadIdx.x == 0) {
-    sh_count = 0;
-    sh_thr = 0;
+  // prefix of the threshold found so far: candidates with (key >> shift) > prefix are in for
+  // certain, those with (key >> shift) == prefix are undecided
+  unsigned int prefix = 0;
+  int shift = 32, need = R;       // need = how many of the undecided ones are wanted
+  bool take_all = false, ordered_ties = false;
+  const int widths[3] = {12, 12, 8};
+  for (int level = 0; level < 3; ++level) {
+    const int width = widths[level];
+    const int new_shift = shift - width;
+    for (int i = threadIdx.x; i < kSelBins; i += kSelThreads) hist[i] = 0;
+    __syncthreads();
+    const unsigned int pf = prefix;
+    const int sh_old = shift;
+    for_each_candidate(p, h, Q, [&](unsigned int wk, unsigned int) {
+      if (sh_old == 32 || (wk >> sh_old) == pf) atomicAdd(&hist[(wk >> new_shift) & ((1u << width) - 1u)], 1);
+    });
+    __syncthreads();
+    // the digit at which the count from the top reaches `need`
+    if (warp == 0) {
+      const int bins = 1 << width;
+      int above = 0, found = -1, found_above = 0;
+      for (int top = bins - 32; top >= 0 && found < 0; top -= 32) {
+        const int b = top + (31 - lane);              // lane 0 holds the highest digit of the chunk
+        const int c = hist[b];
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const bool hit = above + incl >= need;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (m) {
+          const int l = __ffs(m) - 1;
+          found = top + (31 - l);
+          found_above = above + __shfl_sync(0xffffffffu, incl - c, l);
+        }
+        above += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) {
+        sh_bin = found;                 // -1: fewer than `need` undecided candidates exist
+        sh_above = found >= 0 ? found_above : above;
+        sh_ties = found >= 0 ? hist[found] : 0;
+      }
+    }
+    __syncthreads();
+    if (sh_bin < 0) {
+      take_all = true;                  // everything undecided is wanted
+      break;
+    }
+    prefix = (prefix << width) | static_cast<unsigned int>(sh_bin);
+    shift = new_shift;
+    const int decided = (R - need) + sh_above;      // candidates strictly above the new prefix
+    need -= sh_above;
+    if (decided + sh_ties <= kSelCap) break;        // they all fit: sort settles the rest
+    if (level == 2) ordered_ties = true;            // one exact weight, more copies than fit
+    __syncthreads();
   }
+  // ---- collect
+  if (threadIdx.x == 0) sh_count = 0;
   __syncthreads();
-  for (int base = 0; base < Q; base += kSelBatch) {
-    const int q = base + threadIdx.x;
-    unsigned long long mine[4];
-    int n_mine = 0;
-    if (q < Q) {
-      const int v = p.query_ids[q];
-      if (v >= 0 && v < p.voxel_used) {
-        const long long r = static_cast<long long>(h) * p.voxel_cap + v;
-        const int n = p.piv_row_cnt[r];
-        const unsigned int thr = sh_thr;
-        for (int s = 0; s < n && s < 4; ++s) {
-          const int seg = p.piv_row_seg[r * p.P + s];
-          const unsigned int wk = wkey(p.piv_W[seg]);
-          if (wk > thr || sh_count < R) {
-            mine[n_mine++] = (static_cast<unsigned long long>(wk) << 32) |
-                             static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<unsigned int>(q * p.P + s));
-          }
+  if (!ordered_ties) {
+    const unsigned int pf = prefix;
+    const int sh = shift;
+    for_each_candidate(p, h, Q, [&](unsigned int wk, unsigned int idx) {
+      if (take_all || sh == 32 || (wk >> sh) >= pf) {
+        const int pos = atomicAdd(&sh_count, 1);
+        if (pos < kSelCap) cand[pos] = (static_cast<unsigned long long>(wk) << 32) | (0xFFFFFFFFu - idx);
+      }
+    });
+  } else {
+    // weights above the threshold in any order, then the first `need` candidates that carry the
+    // threshold weight itself, in candidate order (batches of one voxel per thread, block scan)
+    const unsigned int T = prefix;
+    for_each_candidate(p, h, Q, [&](unsigned int wk, unsigned int idx) {
+      if (wk > T) {
+        const int pos = atomicAdd(&sh_count, 1);
+        cand[pos] = (static_cast<unsigned long long>(wk) << 32) | (0xFFFFFFFFu - idx);
+      }
+    });
+    __syncthreads();
+    int taken = 0;                    // ties accepted so far (same value in every thread)
+    for (int base = 0; base < Q && taken < need; base += kSelThreads) {
+      const int q = base + threadIdx.x;
+      unsigned int mine[4];
+      int n_mine = 0;
+      if (q < Q) {
+        const int v = p.query_ids[q];
+        if (v >= 0 && v < p.voxel_used) {
+          const long long r = static_cast<long long>(h) * p.voxel_cap + v;
+          const int n = min(p.piv_row_cnt[r], 4);
+          for (int s = 0; s < n; ++s)
+            if (wkey(p.piv_W[p.piv_row_seg[r * p.P + s]]) == T) mine[n_mine++] = static_cast<unsigned int>(q * p.P + s);
         }
       }
-    }
-    // ordered append
-    int incl = n_mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    if (lane == 31) warp_sums[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-      int w = warp_sums[lane];
+      int incl = n_mine;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += t;
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
       }
-      warp_sums[lane] = w;
-    }
-    __syncthreads();
-    const int off = sh_count + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - n_mine;
-    for (int s = 0; s < n_mine; ++s) cand[off + s] = mine[s];
-    __syncthreads();
-    if (threadIdx.x == 0) sh_count += warp_sums[31];
-    __syncthreads();
-    // keep the buffer small enough for the next batch
-    if (sh_count + kSelBatch * 4 > kSelCap) {
-      const int cnt = sh_count;
-      int np2 = 1;
-      while (np2 < cnt) np2 <<= 1;
-      for (int i = cnt + threadIdx.x; i < np2; i += blockDim.x) cand[i] = 0ull;
+      if (lane == 31) warp_sums[warp] = incl;
       __syncthreads();
-      bitonic_desc(cand, np2);
-      if (threadIdx.x == 0) {
-        sh_count = min(cnt, R);
-        if (cnt >= R) sh_thr = static_cast<unsigned int>(cand[R - 1] >> 32);
+      if (warp == 0) {
+        int w = lane < kSelThreads / 32 ? warp_sums[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, w, o);
+          if (lane >= o) w += t;
+        }
+        if (lane < kSelThreads / 32) warp_sums[lane] = w;
       }
+      __syncthreads();
+      const int off = taken + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - n_mine;
+      for (int s = 0; s < n_mine; ++s) {
+        if (off + s < need) {
+          const int pos = atomicAdd(&sh_count, 1);
+          cand[pos] = (static_cast<unsigned long long>(T) << 32) | (0xFFFFFFFFu - mine[s]);
+        }
+      }
+      taken += warp_sums[kSelThreads / 32 - 1];
       __syncthreads();
     }
   }
+  __syncthreads();
   {
-    const int cnt = sh_count;
+    const int cnt = min(sh_count, kSelCap);
     int np2 = 1;
     while (np2 < cnt) np2 <<= 1;
     for (int i = cnt + threadIdx.x; i < np2; i += blockDim.x) cand[i] = 0ull;
@@ -205,14 +312,14 @@ int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_
   int dev = 0;
   if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
   static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
-  const int smem = stac::kSelCap * 8;
+  const int smem = stac::kSelCap * 8 + stac::kSelBins * 4;
   if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(stac::retrieve_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return STAC_ERR_CUDA;
     attr_done.mark(dev);
   }
-  stac::retrieve_select_kernel<<<pool->heads, 1024, smem, st>>>(rp);
+  stac::retrieve_select_kernel<<<pool->heads, stac::kSelThreads, smem, st>>>(rp);
   const int vpt = token_bytes / 16;
   const long long total = static_cast<long long>(retrieve_size) * vpt;
   dim3 grid(static_cast<unsigned>((total + 255) / 256), pool->heads);

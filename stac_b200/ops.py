@@ -31,6 +31,37 @@ class DeviceStatus:
             raise _lib.StacError(f"{what}: device error {code} ({self.NAMES.get(code, 'unknown')})")
 
 
+class LaggedInts:
+    """Device int32 values mirrored on the host WITHOUT a synchronisation at the producing call:
+    ``push`` enqueues copies into pinned host memory on the current stream and records an event;
+    ``pull`` is made by the NEXT call that needs the numbers, by which time that event lies a
+    whole stream step in the past, so waiting for it does not stall a host that runs at most
+    one step ahead of the GPU.  ``pull`` returns None when nothing is pending."""
+
+    def __init__(self, n):
+        self.pin = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.event = None
+
+    def push(self, *tensors):
+        off = 0
+        for t in tensors:
+            n = t.numel()
+            self.pin[off:off + n].copy_(t.reshape(-1), non_blocking=True)
+            off += n
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def pending(self):
+        return self.event is not None
+
+    def pull(self):
+        if self.event is None:
+            return None
+        self.event.synchronize()
+        self.event = None
+        return self.pin.tolist()
+
+
 _workspaces = {}
 
 

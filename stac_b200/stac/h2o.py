@@ -140,7 +140,8 @@ class HeavyHittersKV(KVManager):
         if n_base + k == T:
             return  # every token is kept: the reference's compaction would be the identity
         Tb = self.reserved_buffer_token_size
-        keep, drop = self._select(self._scores_hot, Tb, L * H, T, n_base + k)
+        with self._stage("h2o_select"):
+            keep, drop = self._select(self._scores_hot, Tb, L * H, T, n_base + k)
         self._apply_keep_and_compact_parallel(keep, drop)
 
     @torch.no_grad()

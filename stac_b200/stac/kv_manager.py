@@ -25,6 +25,30 @@ from .._lib import check, ptr, stream_ptr
 logger = logging.getLogger(__name__)
 
 
+class _Stage:
+    """Brackets one stage of the path with CUDA events when the manager has a trace sink
+    (``manager.stage_trace = []``); does nothing otherwise.  The sink receives
+    (stage name, start event, end event); nothing is synchronised here."""
+
+    __slots__ = ("sink", "name", "e0")
+
+    def __init__(self, sink, name):
+        self.sink, self.name, self.e0 = sink, name, None
+
+    def __enter__(self):
+        if self.sink is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.sink is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.sink.append((self.name, self.e0, e1))
+        return False
+
+
 class KVManager:
     def __init__(self, num_layers: int, num_heads: int, head_dim: int, token_per_frame: int,
                  register_layers: Optional[List[int]] = None, chunk_size: int = 1, buffer_size: int = 8,
@@ -88,6 +112,11 @@ class KVManager:
         self.use_cpu = False
         self._status = None
         self._base_cache = {}
+        self._rope_rows = {}         # query length -> rows of the rotary tables (largest position + 1)
+        self.stage_trace = None      # set to a list to collect (stage, start event, end event)
+
+    def _stage(self, name):
+        return _Stage(self.stage_trace, name)
 
     # ------------------------------------------------------------------ utilities
     def is_managed(self, layer_idx: int) -> bool:
@@ -233,6 +262,63 @@ class KVManager:
                                         first_id, D, 2, stream_ptr()),
               "stac_append_kv")
         self._offset_hot[slot] = old_T + new_T
+
+    @torch.no_grad()
+    def append_qkv(self, qkv, layer_idx: int, *, q_norm=None, k_norm=None, rope=None, pos=None):
+        """The attention layer's projection epilogue and append_kv in one kernel
+        (causalvggt/layers/attention.py:119-128, :141): `qkv` is the output of the layer's QKV
+        projection, [1, T, 3*H*D] (or [1, T, 3, H, D]) bf16; `q_norm` / `k_norm` are the layer's
+        ``nn.LayerNorm(head_dim)`` modules (None or Identity: no normalisation); `rope` is its
+        ``RotaryPositionEmbedding2D`` (its own frequency cache supplies the cos / sin values) with
+        `pos` [1, T, 2] integer (y, x) positions, or None.  K and V go straight into the cache
+        tail (no [B,H,T,D] copies are ever made); returns q [1, T, H, D] bf16, ready for
+        decode_sparse_attn."""
+        H, D = self.num_heads, self.head_dim
+        if D != 64:
+            raise ValueError("the fused epilogue supports head_dim 64")
+        assert qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.shape[0] == 1, "qkv: [1, T, 3*H*D] bf16 on the GPU"
+        T_new = qkv.shape[1]
+        x = qkv.reshape(T_new, 3 * H * D)
+        if x.stride(1) != 1 or x.data_ptr() % 4:
+            x = x.contiguous()
+        assert T_new % self.token_per_f == 0, "T_new must be a multiple of token_per_frame in append_qkv()."
+        slot = self._to_slot(layer_idx, strict=True)
+        old_T = self._offset_hot[slot]
+        if old_T + T_new > self.reserved_buffer_token_size:
+            raise RuntimeError("the fused epilogue writes to the GPU buffer only; use append_kv when tokens spill to the host")
+
+        def affine(mod):
+            if mod is None or not hasattr(mod, "weight") or mod.weight is None:
+                return None, None, 1e-5
+            w = mod.weight.detach().to(self.device, torch.float32).contiguous()
+            b = (mod.bias.detach().to(self.device, torch.float32).contiguous() if mod.bias is not None
+                 else torch.zeros_like(w))
+            return w, b, float(mod.eps)
+        qw, qb, eps = affine(q_norm)
+        kw, kb, eps_k = affine(k_norm)
+        eps = eps if qw is not None else eps_k
+        cos = sin = p64 = None
+        n_pos = 0
+        if rope is not None:
+            assert pos is not None and pos.shape[-1] == 2 and pos.shape[-2] == T_new
+            p64 = pos.reshape(T_new, 2).to(self.device, torch.int64).contiguous()
+            n_pos = self._rope_rows.get(T_new)
+            if n_pos is None:          # one host read per query length: positions repeat chunk after chunk
+                n_pos = int(p64.max().item()) + 1
+                self._rope_rows[T_new] = n_pos
+            c32, s32 = rope._compute_frequency_components(D // 2, n_pos, self.device, torch.float32)
+            cos, sin = c32[:, : D // 4].contiguous(), s32[:, : D // 4].contiguous()
+        q_out = torch.empty((1, T_new, H, D), dtype=torch.bfloat16, device=self.device)
+        kc, vc, ti = self.key_cache_hot[slot], self.value_cache_hot[slot], self._token_indices_hot[slot]
+        first_id = self._processed_frames * self.token_per_f
+        check(_lib.lib().stac_qkv_epilogue_append(
+            ptr(x), x.stride(0), ptr(qw), ptr(qb), ptr(kw), ptr(kb), eps, ptr(p64), ptr(cos), ptr(sin), n_pos,
+            ptr(q_out), q_out.stride(1), ptr(kc), ptr(vc), kc.stride(0), ptr(ti), ti.stride(0), H, T_new, old_T,
+            first_id, stream_ptr()), "stac_qkv_epilogue_append")
+        if slot == self._L_eff - 1:
+            self._processed_frames += T_new // self.token_per_f
+        self._offset_hot[slot] = old_T + T_new
+        return q_out
 
     @torch.no_grad()
     def prefill(self, query_states, key_states, value_states, layer_idx: int):

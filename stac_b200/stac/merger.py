@@ -15,6 +15,7 @@ import torch
 from .. import _lib
 from .._lib import META_BUF_FREE_LEN, META_BUF_TOP, META_BUF_USED, META_OVER_COUNT, META_PIV_TOP, META_PIV_USED
 from .._lib import StacEvicted, StacPool, check, ptr, stream_ptr
+from ..ops import DeviceStatus, LaggedInts
 
 MAX_LIST = 1 << 22        # STAC_MERGE_MAX_LIST
 
@@ -76,6 +77,9 @@ class VoxelKVMerger:
         self._meta = torch.zeros(_lib.META_SIZE, dtype=torch.int32, device=dev)
         self._meta_host = [0] * _lib.META_SIZE
         self._over_max_head = 0
+        self._voxel_count_dev = None     # device scalar with the table's voxel count (set by the manager)
+        # counters, overflow offsets and the status word of the last insert, read one call late
+        self._mirror = LaggedInts(_lib.META_SIZE + self.H + 1 + 1)
         self._scratch = None
         self._ret_sel = None
 
@@ -142,8 +146,9 @@ class VoxelKVMerger:
         """Everything a later insert / retrieve depends on, cut to the used extents: row maps of
         the used voxels, both pools up to their bump pointers, the free list, the carried-over
         overflow list and the device counters."""
+        self._pull_meta()
         m = self._meta_host
-        V = int(self._voxel_offset)
+        V = self.used_voxels()
         top_b, n_free, top_p, n_over = m[META_BUF_TOP], m[META_BUF_FREE_LEN], m[_lib.META_PIV_TOP], m[META_OVER_COUNT]
         cur = self._over[self._over_cur]
         cpu = lambda t: t.cpu().clone()
@@ -222,20 +227,40 @@ class VoxelKVMerger:
         s.over_hv_out, s.over_start_out = nxt["hv"].data_ptr(), nxt["start"].data_ptr()
         s.over_cap = self._over_cap
         s.meta = self._meta.data_ptr()
+        s.voxel_count = self._voxel_count_dev.data_ptr() if self._voxel_count_dev is not None else None
         return s
 
-    def _read_meta(self):
-        meta = self._meta.cpu().tolist()
-        start = self._over[self._over_cur]["start"].cpu()
-        self._meta_host = meta
-        self._over_max_head = int((start[1:] - start[:-1]).max().item()) if self.H > 0 else 0
+    def _push_meta(self):
+        """Enqueue the copy of the pool counters, the per-head overflow offsets and the status word
+        to pinned host memory behind the insert that produced them; nothing waits here."""
+        word = self._status.word if self._status is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._mirror.push(self._meta, self._over[self._over_cur]["start"], word)
+
+    def _pull_meta(self):
+        """Take in what the last insert left behind (waits for that insert if it is still running);
+        a device-side error of that insert is raised here."""
+        vals = self._mirror.pull()
+        if vals is None:
+            return
+        n = _lib.META_SIZE
+        self._meta_host = vals[:n]
+        start = vals[n:n + self.H + 1]
+        self._over_max_head = max((b - a for a, b in zip(start[:-1], start[1:])), default=0)
+        code = vals[n + self.H + 1]
+        if code != 0 and self._status is not None:
+            self._status.clear()
+            raise _lib.StacError(f"voxel merge: device error {code} ({DeviceStatus.NAMES.get(code, 'unknown')})")
 
     # ------------------------------------------------------------------ insert
     @torch.no_grad()
-    def insert_evicted(self, k_cache, v_cache, scores, voxel_ids, positions, tokens_per_head, num_voxels):
+    def insert_evicted(self, k_cache, v_cache, scores, voxel_ids, positions, tokens_per_head, num_voxels,
+                       voxel_count_dev=None):
         """Evicted tokens read in place: token j of pool head h sits at position
         positions[h, j] of k_cache/v_cache [H, T, D], scores/voxel_ids [H, T]
-        (positions None = the first tokens_per_head positions)."""
+        (positions None = the first tokens_per_head positions).  `num_voxels` may be an upper
+        bound of the voxel count if `voxel_count_dev` (int32 device scalar with the exact count)
+        is given: the bound sizes the row arrays, the exact count is recorded on the device."""
+        self._voxel_count_dev = voxel_count_dev
         H, D = self.H, self.D
         Tn = int(tokens_per_head)
         if Tn == 0:
@@ -244,6 +269,7 @@ class VoxelKVMerger:
         assert k_cache.stride(-1) == 1 and k_cache.stride(1) == D and v_cache.stride() == k_cache.stride()
         assert scores.dtype == torch.float32 and voxel_ids.dtype == torch.int32
         assert scores.stride(1) == 1 and voxel_ids.stride() == scores.stride()
+        self._pull_meta()                 # counters of the previous insert (a whole step old)
         self._token_count += H * Tn
         self.ensure_capacity(num_voxels)
         over_in = self._meta_host[META_OVER_COUNT]
@@ -296,9 +322,7 @@ class VoxelKVMerger:
                                           stream_ptr())
         check(st, "stac_merge_insert")
         self._over_cur = 1 - self._over_cur
-        self._read_meta()
-        if self._status is not None:
-            self._status.raise_if_set("voxel merge")
+        self._push_meta()
 
     @torch.no_grad()
     def insert_and_merge(self, K_new, V_new, S_new, I_new, VX_new, num_voxels: int, mode: str = "default"):
@@ -348,7 +372,7 @@ class VoxelKVMerger:
         if req <= 0:
             return self._retrieve_unbounded(voxel_ids, return_buf, want_idx)
         if voxel_ids is None:
-            ids = torch.arange(int(self._voxel_offset), device=dev, dtype=torch.int32)
+            ids = torch.arange(self.used_voxels(), device=dev, dtype=torch.int32)
         else:
             ids = torch.unique(voxel_ids.to(device=dev, dtype=torch.int64))
             ids = ids[(ids >= 0) & (ids < self._voxel_offset)].to(torch.int32).contiguous()
@@ -367,7 +391,7 @@ class VoxelKVMerger:
         a fixed retrieve_size."""
         dev, H, P, B, D = self.device, self.H, self.P, self.B, self.D
         if voxel_ids is None:
-            vid = torch.arange(int(self._voxel_offset), device=dev, dtype=torch.int64)
+            vid = torch.arange(self.used_voxels(), device=dev, dtype=torch.int64)
         else:
             vid = torch.unique(voxel_ids.to(device=dev, dtype=torch.int64))
             vid = vid[(vid >= 0) & (vid < self._voxel_offset)]
@@ -423,6 +447,7 @@ class VoxelKVMerger:
 
     # ------------------------------------------------------------------ stats
     def _pool_counts(self):
+        self._pull_meta()
         m = self._meta_host
         return m[META_BUF_USED], self._buf_cap, m[META_PIV_USED], self._piv_cap
 
@@ -430,13 +455,24 @@ class VoxelKVMerger:
         buf_data, buf_alloc, piv_data, piv_alloc = self._pool_counts()
         tc = float(self._token_count + 1e-6)
         return dict(head_dim=self.D, num_heads=self.H, pivot_capacity=self.P, buffer_capacity=self.B,
-                    used_voxels=self._voxel_offset, allocated_voxels=self._voxel_alloc,
+                    used_voxels=self.used_voxels(), allocated_voxels=self._voxel_alloc,
                     token_count=self._token_count, merge_compress_ratio=piv_data / tc,
                     best_compress_ratio=(piv_data + buf_data) / tc,
                     real_compress_ratio=(piv_alloc + buf_alloc) / tc,
                     pivot_pool_used=piv_data, pivot_pool_alloc=piv_alloc,
                     buffer_pool_used=buf_data, buffer_pool_alloc=buf_alloc,
                     dropped_tokens=self._meta_host[_lib.META_DROPPED])
+
+    def used_voxels(self) -> int:
+        """Voxels known at the last insert (exact; waits for that insert if need be)."""
+        self._pull_meta()
+        if self._voxel_count_dev is not None:
+            return int(self._meta_host[_lib.META_VOXELS])
+        return int(self._voxel_offset)
+
+    def check_status(self):
+        """Wait for the last insert and raise if it reported a device-side error."""
+        self._pull_meta()
 
     def memory(self) -> dict:
         buf_data, buf_alloc, piv_data, piv_alloc = self._pool_counts()
@@ -450,7 +486,8 @@ class VoxelKVMerger:
     # ------------------------------------------------------------------ test hooks
     def snapshot(self):
         """Host copies of the slot maps and pool contents over the used voxels (tests)."""
-        V = int(self._voxel_offset)
+        self._pull_meta()
+        V = self.used_voxels()
         m = self._meta.cpu().tolist()
         cur = self._over[self._over_cur]
         n_over = m[META_OVER_COUNT]

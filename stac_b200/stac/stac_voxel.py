@@ -6,8 +6,11 @@ Per chunk, in the reference's call order:
   append_kv (per layer) -> decode_sparse_attn (per layer: window + pivot attention, column sums
   -> scores) -> append_positions (points -> voxel ids, neighbour voxels of the recent tokens)
   -> [retrieve_kv] -> prune_kv (H2O keep set, eviction merge into the voxel memory, compaction).
-Each step is one or a few kernels of libstac_b200.so; the only host reads are the voxel count
-(4 bytes, after append_positions) and the pool counters (after the eviction merge).
+Each step is one or a few kernels of libstac_b200.so.  Nothing on this path waits for the GPU:
+the voxel count and the pool counters travel to pinned host memory behind the kernels that
+produce them and are taken in by the next call that needs them, one stream step later; until
+then the host works with an upper bound of the voxel count (stats getters return exact
+numbers and wait if they must).
 """
 
 import logging
@@ -183,7 +186,8 @@ class STACVoxelKV(HeavyHittersKV):
         T_new = new_positions.shape[0]
         if T_new == 0:
             return
-        ids = self._vm.upsert_points(new_positions, new_pos_mask)
+        with self._stage("voxel_upsert"):
+            ids = self._vm.upsert_points(new_positions, new_pos_mask)
         old_VT = self._offset_voxel[0]
         total = old_VT + T_new
         assert all(o == total for o in self._offset_hot), (
@@ -192,7 +196,8 @@ class STACVoxelKV(HeavyHittersKV):
         self._token_voxel_indices[:, :, old_VT:total].copy_(
             ids.view(1, 1, -1).expand(self._L_eff, self.num_heads, -1))
         self._offset_voxel = [total] * self._L_eff
-        self._search_recent_neighbors(slot_idx=self._L_eff - 1, dist_thres=2 * self._voxel_size_f)
+        with self._stage("voxel_neighbors"):
+            self._search_recent_neighbors(slot_idx=self._L_eff - 1, dist_thres=2 * self._voxel_size_f)
 
     @torch.no_grad()
     def append_pointmap(self, world_points: torch.Tensor, world_points_conf: torch.Tensor, patch_size: int,
@@ -221,8 +226,10 @@ class STACVoxelKV(HeavyHittersKV):
     def _apply_keep_and_compact_parallel(self, keep_idx_lh: torch.Tensor, drop_idx_lh: torch.Tensor = None):
         """Evicted tokens go to the voxel memory, then the cache is compacted
         (stac/stac_voxel.py:409-419)."""
-        self._pool_drops_vectorized_parallel(keep_idx_lh, drop_idx_lh)
-        self._compact(keep_idx_lh, vx=self._vx)
+        with self._stage("merge"):
+            self._pool_drops_vectorized_parallel(keep_idx_lh, drop_idx_lh)
+        with self._stage("compact"):
+            self._compact(keep_idx_lh, vx=self._vx)
         self._token_voxel_indices = self._vx[self._cur]
         self._offset_voxel = [keep_idx_lh.shape[-1]] * self._L_eff
 
@@ -240,7 +247,8 @@ class STACVoxelKV(HeavyHittersKV):
         Tb = self.reserved_buffer_token_size
         self._vstore.insert_evicted(self.key_cache_hot.view(L * H, Tb, D), self.value_cache_hot.view(L * H, Tb, D),
                                     self._scores_hot.view(L * H, Tb), self._token_voxel_indices.view(L * H, Tb),
-                                    drop_idx_lh.view(L * H, T_d), T_d, self._vm.get_voxel_num())
+                                    drop_idx_lh.view(L * H, T_d), T_d, self._vm.voxel_num_bound(),
+                                    voxel_count_dev=self._vm._n_dev)
 
     # ------------------------------------------------------------------ retrieval
     def retrieve_kv(self, layer_idx, **kwargs):
@@ -256,7 +264,7 @@ class STACVoxelKV(HeavyHittersKV):
         voxel_ids = kwargs.get("voxel_ids", None)
         R = self.retrieval_token_size
         if voxel_ids is None:
-            if self._vm.get_voxel_num() == 0:
+            if self._vm.voxel_num_bound() == 0:
                 for s in range(L):
                     self._clear_retrieval_cache(s)
                 return 0, 0
@@ -269,7 +277,8 @@ class STACVoxelKV(HeavyHittersKV):
                 K, V, M, B = self._vstore.retrieve(voxel_ids=ids[:n], return_buf=kwargs.get("return_buf", False),
                                                    retrieve_size=R)
             else:
-                K, V, M, B = self._vstore.retrieve_device(ids, count, R)
+                with self._stage("retrieve"):
+                    K, V, M, B = self._vstore.retrieve_device(ids, count, R)
         else:
             K, V, M, B = self._vstore.retrieve(voxel_ids=voxel_ids, return_buf=kwargs.get("return_buf", False),
                                                retrieve_size=R)

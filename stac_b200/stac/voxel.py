@@ -11,6 +11,7 @@ import torch
 
 from .. import _lib
 from .._lib import check, ptr, stream_ptr
+from ..ops import LaggedInts
 
 
 def _pow2_at_least(n):
@@ -41,7 +42,9 @@ class BinaryVoxel:
         self._nbr_count = torch.zeros(1, dtype=torch.int32, device=dev)
         self._scratch = torch.empty(_lib.lib().stac_voxel_scratch_bytes(_lib.VOXEL_MAX_POINTS),
                                     dtype=torch.uint8, device=dev)
-        self._n = 0
+        self._n = 0                 # voxel count as of the last call whose result was read back
+        self._unread = 0            # points upserted since then: count <= _n + _unread
+        self._mirror = LaggedInts(1)
         check(_lib.lib().stac_voxel_hash_clear(ptr(self._hash_keys), self._hash_cap, stream_ptr()),
               "stac_voxel_hash_clear")
 
@@ -53,6 +56,7 @@ class BinaryVoxel:
         new_cap = self._cap
         while new_cap < need:
             new_cap *= 2
+        self._sync_count()
         old_keys, n_dev, n = self._table_keys, self._n_dev, self._n
         self._alloc(new_cap)
         self._table_keys[: old_keys.numel()].copy_(old_keys)
@@ -65,6 +69,7 @@ class BinaryVoxel:
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self):
         """The table is its key list (id = position); the hash table is rebuilt on load."""
+        self._sync_count()
         return {"n": int(self._n), "table_keys": self._table_keys[: self._n].cpu()}
 
     def load_state_dict(self, sd):
@@ -73,11 +78,29 @@ class BinaryVoxel:
         if n > self._cap:
             self._grow(n)
         self._table_keys[:n].copy_(sd["table_keys"])
-        self._n = n
+        self._n, self._unread = n, 0
         self._n_dev.fill_(n)
         check(_lib.lib().stac_voxel_rehash(ptr(self._table_keys), ptr(self._n_dev), self._cap,
                                            ptr(self._hash_keys), ptr(self._hash_vals), self._hash_cap,
                                            stream_ptr()), "stac_voxel_rehash")
+
+    # ------------------------------------------------------------------ voxel count on the host
+    def _pull_count(self):
+        """Take in the count that the previous upsert left in pinned memory (its copy was enqueued
+        behind that call's kernels, a whole step ago)."""
+        vals = self._mirror.pull()
+        if vals is not None:
+            self._n, self._unread = int(vals[0]), 0
+
+    def _sync_count(self):
+        """Exact count now (waits for the last upsert if its result has not been read yet)."""
+        self._pull_count()
+
+    def voxel_num_bound(self) -> int:
+        """Upper bound of the voxel count that never waits for the GPU: the last count read back
+        plus the points upserted since.  Enough to size arrays and to filter ids (ids handed out so
+        far are below the true count)."""
+        return self._n + self._unread
 
     # ------------------------------------------------------------------ upsert
     def _upsert(self, points, ijk, mask, n):
@@ -85,6 +108,7 @@ class BinaryVoxel:
             return torch.empty(0, dtype=torch.int32, device=self.device)
         if n > _lib.VOXEL_MAX_POINTS:
             raise ValueError(f"at most {_lib.VOXEL_MAX_POINTS} points per upsert call, got {n}")
+        self._pull_count()
         if self._n + n > self._cap:
             self._grow(self._n + n)
         ids = torch.empty(n, dtype=torch.int32, device=self.device)
@@ -94,8 +118,9 @@ class BinaryVoxel:
             ptr(self._scratch), self._scratch.numel(),
             ptr(self._status.word) if self._status is not None else None, stream_ptr())
         check(st, "stac_voxel_upsert")
-        # one 4-byte read per call: the managers size the voxel memory from the voxel count
-        self._n = int(self._n_dev.item())
+        # the new count travels to pinned memory behind the kernels; nobody waits for it here
+        self._unread += n
+        self._mirror.push(self._n_dev)
         return ids
 
     @torch.no_grad()
@@ -142,16 +167,20 @@ class BinaryVoxel:
 
     # ------------------------------------------------------------------ accessors
     def get_voxel_num(self) -> int:
+        """Exact number of voxels (waits for the last upsert to finish if need be)."""
+        self._sync_count()
         return self._n
 
     def get_voxel_size(self) -> float:
         return self._voxel_size
 
     def get_voxel_keys_1d(self) -> torch.Tensor:
+        self._sync_count()
         return self._table_keys[: self._n]
 
     def get_voxel_keys(self) -> torch.Tensor:
         """Integer coordinates [N,3] int32, unpacked from the 63-bit keys."""
+        self._sync_count()
         k = self._table_keys[: self._n]
         off = 1 << 20
         m = (1 << 21) - 1

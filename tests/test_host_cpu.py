@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
         assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
     assert set(_lib.SIGNATURES) == set(names)
     lib = _lib.lib()
-    assert lib.stac_abi_version() == 1
+    assert lib.stac_abi_version() == 2
     assert lib.stac_status_string(1) == b"bad argument"
     # row log-sum-exps (+ 256 words of flags and counters, rounded up to 256 bytes) + two partial results per CTA
     lse_bytes = ((1041 * 16 + 256) * 4 + 255) // 256 * 256
@@ -43,8 +43,8 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layout_matches_header():
     import ctypes
     from stac_b200 import _lib
-    # 10 4-byte fields, 6 pointers + int (+pad), 7 pointers + int (+pad), 10 pointers, int (+pad), pointer
-    assert ctypes.sizeof(_lib.StacPool) == 40 + 6 * 8 + 8 + 7 * 8 + 8 + 10 * 8 + 8 + 8
+    # 10 4-byte fields, 6 pointers + int (+pad), 7 pointers + int (+pad), 10 pointers, int (+pad), 2 pointers
+    assert ctypes.sizeof(_lib.StacPool) == 40 + 6 * 8 + 8 + 7 * 8 + 8 + 10 * 8 + 8 + 8 + 8
     assert ctypes.sizeof(_lib.StacEvicted) == 8 * 8 + 8
 
 

@@ -342,3 +342,49 @@ def test_long_stream_with_bounded_voxel_memory():
     # the pools themselves never grow past their bounds (the row maps grow with the voxel count)
     assert kv._vstore._buf_cap <= max_buf and kv._vstore._piv_cap <= max_piv
     kv.free()
+
+
+def test_steady_state_steps_never_wait_for_the_gpu():
+    """The reference's loop blocks on the GPU several times per chunk (.item(), .cpu().tolist(),
+    a stream synchronise inside the merger, stream_session.py:451-553).  Here a steady-state
+    chunk (append_kv + attention per layer, append_positions, retrieve, prune with eviction
+    merge) must not contain a single implicit synchronisation: torch raises on any under
+    set_sync_debug_mode("error").  Counters are read one step late from pinned memory."""
+    c = dict(cases.MANAGER_GPU)
+    kv = _make(c)
+    L, H, D = c["L"], c["H"], c["D"]
+    dev = torch.device(DEV)
+    inputs = []
+    for k, v, cs, pts, mask in cases.manager_inputs(c):
+        inputs.append((torch.from_numpy(k).to(torch.bfloat16).to(dev), torch.from_numpy(v).to(torch.bfloat16).to(dev),
+                       torch.from_numpy(pts).to(dev), torch.from_numpy(mask).to(dev)))
+    g = torch.Generator(device="cpu").manual_seed(5)
+    Tq = inputs[0][0].shape[2]
+    q = torch.randn(1, Tq, H, D, generator=g).to(torch.bfloat16).to(dev)
+
+    def step(i):
+        k, v, pts, mask = inputs[i]
+        for l in range(L):
+            kv.append_kv(k[l][None], v[l][None], l)
+            kv.decode_sparse_attn(q, l)
+        kv.append_positions(pts, mask)
+        if i >= 6:
+            for l in range(L):
+                kv.retrieve_kv(l, return_buf=True)
+        kv.prune_kv()
+
+    warm = 12                     # past the first evictions, pool growth and scratch sizing
+    for i in range(warm):
+        step(i)
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        for i in range(warm, len(inputs)):
+            step(i)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    kv.check_status()
+    info = kv.get_merger_info()
+    assert info["pivot_pool_used"] > 0 and info["used_voxels"] == kv._vm.get_voxel_num()
+    kv.free()

@@ -176,3 +176,52 @@ def test_stream_session_pipeline_runs_unchanged():
         "no token reached the voxel memory"
     for stage in ("aggregator_infer_time", "kv_position_time", "kv_retrieval_time", "kv_evict_merge_time"):
         assert stage in out["stage_ms_per_frame"], stage
+
+
+@needs_ref
+def test_fused_qkv_epilogue_matches_the_reference_layer(ref_modules):
+    """append_qkv (LayerNorm of q and k, 2-D rotary embedding, bf16 rounding, K/V and token ids
+    written into the cache tail in one kernel) against the lines of the reference's
+    SparseAttention.forward that it replaces (causalvggt/layers/attention.py:117-128, :141), run
+    under bf16 autocast as main.py runs them."""
+    from stac_b200.stac import STACVoxelKV
+    dev = torch.device("cuda:0")
+    torch.manual_seed(9)
+    dim, heads, ph, pw, special = 256, 4, 5, 6, 5
+    tpf = ph * pw + special
+    rope = ref_modules["Rope"](frequency=100)
+    attn = ref_modules["SparseAttention"](dim=dim, num_heads=heads, qk_norm=True, rope=rope).to(dev).eval()
+    with torch.no_grad():        # non-trivial affine parameters
+        for ln in (attn.q_norm, attn.k_norm):
+            ln.weight.copy_(1 + 0.2 * torch.randn_like(ln.weight))
+            ln.bias.copy_(0.1 * torch.randn_like(ln.bias))
+    attn.set_layer_idx(0)
+    pos1 = ref_modules["PositionGetter"]()(1, ph, pw, device=dev) + 1
+    pos1 = torch.cat([torch.zeros(1, special, 2, device=dev, dtype=pos1.dtype), pos1], 1)
+    mgr = STACVoxelKV(num_layers=1, num_heads=heads, head_dim=dim // heads, **_manager_kwargs(tpf, dev))
+    mgr.reset()
+    done = 0
+    for frames in (2, 1):
+        N = frames * tpf
+        x = torch.randn(1, N, dim, device=dev) * 2
+        pos = pos1.repeat(1, frames, 1)
+        with torch.no_grad(), torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16):
+            qkv = attn.qkv(x)                                                    # the projection itself
+            r = qkv.reshape(1, N, 3, heads, dim // heads).permute(2, 0, 3, 1, 4)
+            q, k, v = r.unbind(0)
+            q, k = attn.q_norm(q), attn.k_norm(k)
+            q = attn.rope(q, pos).type_as(v)
+            k = attn.rope(k, pos).type_as(v)
+        q_ours = mgr.append_qkv(qkv, 0, q_norm=attn.q_norm, k_norm=attn.k_norm, rope=attn.rope, pos=pos)
+        torch.cuda.synchronize()
+
+        def ulps(a, b):          # distance in bf16 steps of the larger magnitude
+            a, b = a.float(), b.float()
+            return ((a - b).abs() / (torch.maximum(a.abs(), b.abs()).clamp_min(1e-3) * 2 ** -7)).max().item()
+        assert ulps(q_ours[0], q[0].transpose(0, 1)) <= 1.01
+        assert ulps(mgr.key_cache_hot[0][:, done:done + N], k[0]) <= 1.01
+        assert torch.equal(mgr.value_cache_hot[0][:, done:done + N], v[0])
+        want_ids = torch.arange(done, done + N, device=dev).expand(heads, -1)
+        assert torch.equal(mgr._token_indices_hot[0][:, done:done + N], want_ids)
+        done += N
+    assert mgr.get_offset() == [done]
