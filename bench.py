@@ -162,7 +162,11 @@ class Stream:
         from stac_b200.stac import STACVoxelKV
         c = dict(CFG)
         if heads is not None:
-            c["heads"] = heads          # head-sharded stream: this rank owns `heads` of the 16 heads
+            # head-sharded stream: this rank owns `heads` of the 16 heads and the same share of the
+            # bounded voxel memory (2 M slots per layer for all heads together)
+            c["max_buffer_slots"] = c["max_buffer_slots"] * heads // c["heads"]
+            c["max_pivot_slots"] = c["max_pivot_slots"] * heads // c["heads"]
+            c["heads"] = heads
         self.cfg = c
         self.torch, self.dev = torch, device
         buffer_size = c["chunk"] + len(c["pinned"]) + c["window"] + c["hh"]
@@ -497,8 +501,8 @@ def run_ours(args):
                                     "prune_total": round(sum(prune_ms) / K, 3)},
                                    **{k_: round(sum(v_) / K, 4) for k_, v_ in stage_ms.items()}),
         "pool": {"voxels": info["used_voxels"], "pivots": info["pivot_pool_used"],
-                 "buffered": info["buffer_pool_used"], "buffer_slots_max": c["max_buffer_slots"],
-                 "pivot_slots_max": c["max_pivot_slots"], "dropped_tokens": info["dropped_tokens"],
+                 "buffered": info["buffer_pool_used"], "buffer_slots_max": stream.cfg["max_buffer_slots"],
+                 "pivot_slots_max": stream.cfg["max_pivot_slots"], "dropped_tokens": info["dropped_tokens"],
                  "tokens_evicted": info["token_count"], "retrieved_valid_pivots": ret_valid,
                  "queried_voxels_mean": round(Q, 1)},
     }
