@@ -38,7 +38,7 @@ CFG = dict(layers=24, heads=16, head_dim=64, tpf=1041, special=5, patch_h=37, pa
            temperature=0.9, prefill_chunks=40,
            # bounded voxel memory of the long-stream configuration: 2M slots per layer
            max_buffer_slots=2_000_000 * 24, max_pivot_slots=2_000_000 * 24)
-ATTN_TRAFFIC_BYTES_PER_CALL = 153.7e6
+ATTN_TRAFFIC_BYTES_PER_CALL = 138.9e6
 METRIC = "stac_hot_path_streaming_frames_per_sec"
 WORKLOAD = ("config4-hot-path: CausalVGGT+STAC stream shapes (24 layers x 16 heads x 64, 1041 tokens/frame, "
             "chunk 4, window 8, hh 2, pinned [0], retrieval 2 frames, bf16); backbone replaced by synthetic "
@@ -493,9 +493,9 @@ def run_ours(args):
                      "flops_formula": "(4+2r)*H*M*N*D, r=1, N = all keys", "live_key_fraction": live_frac,
                      "avg_ms_per_call": round(float(np.mean(att_ms)), 4),
                      # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one call at
-                     # this shape (M=4164, N=17700), one ncu capture
+                     # this shape (M=4164, N=17697), one ncu capture per kernel
                      "traffic": ATTN_TRAFFIC_BYTES_PER_CALL,
-                     "traffic_unit": "bytes per call (fwd 108.4 MB + colsum 45.3 MB; algorithmic 135 MB)"},
+                     "traffic_unit": "bytes per call (fwd 84.7 + 8.8 MB, colsum 45.4 MB; algorithmic 135 MB)"},
         "roofline_memory": roof_mem,
         "stages_ms_per_step": dict({"attention_24_layers": round(sum(att_ms) / K, 3),
                                     "prune_total": round(sum(prune_ms) / K, 3)},

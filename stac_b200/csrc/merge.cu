@@ -71,6 +71,18 @@ template <> struct Elem<__nv_bfloat16> {
   static constexpr bool kIsBf16 = true;
 };
 
+// One slot of a global work list per calling lane: the lanes of a warp that push at the same time
+// take consecutive slots with ONE atomic (the order of a list never reaches an output).
+__device__ __forceinline__ int list_push(int* counter) {
+  const unsigned m = __activemask();
+  const unsigned lane = threadIdx.x & 31;
+  const int leader = __ffs(m) - 1;
+  int base = 0;
+  if (static_cast<int>(lane) == leader) base = atomicAdd(counter, __popc(m));
+  base = __shfl_sync(m, base, leader);
+  return base + __popc(m & ((1u << lane) - 1u));
+}
+
 struct MergeParams {
   // geometry
   int heads, D, P, B, voxel_cap, voxel_used;
@@ -455,7 +467,7 @@ __global__ void __launch_bounds__(256) tokens_sim_kernel(const MergeParams p) {
     p.tok_sim[hb + i] = best_sim;
     p.tok_best[hb + i] = best;
     if (best_sim >= p.sim_thresh && atomicExch(&p.row_flag[hb + ri], 1) == 0)
-      p.merge_list[atomicAdd(&p.plan[kPlanMergeCount], 1)] = make_int2(h, ri);
+      p.merge_list[list_push(&p.plan[kPlanMergeCount])] = make_int2(h, ri);
   }
 }
 
@@ -649,7 +661,7 @@ __global__ void __launch_bounds__(256) rows_rank_kernel(const MergeParams p) {
   const int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
   const int s0 = rst[ri], s1 = rst[ri + 1];
   if (s1 - s0 > 32) {
-    p.defer_list[atomicAdd(&p.plan[kPlanDeferCount], 1)] = make_int2(h, ri);
+    p.defer_list[list_push(&p.plan[kPlanDeferCount])] = make_int2(h, ri);
     return;
   }
   const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
@@ -880,8 +892,8 @@ __global__ void __launch_bounds__(256) rows_phase_b1a_kernel(const MergeParams p
   const int* od = p.old_dest + (hb + ri) * kMaxB;
   bool moves = false;
   for (int c = 0; c < nbuf; ++c) moves = moves || (od[c] != c);
-  if (moves) p.move_list[atomicAdd(&p.plan[kPlanMoveCount], 1)] = make_int2(h, ri);
-  if (info.z & 1) p.full_list[atomicAdd(&p.plan[kPlanFullCount], 1)] = make_int2(h, ri);
+  if (moves) p.move_list[list_push(&p.plan[kPlanMoveCount])] = make_int2(h, ri);
+  if (info.z & 1) p.full_list[list_push(&p.plan[kPlanFullCount])] = make_int2(h, ri);
   else p.buf_row_cnt[r] = newcnt;
 }
 
@@ -1003,10 +1015,12 @@ __global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p) 
 }
 
 // Full buffers -> one pivot each, inserted into the row's pivot slots; the buffer row is released.
-// Eight lanes per row, each holding eight of the 64 values of every token (16-byte loads), so a
-// warp works on four rows at once.
+// Eight lanes per row, each holding eight of the 64 values of a token (16-byte loads), so a warp
+// works on four rows at once.  Tokens are streamed (keys twice: once for the weights, once for
+// the weighted mean; the second read hits the cache) so that few registers are live and many
+// rows are in flight per SM.
 template <typename T>
-__global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(128, 8) rows_phase_b2_kernel(const MergeParams p) {
   const int lane = threadIdx.x & 31, sub = threadIdx.x & 7;
   const int gbase = lane & 24;                       // first lane of this group
   const unsigned gmask = 0xffu << gbase;
@@ -1030,28 +1044,6 @@ __global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p)
     // ---- the buffer is full: B tokens -> one pivot (stac/merger.py:408-461)
     float ts = 0.f;
     if (sub < B) ts = fmaxf(p.buf_S[my_seg], 1e-6f);
-    float tk[kMaxB][8];
-    float den[kMaxB];
-#pragma unroll
-    for (int c = 0; c < kMaxB; ++c) {
-      const int sg = __shfl_sync(gmask, my_seg, gbase + c);
-      den[c] = 1.f;
-      if (c < B) {
-        Row8<T>::load(bK + static_cast<long long>(sg) * D, sub, tk[c]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) tk[c][e] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int c = 0; c < kMaxB; ++c) {
-      if (c < B) {
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ss += tk[c][e] * tk[c][e];
-        den[c] = fmaxf(sqrtf(group8_sum(ss, gmask)), 1e-6f);
-      }
-    }
     int seed = 0;
     float seed_s = -INFINITY, sumS = 0.f;
     for (int c = 0; c < B; ++c) {
@@ -1063,29 +1055,40 @@ __global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p)
       sumS = __fadd_rn(sumS, sc);
     }
     float kn_seed[8];
+    {
+      const int sg = __shfl_sync(gmask, my_seg, gbase + seed);
+      float k[8];
+      Row8<T>::load(bK + static_cast<long long>(sg) * D, sub, k);
+      float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) kn_seed[e] = 0.f;
+      for (int e = 0; e < 8; ++e) ss += k[e] * k[e];
+      const float den = fmaxf(sqrtf(group8_sum(ss, gmask)), 1e-6f);
 #pragma unroll
-    for (int c = 0; c < kMaxB; ++c) {
-      if (c == seed) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kn_seed[e] = __fdiv_rn(tk[c][e], den[c]);
-      }
+      for (int e = 0; e < 8; ++e) kn_seed[e] = __fdiv_rn(k[e], den);
     }
+    // pass 1 over the keys: w_c = exp(cos(k_c, seed))
     float w[kMaxB];
     float Wsum = 0.f;
 #pragma unroll
     for (int c = 0; c < kMaxB; ++c) {
       w[c] = 0.f;
       if (c < B) {
+        const int sg = __shfl_sync(gmask, my_seg, gbase + c);
+        float k[8];
+        Row8<T>::load(bK + static_cast<long long>(sg) * D, sub, k);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += k[e] * k[e];
+        const float den = fmaxf(sqrtf(group8_sum(ss, gmask)), 1e-6f);
         float d = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) d += __fdiv_rn(tk[c][e], den[c]) * kn_seed[e];
+        for (int e = 0; e < 8; ++e) d += __fdiv_rn(k[e], den) * kn_seed[e];
         d = fminf(1.f, fmaxf(-1.f, group8_sum(d, gmask)));
         w[c] = expf(d);
         Wsum = __fadd_rn(Wsum, w[c]);
       }
     }
+    // pass 2: the weighted means of keys and values
     float nk[8], nv[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) nk[e] = nv[e] = 0.f;
@@ -1095,11 +1098,12 @@ __global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p)
       if (c < B) {
         const float cn = __fdiv_rn(w[c], wden);
         const int sg = __shfl_sync(gmask, my_seg, gbase + c);
-        float tv[8];
+        float tk[8], tv[8];
+        Row8<T>::load(bK + static_cast<long long>(sg) * D, sub, tk);
         Row8<T>::load(bV + static_cast<long long>(sg) * D, sub, tv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          nk[e] = __fadd_rn(nk[e], __fmul_rn(cn, tk[c][e]));
+          nk[e] = __fadd_rn(nk[e], __fmul_rn(cn, tk[e]));
           nv[e] = __fadd_rn(nv[e], __fmul_rn(cn, tv[e]));
         }
       }
@@ -1117,87 +1121,74 @@ __global__ void __launch_bounds__(128) rows_phase_b2_kernel(const MergeParams p)
       }
     } else {
       // saturated: fold the lowest-weight pivot into its most similar neighbour, reuse its slot
-      float pkn[kMaxP][8];
-      float pw[kMaxP];
-      int ps[kMaxP];
+      int ps_l = -1;                  // lane q < P holds segment and weight of pivot q
+      float pw_l = INFINITY;
+      if (sub < p.P) {
+        ps_l = p.piv_row_seg[r * p.P + sub];
+        pw_l = p.piv_W[ps_l];
+      }
       int victim = 0;
       float wmin = INFINITY;
-#pragma unroll
-      for (int q = 0; q < kMaxP; ++q) {
-        ps[q] = -1;
-        pw[q] = INFINITY;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) pkn[q][e] = 0.f;
-        if (q < p.P) {
-          ps[q] = p.piv_row_seg[r * p.P + q];
-          pw[q] = p.piv_W[ps[q]];
-          if (pw[q] < wmin) {
-            wmin = pw[q];
-            victim = q;
-          }
-          float pk[8];
-          Row8<T>::load(pK + static_cast<long long>(ps[q]) * D, sub, pk);
-          // the reference normalises in the pool dtype here (stac/merger.py:493-495)
-          float ss = 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ss += pk[e] * pk[e];
-          float nrm = Elem<T>::round(sqrtf(group8_sum(ss, gmask)));
-          nrm = fmaxf(nrm, Elem<T>::round(1e-6f));
-#pragma unroll
-          for (int e = 0; e < 8; ++e) pkn[q][e] = Elem<T>::round(__fdiv_rn(pk[e], nrm));
+      for (int q = 0; q < p.P; ++q) {
+        const float wq = __shfl_sync(gmask, pw_l, gbase + q);
+        if (wq < wmin) {
+          wmin = wq;
+          victim = q;
         }
       }
+      // keys normalised in the pool dtype, as the reference does here (stac/merger.py:493-495)
+      auto load_normalised = [&](int seg, float (&out)[8]) {
+        float pk[8];
+        Row8<T>::load(pK + static_cast<long long>(seg) * D, sub, pk);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += pk[e] * pk[e];
+        float nrm = Elem<T>::round(sqrtf(group8_sum(ss, gmask)));
+        nrm = fmaxf(nrm, Elem<T>::round(1e-6f));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out[e] = Elem<T>::round(__fdiv_rn(pk[e], nrm));
+      };
+      const int vseg = __shfl_sync(gmask, ps_l, gbase + victim);
+      const float Wv = __shfl_sync(gmask, pw_l, gbase + victim);
       float vn[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) vn[e] = 0.f;
-#pragma unroll
-      for (int q = 0; q < kMaxP; ++q)
-        if (q == victim) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) vn[e] = pkn[q][e];
-        }
+      load_normalised(vseg, vn);
       int nb = 0;
       float best = -INFINITY;
+      for (int q = 0; q < p.P; ++q) {
+        if (q == victim) continue;
+        const int qseg = __shfl_sync(gmask, ps_l, gbase + q);
+        float pkn[8];
+        load_normalised(qseg, pkn);
+        float d = 0.f;
 #pragma unroll
-      for (int q = 0; q < kMaxP; ++q) {
-        if (q < p.P && q != victim) {
-          float d = 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) d += pkn[q][e] * vn[e];
-          d = Elem<T>::round(group8_sum(d, gmask));
-          if (d > best) {
-            best = d;
-            nb = q;
-          }
+        for (int e = 0; e < 8; ++e) d += pkn[e] * vn[e];
+        d = Elem<T>::round(group8_sum(d, gmask));
+        if (d > best) {
+          best = d;
+          nb = q;
         }
       }
       if (p.P == 1) nb = victim;   // no neighbour to fold into: the victim is simply replaced
       float scale;
       if (Elem<T>::kIsBf16) scale = Elem<T>::round(expf(Elem<T>::round(best - 1.0f)));
       else scale = expf(best - 1.0f);
-      int vseg = -1, nseg = -1;
-      float Wv = 0.f, Wn = 0.f;
-#pragma unroll
-      for (int q = 0; q < kMaxP; ++q) {
-        if (q == victim) { vseg = ps[q]; Wv = pw[q]; }
-        if (q == nb) { nseg = ps[q]; Wn = pw[q]; }
-      }
+      const int nseg = __shfl_sync(gmask, ps_l, gbase + nb);
+      const float Wn = __shfl_sync(gmask, pw_l, gbase + nb);
       if (p.P > 1) {
         const float Wj = __fmul_rn(Wv, scale);
         const float denom = fmaxf(__fadd_rn(Wj, Wn), 1e-8f);
         const float fj = __fdiv_rn(Wj, denom), fk = __fdiv_rn(Wn, denom);
-        float kj[8], kk[8], vj[8], vk[8];
-        Row8<T>::load(pK + static_cast<long long>(vseg) * D, sub, kj);
-        Row8<T>::load(pK + static_cast<long long>(nseg) * D, sub, kk);
-        Row8<T>::load(pV + static_cast<long long>(vseg) * D, sub, vj);
-        Row8<T>::load(pV + static_cast<long long>(nseg) * D, sub, vk);
+        float a[8], b[8];
+        Row8<T>::load(pK + static_cast<long long>(vseg) * D, sub, a);
+        Row8<T>::load(pK + static_cast<long long>(nseg) * D, sub, b);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          kk[e] = __fadd_rn(__fmul_rn(fj, kj[e]), __fmul_rn(fk, kk[e]));
-          vk[e] = __fadd_rn(__fmul_rn(fj, vj[e]), __fmul_rn(fk, vk[e]));
-        }
-        Row8<T>::store(pK + static_cast<long long>(nseg) * D, sub, kk);
-        Row8<T>::store(pV + static_cast<long long>(nseg) * D, sub, vk);
+        for (int e = 0; e < 8; ++e) b[e] = __fadd_rn(__fmul_rn(fj, a[e]), __fmul_rn(fk, b[e]));
+        Row8<T>::store(pK + static_cast<long long>(nseg) * D, sub, b);
+        Row8<T>::load(pV + static_cast<long long>(vseg) * D, sub, a);
+        Row8<T>::load(pV + static_cast<long long>(nseg) * D, sub, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] = __fadd_rn(__fmul_rn(fj, a[e]), __fmul_rn(fk, b[e]));
+        Row8<T>::store(pV + static_cast<long long>(nseg) * D, sub, b);
         if (sub == 0) {
           p.piv_W[nseg] = denom;
           p.piv_S[nseg] = __fadd_rn(p.piv_S[vseg], p.piv_S[nseg]);
@@ -1303,7 +1294,7 @@ int launch_merge(MergeParams& mp, cudaStream_t st) {
   rows_phase_b1a_kernel<<<grid_a1, 256, 0, st>>>(mp);
   rows_phase_b1m_kernel<T, 2><<<148 * 6, 256, 0, st>>>(mp);
   tokens_place_kernel<T><<<grid_sim, 256, 0, st>>>(mp);
-  rows_phase_b2_kernel<T><<<148 * 8, 128, 0, st>>>(mp);
+  rows_phase_b2_kernel<T><<<148 * 16, 128, 0, st>>>(mp);
   finalize_kernel<<<148 * 4, 256, 0, st>>>(mp);   // grid-stride over the freed ids (known on the device only)
   carry_overflow_kernel<T><<<148, 256, 0, st>>>(mp);
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;

@@ -102,6 +102,26 @@ __device__ __forceinline__ void for_each_candidate(const RetrieveParams& p, int 
   }
 }
 
+// Shared-memory counters are bumped once per warp and distinct value, not once per lane: the
+// weights of one head fall into few histogram bins (their exponents are alike), and the lanes of
+// a warp would otherwise queue up on the same word.
+__device__ __forceinline__ void hist_add(int* hist, unsigned int bin) {
+  const unsigned int m = __activemask();
+  const unsigned int peers = __match_any_sync(m, bin);
+  const unsigned int lane = threadIdx.x & 31;
+  if ((peers & ((1u << lane) - 1u)) == 0u) atomicAdd(&hist[bin], __popc(peers));
+}
+// One slot of a shared list per calling lane (slots of one warp are consecutive).
+__device__ __forceinline__ int list_push(int* counter) {
+  const unsigned int m = __activemask();
+  const unsigned int lane = threadIdx.x & 31;
+  const int leader = __ffs(m) - 1;
+  int base = 0;
+  if (static_cast<int>(lane) == leader) base = atomicAdd(counter, __popc(m));
+  base = __shfl_sync(m, base, leader);
+  return base + __popc(m & ((1u << lane) - 1u));
+}
+
 // Top R candidates of one head by (weight desc, candidate index asc).  A radix select on the
 // weight key finds the threshold digit by digit (12 + 12 + 8 bits, one pass over the candidates
 // per digit) and stops as soon as the candidates at or above the current prefix fit the
@@ -131,7 +151,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const R
     const unsigned int pf = prefix;
     const int sh_old = shift;
     for_each_candidate(p, h, Q, [&](unsigned int wk, unsigned int) {
-      if (sh_old == 32 || (wk >> sh_old) == pf) atomicAdd(&hist[(wk >> new_shift) & ((1u << width) - 1u)], 1);
+      if (sh_old == 32 || (wk >> sh_old) == pf) hist_add(hist, (wk >> new_shift) & ((1u << width) - 1u));
     });
     __syncthreads();
     // the digit at which the count from the top reaches `need`
@@ -183,7 +203,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const R
     const int sh = shift;
     for_each_candidate(p, h, Q, [&](unsigned int wk, unsigned int idx) {
       if (take_all || sh == 32 || (wk >> sh) >= pf) {
-        const int pos = atomicAdd(&sh_count, 1);
+        const int pos = list_push(&sh_count);
         if (pos < kSelCap) cand[pos] = (static_cast<unsigned long long>(wk) << 32) | (0xFFFFFFFFu - idx);
       }
     });
@@ -193,7 +213,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const R
     const unsigned int T = prefix;
     for_each_candidate(p, h, Q, [&](unsigned int wk, unsigned int idx) {
       if (wk > T) {
-        const int pos = atomicAdd(&sh_count, 1);
+        const int pos = list_push(&sh_count);
         cand[pos] = (static_cast<unsigned long long>(wk) << 32) | (0xFFFFFFFFu - idx);
       }
     });
