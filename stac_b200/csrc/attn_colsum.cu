@@ -397,7 +397,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // Fast forward kernel.  Softmax is invariant to the reference subtracted before the exponent,
 // so instead of a running maximum every row uses ONE reference: the exact maximum of its
 // first key tile.  Nothing is ever rescaled: P V accumulates in TMEM across all key tiles of
-// the row block, three softmax warpgroups take key tiles round-robin and keep only a partial
+// the row block, the softmax warpgroups (four) take key tiles round-robin and keep only a partial
 // row sum each.  The scheme is exact as long as no later score exceeds the reference by more
 // than 2^60 (probabilities then stay far inside the bf16 / fp32 range); a row whose sum of
 // probabilities leaves that range raises `fallback` and the exact kernel, launched right
@@ -405,8 +405,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 //
 // Shared memory carries only the operands TMA brings in.  Key tiles are 112 keys wide so that
 // FOUR score buffers fit beside the output accumulator in the 512 TMEM columns (4 x 112 + 64):
-// three are being exponentiated while the fourth goes through P V and the next Q K^T, so a
-// warpgroup finds its next tile scored when it gets there.  The probabilities go back into
+// with four softmax warpgroups each has a buffer of its own and the other three keep the
+// exponential unit busy while one waits for its buffer to go through P V and the next Q K^T
+// (with three, the fourth buffer is scored ahead, so a warpgroup finds its next tile ready;
+// measured 3.4 % slower at 4164 x 17697 keys than four).  The probabilities go back into
 // the columns their scores came from (bf16, two per column) and feed the P V MMA as its A
 // operand straight from tensor memory.  The tensor pipe has a floor of about 48 clocks per
 // MMA instruction whatever its width and idles while its issuing thread does anything else,
@@ -427,7 +429,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // never two (a CTA's middle segments are whole items of at least kFastMinSplitTiles tiles, far
 // longer than the few tiles the score ring lets the warpgroups be apart).
 // ---------------------------------------------------------------------------------------
-constexpr int kFastThreads = 512;   // warpgroup 0 control (warps 0, 3 TMA, warps 1-2 MMA issue), 1..3 softmax
+#ifndef STAC_FAST_WGS
+#define STAC_FAST_WGS 4
+#endif
+constexpr int kFastWgs = STAC_FAST_WGS;            // softmax warpgroups (3 or 4); key tile c goes to warpgroup c % kFastWgs
+static_assert(kFastWgs == 3 || kFastWgs == 4, "three or four softmax warpgroups");
+// With three warpgroups a thread double-buffers its tensor-memory loads (64 score registers) and
+// prefetches its next tile; with four the launch leaves 96 registers per thread, so loads are
+// single-buffered and the fourth warp per scheduler hides their latency instead.  The hand-over
+// rules between segments hold for both: a warpgroup's last tile of a middle segment (at least
+// kFastMinSplitTiles >= 2 * kFastWgs tiles) lies kFastRing or more tiles into it, so its score
+// buffer is a reused one and cannot be scored before the previous segment's accumulator has
+// been read out.
+constexpr bool kFastDouble = kFastWgs == 3;
+constexpr int kFastThreads = 128 + 128 * kFastWgs;   // warpgroup 0 control (warps 0, 3 TMA, warps 1-2 MMA issue), then softmax
 constexpr int kFastKStages = 5;
 constexpr int kFastVStages = 5;
 constexpr int kFT = 112;                        // keys per tile
@@ -437,22 +452,24 @@ constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 constexpr int kPartFloats = kBM * kD + 2 * kBM; // one partial result: O[128][64], row sums, row references
 constexpr int kFastMaxCtas = 160;               // partial-result slots are provided for this many CTAs
 constexpr int kFastMinSplitTiles = 8;           // shorter key ranges run one CTA per item
+static_assert(kFastMinSplitTiles >= 2 * kFastWgs && kFastRing <= kFastMinSplitTiles, "segment hand-over rule");
 #ifndef STAC_FAST_PAIR_MASK
 #define STAC_FAST_PAIR_MASK 0x8080u
 #endif
 constexpr unsigned kFastPairMask = STAC_FAST_PAIR_MASK;   // which of 16 consecutive PAIRS of exponentials run on the FMA pipes
-constexpr int kFastCtlRegs = 56, kFastSoftmaxRegs = 152;   // setmaxnreg targets; must fit the launch allocation
-static_assert(128 * kFastCtlRegs + 384 * kFastSoftmaxRegs <= kFastThreads * ((65536 / kFastThreads) / 8 * 8),
+// setmaxnreg targets; must fit the launch allocation
+constexpr int kFastCtlRegs = kFastWgs == 3 ? 56 : 40, kFastSoftmaxRegs = kFastWgs == 3 ? 152 : 104;
+static_assert(128 * kFastCtlRegs + 128 * kFastWgs * kFastSoftmaxRegs <= kFastThreads * ((65536 / kFastThreads) / 8 * 8),
               "fast forward kernel: setmaxnreg targets exceed the CTA's register allocation");
 
 struct FastSmem {
   uint8_t q[2][kTileBytes];                     // query tile of the segment (parity)
   uint8_t k[kFastKStages][kFastTileBytes];
   uint8_t v[kFastVStages][kFastTileBytes];
-  float bias2[3][kBN];
+  float bias2[kFastWgs][kBN];
   float m_ref[2][kBM];                          // row references of the segment (parity)
-  float lpart[2][2][kBM];                       // row sums of warpgroups 1 and 2 (segment parity)
-  int live[2][2];                               // did warpgroup 1 / 2 see a key that is not masked (segment parity)
+  float lpart[2][kFastWgs - 1][kBM];            // row sums of warpgroups 1.. (segment parity)
+  int live[2][kFastWgs - 1];                    // did warpgroup 1.. see a key that is not masked (segment parity)
   uint64_t q_full[2];
   uint64_t q_empty[2];
   uint64_t k_full[kFastKStages];
@@ -463,7 +480,7 @@ struct FastSmem {
   uint64_t p_full[kFastRing];    // its probabilities are in TMEM
   uint64_t buf_free[kFastRing];  // the P V MMAs that read them are done
   uint64_t ref_ready[2];
-  uint64_t l_ready[2];           // warpgroups 1 and 2 have published their row sums of the segment (parity)
+  uint64_t l_ready[2];           // warpgroups 1.. have published their row sums of the segment (parity)
   uint64_t o_done;               // all P V MMAs of the segment are complete
   uint64_t o_free;               // the segment's accumulator has been read out of TMEM
   uint32_t tmem_base;
@@ -565,7 +582,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&sm.q_full[i], 1);
       mbar_init(&sm.q_empty[i], 1);
       mbar_init(&sm.ref_ready[i], 128);
-      mbar_init(&sm.l_ready[i], 256);
+      mbar_init(&sm.l_ready[i], 128 * (kFastWgs - 1));
     }
     for (int s = 0; s < kFastKStages; ++s) {
       mbar_init(&sm.k_full[s], 1);
@@ -725,11 +742,11 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const float c2 = p.scale_log2;
     const uint64_t c2c2 = pack_f32x2(c2, c2);
     const float* bias2 = sm.bias2[g];
-    uint32_t ra[32], rb[32], pk[16];
+    uint32_t ra[32], rb[32], pk[16];   // rb: second score buffer (three warpgroups) and the read-out of O
     bool overflow = false;
     FwdWalk walk(p, n_tiles);
     int seg = 0, item, t0, t1;
-    int c_base = 0;   // key tiles of earlier segments: tile c of the CTA uses ring buffer c % 4, warpgroup c % 3
+    int c_base = 0;   // key tiles of earlier segments: tile c of the CTA uses ring buffer c % 4, warpgroup c % kFastWgs
     for (; walk.next(item, t0, t1); ++seg) {
       const int h = item / p.n_q_tiles, m_tile = item - h * p.n_q_tiles;
       const int len = t1 - t0;
@@ -740,7 +757,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       bool have_ref = false;
       bool any_live = false;  // some key tile of this warpgroup in this segment had a key that is not masked
       bool fetching = false;  // the first 32 scores of the next tile are already on their way into ra
-      for (int x = (g + 3 - c_base % 3) % 3; x < len; x += 3) {
+      for (int x = (g + kFastWgs - c_base % kFastWgs) % kFastWgs; x < len; x += kFastWgs) {
         const int c = c_base + x;
         const int b = c & (kFastRing - 1), round = c >> 2;
         const int j = t0 + x;
@@ -776,9 +793,10 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           tmem_st16(s_addr + 16, pk);
           tmem_st16(s_addr + 32, pk);
           tmem_st8(s_addr + 48, pk);
-          const int b2n = (c + 3) & (kFastRing - 1), round2n = (c + 3) >> 2;
+          const int b2n = (c + kFastWgs) & (kFastRing - 1), round2n = (c + kFastWgs) >> 2;
           fetching = false;
-          if (x + 3 < len && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2n], round2n & 1))) {
+          if (kFastDouble && x + kFastWgs < len &&
+              __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2n], round2n & 1))) {
             tc_fence_after();
             tmem_ld32(tmem + lane_base + b2n * kFT, ra);
             fetching = true;
@@ -815,40 +833,64 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           negm2 = pack_f32x2(-m_ref, -m_ref);
         }
         // keys 0..31 are on their way into ra
-        tmem_ld_wait();
-        tmem_ld32(s_addr + 32, rb);
-        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
-        else fast_exp_chunk<false, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
-        tmem_st16(s_addr, pk);
-        tmem_ld_wait();
-        tmem_ld32(s_addr + 64, ra);
-        if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2c2, negm2, l0, l1);
-        else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2c2, negm2, l0, l1);
-        tmem_st16(s_addr + 16, pk);
-        tmem_ld_wait();
-        tmem_ld16(s_addr + 96, rb);
-        if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
-        else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
-        tmem_st16(s_addr + 32, pk);
-        tmem_ld_wait();
-        // this warpgroup's next tile of the segment is normally scored by now: start fetching it
-        // (never wait for it here: its buffer is released by another warpgroup's P V, which may
-        // be behind this one)
-        const int b2 = (c + 3) & (kFastRing - 1), round2 = (c + 3) >> 2;
-        const bool more = x + 3 < len;
-        fetching = false;
-        if (more && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
-          tc_fence_after();
-          tmem_ld32(tmem + lane_base + b2 * kFT, ra);
-          fetching = true;
-        }
-        if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2c2, negm2, l0, l1);
-        else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2c2, negm2, l0, l1);
-        tmem_st8(s_addr + 48, pk);
-        if (more && !fetching && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
-          tc_fence_after();                  // second chance, a chunk later
-          tmem_ld32(tmem + lane_base + b2 * kFT, ra);
-          fetching = true;
+        if constexpr (kFastDouble) {
+          tmem_ld_wait();
+          tmem_ld32(s_addr + 32, rb);
+          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
+          tmem_st16(s_addr, pk);
+          tmem_ld_wait();
+          tmem_ld32(s_addr + 64, ra);
+          if (need_bias) fast_exp_chunk<true, 32>(rb, pk, bias2 + 32, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 32>(rb, pk, bias2 + 32, c2c2, negm2, l0, l1);
+          tmem_st16(s_addr + 16, pk);
+          tmem_ld_wait();
+          tmem_ld16(s_addr + 96, rb);
+          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
+          tmem_st16(s_addr + 32, pk);
+          tmem_ld_wait();
+          // this warpgroup's next tile of the segment is normally scored by now: start fetching it
+          // (never wait for it here: its buffer is released by another warpgroup's P V, which may
+          // be behind this one)
+          const int b2 = (c + kFastWgs) & (kFastRing - 1), round2 = (c + kFastWgs) >> 2;
+          const bool more = x + kFastWgs < len;
+          fetching = false;
+          if (more && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+            tc_fence_after();
+            tmem_ld32(tmem + lane_base + b2 * kFT, ra);
+            fetching = true;
+          }
+          if (need_bias) fast_exp_chunk<true, 16>(rb, pk, bias2 + 96, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 16>(rb, pk, bias2 + 96, c2c2, negm2, l0, l1);
+          tmem_st8(s_addr + 48, pk);
+          if (more && !fetching && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
+            tc_fence_after();                  // second chance, a chunk later
+            tmem_ld32(tmem + lane_base + b2 * kFT, ra);
+            fetching = true;
+          }
+        } else {
+          // one score buffer per thread: load, wait, convert, store, chunk by chunk
+          tmem_ld_wait();
+          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
+          tmem_ld32(s_addr + 32, ra);
+          tmem_st16(s_addr, pk);
+          tmem_ld_wait();
+          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 32, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 32>(ra, pk, bias2 + 32, c2c2, negm2, l0, l1);
+          tmem_ld32(s_addr + 64, ra);
+          tmem_st16(s_addr + 16, pk);
+          tmem_ld_wait();
+          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
+          tmem_ld16(s_addr + 96, ra);
+          tmem_st16(s_addr + 32, pk);
+          tmem_ld_wait();
+          if (need_bias) fast_exp_chunk<true, 16>(ra, pk, bias2 + 96, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 16>(ra, pk, bias2 + 96, c2c2, negm2, l0, l1);
+          tmem_st8(s_addr + 48, pk);
+          fetching = false;
         }
         tmem_st_wait();
         tc_fence_before();
@@ -870,12 +912,14 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           m_ref = sm.m_ref[sb][row];
         }
         mbar_wait(&sm.l_ready[sb], (seg >> 1) & 1, p.err, DEV_TIMEOUT_CONSUMER);
-        const float l = (lsum + sm.lpart[sb][0][row]) + sm.lpart[sb][1][row];
+        float l = (lsum + sm.lpart[sb][0][row]) + sm.lpart[sb][1][row];
+        if constexpr (kFastWgs == 4) l += sm.lpart[sb][2][row];
         // A segment whose keys are all masked has no reference (m_ref is a placeholder): it must not
         // take part in a join.  A segment with live keys whose probabilities all underflowed (its
         // first tile was masked, so the placeholder was used, and the live scores lie far below
         // it) cannot be represented: the exact kernel redoes the call.
-        const bool seg_live = any_live || sm.live[sb][0] != 0 || sm.live[sb][1] != 0;
+        bool seg_live = any_live || sm.live[sb][0] != 0 || sm.live[sb][1] != 0;
+        if constexpr (kFastWgs == 4) seg_live = seg_live || sm.live[sb][2] != 0;
         if (seg_live && !(l > 0.f)) overflow = true;
         mbar_wait(&sm.o_done, seg & 1, p.err, DEV_TIMEOUT_MMA);
         tc_fence_after();
@@ -932,9 +976,9 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const float m_pub = seg_live ? m_ref : -INFINITY;
           slot[kBM * kD + kBM + row] = m_pub;
           __threadfence();                       // this thread's part is visible device-wide ...
-          named_bar_sync(4, 128);                // ... and so is every other row's
+          named_bar_sync(6, 128);                // ... and so is every other row's
           if (row == 0) sm.join_flag = atomicAdd(p.part_count + cut, 1);
-          named_bar_sync(4, 128);
+          named_bar_sync(6, 128);
           if (sm.join_flag == 1) {
             // the other CTA's part was complete before its counter increment, which came first
             __threadfence();

@@ -20,7 +20,7 @@ namespace {
 
 constexpr int kSelCap = 8192;     // shared-memory candidate buffer (64-bit keys)
 constexpr int kSelThreads = 512;
-constexpr int kSelBins = 4096;    // 12-bit digits of the weight key, most significant first
+constexpr int kSelBins = 8192;    // counters of one radix digit (13 + 11 + 8 bits, most significant first)
 constexpr int kSelUnroll = 2;     // queried voxels per thread in flight
 
 __device__ __forceinline__ unsigned int wkey(float f) {
@@ -123,14 +123,17 @@ __device__ __forceinline__ int list_push(int* counter) {
 }
 
 // Top R candidates of one head by (weight desc, candidate index asc).  A radix select on the
-// weight key finds the threshold digit by digit (12 + 12 + 8 bits, one pass over the candidates
+// weight key finds the threshold digit by digit (13 + 11 + 8 bits, one pass over the candidates
 // per digit) and stops as soon as the candidates at or above the current prefix fit the
 // shared-memory buffer, which is then sorted; with the usual spread of weights that is after the
 // first digit, i.e. two passes.  Only when more than kSelCap - R candidates share one exact
 // weight is the last group taken in candidate order by an ordered pass.
-__global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const RetrieveParams p) {
-  extern __shared__ unsigned long long cand[];  // kSelCap keys, then kSelBins counters
-  int* hist = reinterpret_cast<int*>(cand + kSelCap);
+__global__ void __launch_bounds__(kSelThreads, 3) retrieve_select_kernel(const RetrieveParams p) {
+  // kSelCap keys; the digit counters live in the same 64 KB (they are dead once the threshold is
+  // known and the keys are collected), so three CTAs fit one SM and 384 heads run in one wave
+  extern __shared__ unsigned long long cand[];
+  int* hist = reinterpret_cast<int*>(cand);
+  static_assert(kSelBins * 4 <= kSelCap * 8, "digit counters must fit the candidate buffer");
   __shared__ int warp_sums[kSelThreads / 32];
   __shared__ int sh_count, sh_bin, sh_above, sh_ties;
   const int h = blockIdx.x;
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const R
   unsigned int prefix = 0;
   int shift = 32, need = R;       // need = how many of the undecided ones are wanted
   bool take_all = false, ordered_ties = false;
-  const int widths[3] = {12, 12, 8};
+  const int widths[3] = {13, 11, 8};
   for (int level = 0; level < 3; ++level) {
     const int width = widths[level];
     const int new_shift = shift - width;
@@ -195,7 +198,8 @@ __global__ void __launch_bounds__(kSelThreads, 2) retrieve_select_kernel(const R
     if (level == 2) ordered_ties = true;            // one exact weight, more copies than fit
     __syncthreads();
   }
-  // ---- collect
+  // ---- collect (the counters are no longer needed: their memory becomes the key buffer)
+  __syncthreads();
   if (threadIdx.x == 0) sh_count = 0;
   __syncthreads();
   if (!ordered_ties) {
@@ -332,7 +336,7 @@ int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_
   int dev = 0;
   if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
   static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
-  const int smem = stac::kSelCap * 8 + stac::kSelBins * 4;
+  const int smem = stac::kSelCap * 8;
   if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(stac::retrieve_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
