@@ -569,16 +569,44 @@ def run_microbench_attn(args):
         call(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     e0.record()
     for i in range(args.steps):
         call(i)
     e1.record()
+    host_us = (time.perf_counter() - t0) / args.steps * 1e6
     torch.cuda.synchronize()
     st.raise_if_set("attention microbench")
-    ms = e0.elapsed_time(e1) / args.steps
+    eager_ms = e0.elapsed_time(e1) / args.steps
+    # The same calls replayed from a CUDA graph (24 calls, one per layer of a chunk): at the
+    # short shapes a call's kernels take less time than the Python and ctypes work of issuing
+    # them, so the eager loop measures the host.  `value` is the graph figure.
+    side = torch.cuda.Stream()
+    n_graph = 24
+    with torch.cuda.stream(side):
+        for i in range(3):
+            call(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            keep = [call(i) for i in range(n_graph)]
+        reps = max(1, (args.steps + n_graph - 1) // n_graph)
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record(side)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(side)
+        torch.cuda.synchronize()
+    st.raise_if_set("attention microbench (graph)")
+    ms = e0.elapsed_time(e1) / (reps * n_graph)
+    del keep
     tf = attn_flops(M, Lk) / (ms / 1e3) / 1e12
     print(json.dumps({"metric": "attn_colsum_tflops", "value": round(tf, 2), "unit": "TFLOP/s",
-                      "ms_per_call": round(ms, 4), "steps": args.steps,
+                      "ms_per_call": round(ms, 4), "timing": f"CUDA graph of {n_graph} calls, {reps} replays",
+                      "eager_ms_per_call": round(eager_ms, 4), "eager_tflops": round(attn_flops(M, Lk) / eager_ms / 1e9, 2),
+                      "host_us_per_call": round(host_us, 1), "steps": args.steps,
                       "config": {"workload": f"config2 attention microbench M={M} Lk={Lk} pivots={n_ret} H=16 D=64 bf16"}}))
 
 

@@ -95,7 +95,7 @@ int stac_attn_colsum(const void* q, int64_t q_row_stride,
  *               power of two, kept at most half full by the caller (stac_voxel_rehash to grow)
  *   n_voxels    i32 device scalar, number of voxels in the table
  * ------------------------------------------------------------------------------------- */
-#define STAC_VOXEL_MAX_POINTS 16384 /* points per stac_voxel_upsert call */
+#define STAC_VOXEL_MAX_POINTS 131072 /* points per stac_voxel_upsert call (125 frames of 1041 tokens) */
 
 size_t stac_voxel_scratch_bytes(int n_points);
 
@@ -110,7 +110,9 @@ int stac_voxel_rehash(const int64_t* table_keys, const int* n_voxels, int table_
  * (k+2^20)*2^42; known keys keep their id, keys new in this call get *n_voxels + rank among
  * the sorted new unique keys.  points f32 [n,3], or ijk i32 [n,3] already quantised (exactly
  * one of the two non-NULL); mask u8 [n] or NULL (0 -> id -1); ids_out i32 [n].  *n_voxels is
- * updated on the device; no host synchronisation. */
+ * updated on the device; no host synchronisation.  n_points <= STAC_VOXEL_MAX_POINTS; up to
+ * 16384 new keys of a call are sorted in shared memory, more (a chunk of sixteen frames or
+ * more on unseen ground) in the scratch, which stac_voxel_scratch_bytes sizes for it. */
 int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* mask, int n_points, float voxel_size,
                       int64_t* table_keys, int table_cap, void* hash_keys, int* hash_vals, int64_t hash_cap,
                       int* n_voxels, int* ids_out, void* scratch, size_t scratch_bytes,

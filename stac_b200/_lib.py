@@ -48,7 +48,7 @@ class StacEvicted(ctypes.Structure):
 (META_BUF_TOP, META_BUF_FREE_LEN, META_PIV_TOP, META_OVER_COUNT, META_BUF_USED, META_PIV_USED, META_DROPPED,
  META_VOXELS) = range(8)
 META_SIZE = 8
-VOXEL_MAX_POINTS = 16384
+VOXEL_MAX_POINTS = 131072
 
 # name -> (restype, argtypes); must list every function declared in include/stac_b200.h
 SIGNATURES = {

@@ -105,6 +105,22 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
 }
 
+#ifdef STAC_TIMESTAMPS
+// Debug build only: first start and last end of each kernel on the GPU's nanosecond timer.
+__device__ unsigned long long g_ts[8] = {~0ull, 0ull, ~0ull, 0ull, ~0ull, 0ull, ~0ull, 0ull};
+__device__ __forceinline__ void ts_mark(int k, bool end) {
+  if (threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (end) atomicMax(&g_ts[2 * k + 1], t);
+    else atomicMin(&g_ts[2 * k], t);
+  }
+}
+#define STAC_TS(k, end) ts_mark(k, end)
+#else
+#define STAC_TS(k, end)
+#endif
+
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k_hot,
                 const __grid_constant__ CUtensorMap tm_v_hot, const __grid_constant__ CUtensorMap tm_k_ret,
@@ -119,7 +135,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int n_tiles = p.n_hot_tiles + p.n_ret_tiles;
   // This kernel is the exact (running-maximum) path.  When it is launched behind the fast
   // kernel it only runs if that one flagged a row whose scores outgrew its fixed reference.
-  if (p.fallback != nullptr && *reinterpret_cast<volatile int*>(p.fallback) == 0) return;
+  STAC_TS(1, false);
+  grid_dep_wait();   // launched behind the fast kernel with programmatic serialization: its flag and outputs are final now
+  if (p.fallback != nullptr && *reinterpret_cast<volatile int*>(p.fallback) == 0) {
+    STAC_TS(1, true);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.bar_q, 1);
@@ -391,6 +412,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  STAC_TS(1, true);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -572,6 +594,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                      const __grid_constant__ CUtensorMap tm_v_ret, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   FastSmem& sm = *reinterpret_cast<FastSmem*>(align1024(smem_raw));
+  STAC_TS(0, false);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_hot = (p.T_hot + kFT - 1) / kFT;
@@ -610,6 +633,9 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t o_tmem = tmem + kFastRing * kFT;   // columns 448..511
+  // The exact kernel behind this one may be scheduled as soon as an SM has room for it (that is,
+  // when this CTA has left); it waits for this grid's completion before it reads the flag.
+  grid_dep_launch();
 
   if (p.zero_colsum != nullptr) {
     // a slice of the column-sum output per CTA (the next kernel adds partial sums onto zeros)
@@ -1029,6 +1055,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  STAC_TS(0, true);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1203,6 +1230,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_k_ret, const ColParams p) {
   extern __shared__ uint8_t smem_raw[];
   ColSmem& sm = *reinterpret_cast<ColSmem*>(align1024(smem_raw));
+  STAC_TS(2, false);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nq = p.n_q_tiles;
@@ -1237,6 +1265,10 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  // Launched with programmatic serialization behind the forward kernels: barriers and tensor
+  // memory are set up while they drain; the row log-sum-exps and the zeroed output are read
+  // and written only after this point.
+  grid_dep_wait();
 
   if (warp < 4) {
     setmaxnreg_dec<kColCtlRegs>();
@@ -1418,6 +1450,7 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  STAC_TS(2, true);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1482,6 +1515,28 @@ size_t attn_lse2_elems_split(int M, int H) { return static_cast<size_t>(H) * sta
 
 // partial results of the split forward kernel: two slots per CTA
 size_t attn_part_elems() { return static_cast<size_t>(2) * kFastMaxCtas * kPartFloats; }
+
+// Launch with programmatic stream serialization: the kernel may become resident while the
+// kernel before it in the stream drains; it calls grid_dep_wait() before it touches anything
+// that kernel wrote.  STAC_PDL=0 builds fall back to plain stream order.
+#ifndef STAC_PDL
+#define STAC_PDL 1
+#endif
+template <typename... KArgs, typename... Args>
+cudaError_t launch_behind(void (*kernel)(KArgs...), dim3 grid, dim3 block, int smem, cudaStream_t stream,
+                          const Args&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = STAC_PDL;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cudaStream_t stream) {
   if (a.D != kD) return STAC_ERR_BAD_ARG;
@@ -1587,8 +1642,10 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   fp.zero_stride = a.colsum_head_stride;
   fp.zero_width = a.T_hot + a.T_ret;
   attn_fwd_fast_kernel<<<grid_fast, kFastThreads, fast_smem, stream>>>(tm_q, tf_kh, tf_vh, tf_kr, tf_vr, fp);
-  attn_fwd_kernel<<<grid_f, kFwdThreads, fwd_smem, stream>>>(tm_q, tm_kh, tm_vh, tm_kr, tm_vr, fp);
   if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(attn_fwd_kernel, grid_f, dim3(kFwdThreads), fwd_smem, stream, tm_q, tm_kh, tm_vh, tm_kr, tm_vr,
+                    fp) != cudaSuccess)
+    return STAC_ERR_CUDA;
 
   if (a.colsum != nullptr) {
     ColParams cp;
@@ -1607,8 +1664,9 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
     // two CTAs, which add their partial sums onto zeros); else one item per CTA
     cp.split = cp.n_items >= n_sm ? 1 : 0;      // then the forward kernel has cleared a.colsum
     const int grid_c = cp.split ? n_sm : cp.n_items;
-    attn_colsum_kernel<<<grid_c, kColThreads, col_smem, stream>>>(tm_qs, tm_kh, tm_kr, cp);
-    if (cudaGetLastError() != cudaSuccess) return STAC_ERR_CUDA;
+    if (launch_behind(attn_colsum_kernel, dim3(grid_c), dim3(kColThreads), col_smem, stream, tm_qs, tm_kh, tm_kr,
+                      cp) != cudaSuccess)
+      return STAC_ERR_CUDA;
   }
   return STAC_OK;
 }
@@ -1677,3 +1735,14 @@ extern "C" int stac_attn_colsum_noalloc(const void* q, int64_t q_row_stride, con
   // written by the forward pass of this same call, so nothing has to be cleared first.
   return stac::attn_colsum_launch(a, scratch, nullptr, dev_status, reinterpret_cast<cudaStream_t>(stream));
 }
+
+#ifdef STAC_TIMESTAMPS
+extern "C" int stac_debug_stamps(unsigned long long* out, int reset) {
+  if (out != nullptr && cudaMemcpyFromSymbol(out, stac::g_ts, sizeof(unsigned long long) * 8) != cudaSuccess) return 1;
+  if (reset) {
+    const unsigned long long init[8] = {~0ull, 0ull, ~0ull, 0ull, ~0ull, 0ull, ~0ull, 0ull};
+    if (cudaMemcpyToSymbol(stac::g_ts, init, sizeof(init)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif

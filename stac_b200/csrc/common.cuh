@@ -123,6 +123,13 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may become resident while the kernel before it in the stream still runs (once every
+// CTA of that kernel has executed grid_dep_launch or exited); grid_dep_wait then blocks until
+// that kernel has completed and its writes are visible.  Without the attribute both are no-ops.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // True in exactly one lane of a converged warp.  The MMA-issuing warps run their loops with all
 // 32 lanes (so that addresses and descriptors are warp-uniform values) and only the elected lane
 // executes the tcgen05.mma / tcgen05.commit instructions.

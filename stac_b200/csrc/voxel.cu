@@ -17,7 +17,8 @@ namespace stac {
 namespace {
 
 constexpr unsigned long long kEmpty = ~0ull;
-constexpr int kSortCap = STAC_VOXEL_MAX_POINTS;  // new keys per call handled by the single-CTA sort
+constexpr int kSortCap = STAC_VOXEL_MAX_POINTS;  // points (hence new keys) per call
+constexpr int kSortSmemKeys = 16384;              // new keys that the sort holds in shared memory
 
 __device__ __forceinline__ unsigned long long hash64(unsigned long long x) {
   x ^= x >> 33;
@@ -87,19 +88,28 @@ __global__ void quantize_lookup_kernel(const float* __restrict__ pts, const int*
 
 // Single CTA: sort the pending keys, drop duplicates, give the survivors ids n_old + rank in
 // ascending key order, append them to the id -> key table and insert them in the hash table.
+// Up to kSortSmemKeys keys are sorted in shared memory; a call with more new keys than that
+// (chunks of sixteen frames and more, all on unseen ground) sorts them where they lie, in the
+// scratch list, which has room for the padding up to the next power of two.
 __global__ void __launch_bounds__(1024, 1)
-insert_new_kernel(const long long* __restrict__ new_keys, const int* __restrict__ new_cnt,
+insert_new_kernel(long long* new_keys, const int* __restrict__ new_cnt,
                   long long* __restrict__ table_keys, int table_cap, unsigned long long* __restrict__ hk,
                   int* __restrict__ hv, int hcap, int* __restrict__ n_voxels, int* err) {
-  extern __shared__ unsigned long long skeys[];
+  extern __shared__ unsigned long long smem_keys[];
   __shared__ int warp_sums[32];
   __shared__ int carry;
   const int n = *new_cnt;
   if (n == 0) return;
   int np2 = 1;
   while (np2 < n) np2 <<= 1;
-  for (int i = threadIdx.x; i < np2; i += blockDim.x)
-    skeys[i] = i < n ? static_cast<unsigned long long>(new_keys[i]) : kEmpty;
+  unsigned long long* skeys = smem_keys;
+  if (np2 <= kSortSmemKeys) {
+    for (int i = threadIdx.x; i < np2; i += blockDim.x)
+      skeys[i] = i < n ? static_cast<unsigned long long>(new_keys[i]) : kEmpty;
+  } else {
+    skeys = reinterpret_cast<unsigned long long*>(new_keys);
+    for (int i = n + threadIdx.x; i < np2; i += blockDim.x) skeys[i] = kEmpty;
+  }
   __syncthreads();
   for (int k = 2; k <= np2; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
@@ -284,6 +294,11 @@ __global__ void rehash_kernel(const long long* __restrict__ table_keys, const in
 }
 
 bool is_pow2(long long x) { return x > 0 && (x & (x - 1)) == 0; }
+size_t pow2_at_least(int n) {
+  size_t p = 1;
+  while (p < static_cast<size_t>(n)) p <<= 1;
+  return p;
+}
 
 
 // One thread per output token: frame s, token t (the first `special` tokens of a frame are zero
@@ -338,8 +353,9 @@ extern "C" {
 
 size_t stac_voxel_scratch_bytes(int n_points) {
   if (n_points <= 0) return 0;
-  // per-point packed keys + pending key list + pending counter (16-byte padded)
-  return static_cast<size_t>(n_points) * 16 + 16;
+  // per-point packed keys + pending key list (with room for the sort's padding to a power of
+  // two) + pending counter (16-byte padded)
+  return (static_cast<size_t>(n_points) + stac::pow2_at_least(n_points)) * 8 + 16;
 }
 
 int stac_voxel_hash_clear(void* hash_keys, int64_t hash_cap, stac_stream_t stream) {
@@ -381,7 +397,7 @@ int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* ma
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   long long* pt_keys = static_cast<long long*>(scratch);
   long long* new_keys = pt_keys + n_points;
-  int* new_cnt = reinterpret_cast<int*>(new_keys + n_points);
+  int* new_cnt = reinterpret_cast<int*>(new_keys + stac::pow2_at_least(n_points));
   if (cudaMemsetAsync(new_cnt, 0, sizeof(int), st) != cudaSuccess) return STAC_ERR_CUDA;
   const int threads = 256;
   const int blocks = (n_points + threads - 1) / threads;
@@ -392,7 +408,7 @@ int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* ma
   int dev = 0;
   if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
   static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
-  const int smem = stac::kSortCap * 8;
+  const int smem = stac::kSortSmemKeys * 8;
   if (attr_done.needs_setup(dev)) {
     if (cudaFuncSetAttribute(stac::insert_new_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)

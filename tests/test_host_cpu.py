@@ -37,7 +37,7 @@ def test_library_exports_every_declared_symbol():
     lse_bytes = ((1041 * 16 + 256) * 4 + 255) // 256 * 256
     assert lib.stac_attn_workspace_bytes(1041, 16) == lse_bytes + 2 * 160 * (128 * 64 + 2 * 128) * 4
     assert lib.stac_merge_scratch_bytes(4, 100, 1000) > 0
-    assert lib.stac_voxel_scratch_bytes(10) == 176
+    assert lib.stac_voxel_scratch_bytes(10) == (10 + 16) * 8 + 16   # keys, key list padded to 16, counter
 
 
 def test_struct_layout_matches_header():

@@ -64,6 +64,28 @@ def test_upsert_integer_coordinates_entry():
     assert np.array_equal(ids, VoxelTable(0.05).upsert(ijk))
 
 
+def test_upsert_of_a_long_chunk_sorts_its_new_keys_outside_shared_memory():
+    """More new voxels in one call than the in-CTA sort holds (16 384): 40 frames of 1041 points
+    on unseen ground, then a second call that mixes known and new voxels."""
+    t_gpu, st = _table(cap=1 << 10)
+    t_ref = VoxelTable(0.05)
+    rs = np.random.RandomState(11)
+    for step, (n, spread) in enumerate([(40 * 1041, 6.0), (125 * 1041, 7.0), (20000, 7.0)]):
+        pts = rs.uniform(-spread, spread, size=(n, 3)).astype(np.float32)
+        mask = rs.rand(n) > 0.05
+        ids = t_gpu.upsert_points(torch.from_numpy(pts), torch.from_numpy(mask)).cpu().numpy()
+        ref = np.full(n, -1, np.int32)
+        n_before = t_ref.num_voxels
+        ref[mask] = t_ref.upsert(quantize(pts, 0.05)[mask])
+        assert t_ref.num_voxels - n_before > 16384, "the case must exceed the shared-memory sort"
+        assert np.array_equal(ids, ref), step
+        assert t_gpu.get_voxel_num() == t_ref.num_voxels
+    st.raise_if_set("voxel")
+    assert np.array_equal(t_gpu.get_voxel_keys_1d().cpu().numpy(), t_ref.keys)
+    with pytest.raises(ValueError):
+        t_gpu.upsert_points(torch.zeros((131073, 3)))
+
+
 @pytest.mark.parametrize("T,n_recent,n_pinned,k", [(700, 200, 100, 150), (15615, 8328, 1041, 2082),
                                                      (333, 50, 0, 1), (1200, 100, 37, 1063)])
 def test_h2o_select_bit_exact(T, n_recent, n_pinned, k):
