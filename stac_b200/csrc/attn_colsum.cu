@@ -1624,14 +1624,21 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   if (device_sm_count(dev, &n_sm) != STAC_OK) return STAC_ERR_CUDA;
   // fast kernel (fixed per-row reference) first; the exact kernel behind it returns at once
   // unless the fast one raised the flag.  With at least one item per SM (and a workspace for
-  // the parts) the units are cut evenly over one CTA per SM, else every CTA takes one item.
+  // the parts) the units are cut evenly over one CTA per SM; with at most half as many items as
+  // SMs (few heads, e.g. a head-sharded stream) every item is cut in two halves, one CTA each;
+  // else every CTA takes one item.  Either way an item is shared by at most two CTAs.
   fp.n_q_tiles = static_cast<int>(grid_f.x);
   fp.n_items = fp.n_q_tiles * a.H;
   const int n_tiles_f = (a.T_hot + kFT - 1) / kFT + (a.T_ret + kFT - 1) / kFT;
-  fp.split = (part != nullptr && fp.n_items >= n_sm && n_sm <= kFastMaxCtas && n_tiles_f >= kFastMinSplitTiles) ? 1 : 0;
+  int grid_split = 0;
+  if (part != nullptr && n_sm <= kFastMaxCtas && n_tiles_f >= kFastMinSplitTiles) {
+    if (fp.n_items >= n_sm) grid_split = n_sm;
+    else if (2 * fp.n_items <= n_sm && n_tiles_f >= 2 * kFastMinSplitTiles) grid_split = 2 * fp.n_items;
+  }
+  fp.split = grid_split > 0 ? 1 : 0;
   fp.part = part;
   fp.part_count = fp.fallback + 1;      // only used (and only present in the workspace) when split
-  const int grid_fast = fp.split ? n_sm : fp.n_items;
+  const int grid_fast = fp.split ? grid_split : fp.n_items;
   if (cudaMemsetAsync(fp.fallback, 0, sizeof(int) * (fp.split ? 1 + kFastMaxCtas : 1), stream) != cudaSuccess)
     return STAC_ERR_CUDA;
   // the column-sum kernel adds partial sums with atomics when its own units are cut evenly over

@@ -94,6 +94,18 @@ def test_forward_units_split_over_all_sms():
     assert np.array_equal(got[0], again[0]) and np.array_equal(got[1], again[1])   # same bits every run
 
 
+@pytest.mark.parametrize("M,H,T_hot,T_ret,spread", [(700, 2, 2500, 140, 1.0), (4164, 2, 3000, 300, 1.0),
+                                                     (300, 16, 3400, 140, 2.0), (520, 3, 1777, 0, 1.0)])
+def test_forward_items_cut_in_two_halves(M, H, T_hot, T_ret, spread):
+    """Few heads (a head-sharded stream): at most half as many (head, query tile) items as SMs
+    and long key ranges, so every item is computed by two CTAs, half of the key tiles each (an odd
+    tile count in the last case), and joined."""
+    got, ref = _run_two_segment(M, H, T_hot, T_ret, seed=M + H, spread=spread)
+    _assert_close(got, ref)
+    again, _ = _run_two_segment(M, H, T_hot, T_ret, seed=M + H, spread=spread)
+    assert np.array_equal(got[0], again[0]) and np.array_equal(got[1], again[1])   # same bits every run
+
+
 def test_forward_split_with_peaked_scores():
     got, ref = _run_two_segment(1100, 16, 1000, 0, seed=34, spread=2.0)
     _assert_close(got, ref)
