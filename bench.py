@@ -344,6 +344,20 @@ def job_throughput(frames_per_rank, ms, world):
     return frames_per_rank * world / (ms / 1e3)
 
 
+def exp2_bound(achieved_tf, clocks, dev):
+    """Second limit of the attention pair at head_dim 64: one exponential per score in each of the
+    two passes, 16 per clock per SM (measured with a stand-alone loop), i.e. (4+2r)*D = 384 flop
+    per two exponentials.  Reported beside the tensor roofline; not the fraction that is judged."""
+    import torch
+    mhz = (clocks or {}).get("sm_mhz") or (clocks or {}).get("sm_max_mhz")
+    if not mhz or not achieved_tf:
+        return None
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    cap = 16.0 * n_sm * mhz * 1e6 / 2.0 * 6 * CFG["head_dim"] / 1e12
+    return {"tflops": round(cap, 1), "frac": round(achieved_tf / cap, 4), "at_sm_mhz": mhz,
+            "rule": "2*H*M*N exponentials per call at 16 per clock per SM; a share of them runs on the FMA pipes"}
+
+
 def attn_flops(M, N, r=1.0, heads=None):
     return (4.0 + 2.0 * r) * (heads or CFG["heads"]) * M * N * CFG["head_dim"]
 
@@ -495,7 +509,8 @@ def run_ours(args):
                      # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one call at
                      # this shape (M=4164, N=17697), one ncu capture per kernel
                      "traffic": ATTN_TRAFFIC_BYTES_PER_CALL,
-                     "traffic_unit": "bytes per call (fwd 84.7 + 8.8 MB, colsum 45.4 MB; algorithmic 135 MB)"},
+                     "traffic_unit": "bytes per call (fwd 84.7 + 8.8 MB, colsum 45.4 MB; algorithmic 135 MB)",
+                     "exp2_unit_bound": exp2_bound(achieved, clocks, dev)},
         "roofline_memory": roof_mem,
         "stages_ms_per_step": dict({"attention_24_layers": round(sum(att_ms) / K, 3),
                                     "prune_total": round(sum(prune_ms) / K, 3)},

@@ -261,7 +261,7 @@ int stac_merge_insert(const stac_pool* pool, const stac_evicted* ev, void* scrat
 /* VoxelKVMerger.retrieve with retrieve_size > 0 (stac/merger.py:1377-1482): per head the
  * pivots of the queried voxels (ascending ids < voxel_used) by W descending; out_K/out_V
  * [heads][R][head_dim], out_mask u8, out_bias f32 = log(max(C,1e-9)) or -inf, sel i32 scratch
- * [heads][R], out_idx i32 [heads][R][2] = (voxel, slot) or NULL.  R <= 4096. */
+ * [heads][R], out_idx i32 [heads][R][2] = (voxel, slot) or NULL.  R <= 8192. */
 int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_count, int retrieve_size,
                   int* sel, void* out_K, void* out_V, uint8_t* out_mask, float* out_bias, int* out_idx,
                   stac_stream_t stream);

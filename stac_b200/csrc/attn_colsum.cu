@@ -465,16 +465,26 @@ static_assert(kFastWgs == 3 || kFastWgs == 4, "three or four softmax warpgroups"
 // been read out.
 constexpr bool kFastDouble = kFastWgs == 3;
 constexpr int kFastThreads = 128 + 128 * kFastWgs;   // warpgroup 0 control (warps 0, 3 TMA, warps 1-2 MMA issue), then softmax
-constexpr int kFastKStages = 5;
-constexpr int kFastVStages = 5;
-constexpr int kFT = 112;                        // keys per tile
-constexpr int kFastTileBytes = kFT * 128;       // 112 rows x 64 bf16
-constexpr int kFastRing = 4;
+#ifndef STAC_FAST_STAGES
+#define STAC_FAST_STAGES 5
+#endif
+constexpr int kFastKStages = STAC_FAST_STAGES;
+constexpr int kFastVStages = STAC_FAST_STAGES;
+#ifndef STAC_FAST_KEYS
+#define STAC_FAST_KEYS 112
+#endif
+constexpr int kFT = STAC_FAST_KEYS;             // keys per tile: 112 (four score buffers); 80 (five buffers, one scored ahead) measured 2 % slower
+static_assert(kFT % 32 == 16 && kFT <= kBN, "a tile is a number of 32-key chunks and one of 16");
+static_assert(kFT == 112 || !kFastDouble, "the double-buffered path is written for 112-key tiles");
+constexpr int kFastTileBytes = kFT * 128;       // kFT rows x 64 bf16
+constexpr int kFastRing = (512 - kD) / kFT;     // score buffers beside the 64 accumulator columns
 constexpr float kFastRowSumLimit = 1.152921504606846976e18f;  // 2^60
 constexpr int kPartFloats = kBM * kD + 2 * kBM; // one partial result: O[128][64], row sums, row references
 constexpr int kFastMaxCtas = 160;               // partial-result slots are provided for this many CTAs
-constexpr int kFastMinSplitTiles = 8;           // shorter key ranges run one CTA per item
-static_assert(kFastMinSplitTiles >= 2 * kFastWgs && kFastRing <= kFastMinSplitTiles, "segment hand-over rule");
+// shorter key ranges run one CTA per item; every warpgroup has a tile at least kFastRing tiles into a
+// middle segment, i.e. one whose score buffer was last used inside the same segment
+constexpr int kFastMinSplitTiles = kFastRing + kFastWgs;
+static_assert(kFastMinSplitTiles >= 2 * kFastWgs, "segment hand-over rule");
 #ifndef STAC_FAST_PAIR_MASK
 #define STAC_FAST_PAIR_MASK 0x8080u
 #endif
@@ -632,7 +642,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t o_tmem = tmem + kFastRing * kFT;   // columns 448..511
+  const uint32_t o_tmem = tmem + kFastRing * kFT;   // 64 columns behind the score buffers
   // The exact kernel behind this one may be scheduled as soon as an SM has room for it (that is,
   // when this CTA has left); it waits for this grid's completion before it reads the flag.
   grid_dep_launch();
@@ -772,7 +782,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool overflow = false;
     FwdWalk walk(p, n_tiles);
     int seg = 0, item, t0, t1;
-    int c_base = 0;   // key tiles of earlier segments: tile c of the CTA uses ring buffer c % 4, warpgroup c % kFastWgs
+    int c_base = 0;   // key tiles of earlier segments: tile c of the CTA uses ring buffer c % kFastRing, warpgroup c % kFastWgs
     for (; walk.next(item, t0, t1); ++seg) {
       const int h = item / p.n_q_tiles, m_tile = item - h * p.n_q_tiles;
       const int len = t1 - t0;
@@ -785,7 +795,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       bool fetching = false;  // the first 32 scores of the next tile are already on their way into ra
       for (int x = (g + kFastWgs - c_base % kFastWgs) % kFastWgs; x < len; x += kFastWgs) {
         const int c = c_base + x;
-        const int b = c & (kFastRing - 1), round = c >> 2;
+        const int b = c % kFastRing, round = c / kFastRing;
         const int j = t0 + x;
         const bool is_ret = j >= n_hot;
         const int n0 = (is_ret ? j - n_hot : j) * kFT;
@@ -815,11 +825,10 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (fetching) tmem_ld_wait();      // the prefetched scores are not needed
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = 0u;
-          tmem_st16(s_addr, pk);
-          tmem_st16(s_addr + 16, pk);
-          tmem_st16(s_addr + 32, pk);
-          tmem_st8(s_addr + 48, pk);
-          const int b2n = (c + kFastWgs) & (kFastRing - 1), round2n = (c + kFastWgs) >> 2;
+#pragma unroll
+          for (int ch = 0; ch < kFT / 32; ++ch) tmem_st16(s_addr + 16 * ch, pk);
+          tmem_st8(s_addr + (kFT - 16) / 2, pk);
+          const int b2n = (c + kFastWgs) % kFastRing, round2n = (c + kFastWgs) / kFastRing;
           fetching = false;
           if (kFastDouble && x + kFastWgs < len &&
               __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2n], round2n & 1))) {
@@ -837,17 +846,15 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if (x == 0) {
             // exact row maximum of the segment's first tile = the row's reference for the segment
             float mx = -INFINITY;
+#pragma unroll
+            for (int ch = 0; ch < kFT / 32; ++ch) {
+              tmem_ld_wait();
+              mx = fast_max_chunk<32>(ra, bias2 + 32 * ch, need_bias, c2, mx);
+              if (ch + 1 < kFT / 32) tmem_ld32(s_addr + 32 * (ch + 1), ra);
+              else tmem_ld16(s_addr + 32 * (ch + 1), ra);
+            }
             tmem_ld_wait();
-            mx = fast_max_chunk<32>(ra, bias2, need_bias, c2, mx);
-            tmem_ld32(s_addr + 32, ra);
-            tmem_ld_wait();
-            mx = fast_max_chunk<32>(ra, bias2 + 32, need_bias, c2, mx);
-            tmem_ld32(s_addr + 64, ra);
-            tmem_ld_wait();
-            mx = fast_max_chunk<32>(ra, bias2 + 64, need_bias, c2, mx);
-            tmem_ld16(s_addr + 96, ra);
-            tmem_ld_wait();
-            mx = fast_max_chunk<16>(ra, bias2 + 96, need_bias, c2, mx);
+            mx = fast_max_chunk<16>(ra, bias2 + kFT - 16, need_bias, c2, mx);
             m_ref = (mx == -INFINITY) ? 0.f : mx;
             sm.m_ref[sb][row] = m_ref;
             mbar_arrive(&sm.ref_ready[sb]);
@@ -879,7 +886,7 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           // this warpgroup's next tile of the segment is normally scored by now: start fetching it
           // (never wait for it here: its buffer is released by another warpgroup's P V, which may
           // be behind this one)
-          const int b2 = (c + kFastWgs) & (kFastRing - 1), round2 = (c + kFastWgs) >> 2;
+          const int b2 = (c + kFastWgs) % kFastRing, round2 = (c + kFastWgs) / kFastRing;
           const bool more = x + kFastWgs < len;
           fetching = false;
           if (more && __all_sync(0xffffffffu, mbar_test(&sm.s_full[b2], round2 & 1))) {
@@ -897,25 +904,19 @@ attn_fwd_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         } else {
           // one score buffer per thread: load, wait, convert, store, chunk by chunk
+#pragma unroll
+          for (int ch = 0; ch < kFT / 32; ++ch) {
+            tmem_ld_wait();
+            if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 32 * ch, c2c2, negm2, l0, l1);
+            else fast_exp_chunk<false, 32>(ra, pk, bias2 + 32 * ch, c2c2, negm2, l0, l1);
+            if (ch + 1 < kFT / 32) tmem_ld32(s_addr + 32 * (ch + 1), ra);
+            else tmem_ld16(s_addr + 32 * (ch + 1), ra);
+            tmem_st16(s_addr + 16 * ch, pk);
+          }
           tmem_ld_wait();
-          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
-          else fast_exp_chunk<false, 32>(ra, pk, bias2, c2c2, negm2, l0, l1);
-          tmem_ld32(s_addr + 32, ra);
-          tmem_st16(s_addr, pk);
-          tmem_ld_wait();
-          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 32, c2c2, negm2, l0, l1);
-          else fast_exp_chunk<false, 32>(ra, pk, bias2 + 32, c2c2, negm2, l0, l1);
-          tmem_ld32(s_addr + 64, ra);
-          tmem_st16(s_addr + 16, pk);
-          tmem_ld_wait();
-          if (need_bias) fast_exp_chunk<true, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
-          else fast_exp_chunk<false, 32>(ra, pk, bias2 + 64, c2c2, negm2, l0, l1);
-          tmem_ld16(s_addr + 96, ra);
-          tmem_st16(s_addr + 32, pk);
-          tmem_ld_wait();
-          if (need_bias) fast_exp_chunk<true, 16>(ra, pk, bias2 + 96, c2c2, negm2, l0, l1);
-          else fast_exp_chunk<false, 16>(ra, pk, bias2 + 96, c2c2, negm2, l0, l1);
-          tmem_st8(s_addr + 48, pk);
+          if (need_bias) fast_exp_chunk<true, 16>(ra, pk, bias2 + kFT - 16, c2c2, negm2, l0, l1);
+          else fast_exp_chunk<false, 16>(ra, pk, bias2 + kFT - 16, c2c2, negm2, l0, l1);
+          tmem_st8(s_addr + (kFT - 16) / 2, pk);
           fetching = false;
         }
         tmem_st_wait();

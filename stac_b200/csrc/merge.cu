@@ -171,7 +171,7 @@ __device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
 }
 
 // ------------------------------------------------------------------------------------ sort
-__global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(1024, 2) sort_tokens_kernel(const MergeParams p) {
   __shared__ int hist[256 * 32];  // [digit][warp]
   __shared__ int warp_sums[32];
   __shared__ int sh_total;
@@ -186,18 +186,30 @@ __global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams 
   // 1. valid evicted tokens in position order
   if (threadIdx.x == 0) sh_carry = 0;
   __syncthreads();
-  for (int base = 0; base < p.n_new; base += 1024) {
-    const int j = base + threadIdx.x;
-    int vx = -1;
-    if (j < p.n_new) {
-      const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + j] : j;
-      vx = p.vx_src[h * p.meta_head_stride + pos];
+  // four consecutive positions per thread: one block scan per 4096 tokens, loads issued together
+  for (int base = 0; base < p.n_new; base += 4096) {
+    const int j0 = base + threadIdx.x * 4;
+    int vxs[4];
+    int sum = 0;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int j = j0 + t;
+      int vx = -1;
+      if (j < p.n_new) {
+        const int pos = p.idx ? p.idx[static_cast<long long>(h) * p.n_new + j] : j;
+        vx = p.vx_src[h * p.meta_head_stride + pos];
+      }
+      vxs[t] = (vx >= 0 && vx < p.voxel_used) ? vx : -1;
+      sum += vxs[t] >= 0 ? 1 : 0;
     }
-    const int ok = (vx >= 0 && vx < p.voxel_used) ? 1 : 0;
-    const int off = sh_carry + block_scan(ok, warp_sums, &sh_total);
-    if (ok) {
-      ka[off] = static_cast<unsigned int>(vx);
-      va[off] = j;
+    int off = sh_carry + block_scan(sum, warp_sums, &sh_total);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      if (vxs[t] >= 0) {
+        ka[off] = static_cast<unsigned int>(vxs[t]);
+        va[off] = j0 + t;
+        ++off;
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) sh_carry += sh_total;
@@ -226,17 +238,46 @@ __global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams 
   const int c0 = warp * chunk;
   const int c1 = min(n, c0 + chunk);
   unsigned int* kin = ka; int* vin = va; unsigned int* kout = kb; int* vout = vb;
+  // A warp's chunk is read into registers once per pass when it is at most kRegIt * 32 items
+  // (lists of up to 8192 tokens): one round trip to L2 per pass instead of one per 32 items in
+  // each of the two loops.
+  constexpr int kRegIt = 8;
+  const bool in_regs = chunk <= 32 * kRegIt;
   for (int pass = 0; pass < p.passes; ++pass) {
     const int shift = pass * 8;
     for (int i = threadIdx.x; i < 256 * 32; i += 1024) hist[i] = 0;
+    unsigned int kreg[kRegIt];
+    int vreg[kRegIt];
+    if (in_regs) {
+#pragma unroll
+      for (int t = 0; t < kRegIt; ++t) {
+        const int i = c0 + t * 32 + lane;
+        kreg[t] = i < c1 ? kin[i] : 0u;
+        vreg[t] = i < c1 ? vin[i] : 0;
+      }
+    }
     __syncthreads();
-    for (int base = c0; base < c1; base += 32) {
-      const int i = base + lane;
-      const bool in = i < c1;
-      const unsigned int d = in ? ((kin[i] >> shift) & 255u) : (256u + lane);
-      const unsigned int peers = __match_any_sync(kFull, d);
-      if (in && (peers & ((1u << lane) - 1)) == 0) hist[d * 32 + warp] += __popc(peers);
-      __syncwarp();
+    if (in_regs) {
+#pragma unroll
+      for (int t = 0; t < kRegIt; ++t) {
+        const int base = c0 + t * 32;
+        if (base < c1) {                                   // warp-uniform
+          const bool in = base + lane < c1;
+          const unsigned int d = in ? ((kreg[t] >> shift) & 255u) : (256u + lane);
+          const unsigned int peers = __match_any_sync(kFull, d);
+          if (in && (peers & ((1u << lane) - 1)) == 0) hist[d * 32 + warp] += __popc(peers);
+          __syncwarp();
+        }
+      }
+    } else {
+      for (int base = c0; base < c1; base += 32) {
+        const int i = base + lane;
+        const bool in = i < c1;
+        const unsigned int d = in ? ((kin[i] >> shift) & 255u) : (256u + lane);
+        const unsigned int peers = __match_any_sync(kFull, d);
+        if (in && (peers & ((1u << lane) - 1)) == 0) hist[d * 32 + warp] += __popc(peers);
+        __syncwarp();
+      }
     }
     __syncthreads();
     // exclusive scan of hist in (digit, warp) order: 8 consecutive entries per thread
@@ -254,15 +295,7 @@ __global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams 
       run += loc[e];
     }
     __syncthreads();
-    for (int base = c0; base < c1; base += 32) {
-      const int i = base + lane;
-      const bool in = i < c1;
-      unsigned int key = 0;
-      int val = 0;
-      if (in) {
-        key = kin[i];
-        val = vin[i];
-      }
+    auto scatter = [&](bool in, unsigned int key, int val) {
       const unsigned int d = in ? ((key >> shift) & 255u) : (256u + lane);
       const unsigned int peers = __match_any_sync(kFull, d);
       const unsigned int before = peers & ((1u << lane) - 1);
@@ -274,6 +307,19 @@ __global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams 
       __syncwarp();
       if (in && before == 0) hist[d * 32 + warp] += __popc(peers);
       __syncwarp();
+    };
+    if (in_regs) {
+#pragma unroll
+      for (int t = 0; t < kRegIt; ++t) {
+        const int base = c0 + t * 32;
+        if (base < c1) scatter(base + lane < c1, kreg[t], vreg[t]);
+      }
+    } else {
+      for (int base = c0; base < c1; base += 32) {
+        const int i = base + lane;
+        const bool in = i < c1;
+        scatter(in, in ? kin[i] : 0u, in ? vin[i] : 0);
+      }
     }
     __syncthreads();
     unsigned int* tk = kin; kin = kout; kout = tk;
@@ -284,20 +330,33 @@ __global__ void __launch_bounds__(1024, 1) sort_tokens_kernel(const MergeParams 
   __syncthreads();
   int* rvx = p.row_vx + static_cast<long long>(h) * p.ncap;
   int* rst = p.row_start + static_cast<long long>(h) * (p.ncap + 1);
-  for (int base = 0; base < n; base += 1024) {
-    const int i = base + threadIdx.x;
-    int head_flag = 0;
-    unsigned int key = 0;
-    if (i < n) {
-      key = kin[i];
-      head_flag = (i == 0 || kin[i - 1] != key) ? 1 : 0;
+  for (int base = 0; base < n; base += 4096) {
+    const int i0 = base + threadIdx.x * 4;
+    unsigned int key[4];
+    int hf[4];
+    int sum = 0;
+    const unsigned int prev = (i0 > 0 && i0 - 1 < n) ? kin[i0 - 1] : 0u;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int i = i0 + t;
+      key[t] = i < n ? kin[i] : 0u;
+      hf[t] = 0;
+      if (i < n) hf[t] = (i == 0 || key[t] != (t == 0 ? prev : key[t - 1])) ? 1 : 0;
+      sum += hf[t];
     }
-    const int r = sh_carry + block_scan(head_flag, warp_sums, &sh_total);
-    if (head_flag) {
-      rvx[r] = static_cast<int>(key);
-      rst[r] = i;
+    int r = sh_carry + block_scan(sum, warp_sums, &sh_total);    // rows that begin before this thread's tokens
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int i = i0 + t;
+      if (i < n) {
+        if (hf[t]) {
+          rvx[r] = static_cast<int>(key[t]);
+          rst[r] = i;
+        }
+        p.tok_row[static_cast<long long>(h) * p.ncap + i] = r + hf[t] - 1;
+        r += hf[t];
+      }
     }
-    if (i < n) p.tok_row[static_cast<long long>(h) * p.ncap + i] = r + head_flag - 1;
     __syncthreads();
     if (threadIdx.x == 0) sh_carry += sh_total;
     __syncthreads();
@@ -417,7 +476,10 @@ __global__ void __launch_bounds__(256) tokens_sim_kernel(const MergeParams p) {
   const long long hb = static_cast<long long>(h) * p.ncap;
   const int code = (((p.passes & 1) ? p.vals_b : p.vals_a) + hb)[i];
   const int ri = p.tok_row[hb + i];
-  const int vx = p.row_vx[hb + ri];
+  // the sorted key is the voxel id: no token -> row -> voxel hops before the row's pivots are known.
+  // (Requesting the pivot segments and keys ahead of the pivot count, all four at once, measured
+  // 10 % slower for the whole merge: more registers and loads for rows that hold no pivot.)
+  const int vx = static_cast<int>((((p.passes & 1) ? p.keys_b : p.keys_a) + hb)[i]);
   const long long r = static_cast<long long>(h) * p.voxel_cap + vx;
   const int npiv = p.piv_row_cnt[r];
   if (sub == 0) p.tok_score[hb + i] = token_score(p, h, code);
@@ -975,11 +1037,12 @@ __global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p) 
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
   if (i >= p.n_tok[h]) return;
   const long long hb = static_cast<long long>(h) * p.ncap;
+  // independent loads first (the sorted key is the voxel id), then the branch
   const int d = p.tok_dest[hb + i];
-  if (d < 0) return;
   const int ri = p.tok_row[hb + i];
   const int code = (((p.passes & 1) ? p.vals_b : p.vals_a) + hb)[i];
-  const int vx = p.row_vx[hb + ri];
+  const int vx = static_cast<int>((((p.passes & 1) ? p.keys_b : p.keys_a) + hb)[i]);
+  if (d < 0) return;
   const uint4* src_k = reinterpret_cast<const uint4*>(token_row_ptr<T>(p, h, code, false)) + sub * kVec;
   const uint4* src_v = reinterpret_cast<const uint4*>(token_row_ptr<T>(p, h, code, true)) + sub * kVec;
   uint4 kv[kVec], vv[kVec];

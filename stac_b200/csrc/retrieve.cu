@@ -321,7 +321,7 @@ int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_
   if (pool == nullptr || query_ids == nullptr || query_count == nullptr || sel == nullptr || out_K == nullptr ||
       out_V == nullptr || out_mask == nullptr || out_bias == nullptr)
     return STAC_ERR_BAD_ARG;
-  if (retrieve_size <= 0 || retrieve_size > 4096 || pool->pivot_cap > 4) return STAC_ERR_BAD_ARG;
+  if (retrieve_size <= 0 || retrieve_size > stac::kSelCap || pool->pivot_cap > 4) return STAC_ERR_BAD_ARG;
   const int token_bytes = pool->head_dim * pool->elem_bytes;
   if (token_bytes % 16 != 0) return STAC_ERR_BAD_ARG;
   stac::RetrieveParams rp;

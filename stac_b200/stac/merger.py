@@ -344,8 +344,8 @@ class VoxelKVMerger:
         """query_ids int32 ascending (device), query_count int32 [1] (device).  Returns
         K, V [H,R,D], mask bool [H,R], bias fp32 [H,R] (and idx int32 [H,R,2])."""
         R = int(retrieve_size)
-        if not (0 < R <= 4096):
-            raise ValueError("retrieve_size must be in 1..4096")
+        if not (0 < R <= 8192):
+            raise ValueError("retrieve_size must be in 1..8192")
         dev = self.device
         K = torch.empty((self.H, R, self.D), dtype=self.dtype, device=dev)
         V = torch.empty((self.H, R, self.D), dtype=self.dtype, device=dev)

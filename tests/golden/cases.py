@@ -42,6 +42,8 @@ MERGER_GPU = {
     "gpu_bf16": dict(_M, H=4, D=64, N=1536, steps=10, init_voxels=32, dtype="bf16", seed=52, n_sites=96),
     "gpu_wide": dict(_M, H=6, D=64, N=4000, steps=4, init_voxels=4096, dtype="bf16", seed=53, n_sites=2500),
     "gpu_crowded": dict(_M, H=2, D=64, N=3000, steps=5, init_voxels=8, dtype="f32", seed=54, n_sites=3),
+    # more than 8192 tokens per pool head and call: the per-head sort leaves its register path
+    "gpu_long": dict(_M, H=2, D=64, N=9100, steps=3, init_voxels=1024, dtype="bf16", seed=55, n_sites=1500),
 }
 
 

@@ -174,6 +174,28 @@ def _compare_pool(snap, m, tag, rtol, atol):
     np.testing.assert_allclose(snap["over_S"], oS, rtol=rtol, atol=atol)
 
 
+def _same_order_up_to_near_ties(idx_gpu, idx_ref, oracle, tag):
+    """The retrieved (voxel, slot) order must be the oracle's.  The order is by pivot weight, and
+    the weights themselves agree only to rounding (sums of exp() evaluated by different libraries),
+    so two pivots whose weights differ in the last bits may change places: allowed only when the
+    oracle's weights of the two entries agree to 4e-6 relative and both lists hold the same
+    entries.  Returns the [H, R] mask of positions where the lists agree."""
+    same = (idx_gpu == idx_ref).all(-1)
+    if same.all():
+        return same
+
+    def weight(h, v, p):
+        return float(oracle.piv.data["W"][int(oracle.piv.row_seg[h, v, p])])
+    for h, i in zip(*np.nonzero(~same)):
+        (vg, pg), (vo, po) = idx_gpu[h, i], idx_ref[h, i]
+        assert vg >= 0 and vo >= 0, (tag, h, i)
+        wg, wo = weight(h, vg, pg), weight(h, vo, po)
+        assert abs(wg - wo) <= 4e-6 * abs(wo), (tag, h, i, wg, wo)
+    for h in range(idx_gpu.shape[0]):
+        assert sorted(map(tuple, idx_gpu[h].tolist())) == sorted(map(tuple, idx_ref[h].tolist())), (tag, h)
+    return same
+
+
 @pytest.mark.parametrize("name", list(cases.MERGER_GPU) + ["f32_d64"])
 def test_merge_and_retrieve_match_oracle(name):
     from stac_b200 import ops
@@ -205,17 +227,18 @@ def test_merge_and_retrieve_match_oracle(name):
     assert info["buffer_pool_used"] == m.buf.used() and info["pivot_pool_used"] == m.piv.used()
     # retrieval: order of (voxel, slot) must be identical
     rs = np.random.RandomState(5)
-    for R in (16, 200, 1000):
-        q = rs.randint(0, t.num_voxels, size=min(t.num_voxels, 300)).astype(np.int64)
+    for R in (16, 200, 1000, 6000):
+        nq = t.num_voxels if R == 6000 else min(t.num_voxels, 300)     # the widest block queries every voxel
+        q = rs.randint(0, t.num_voxels, size=nq).astype(np.int64)
         Kg, Vg, Mg, Bg, Ig = g.retrieve(torch.from_numpy(q).to(DEV), True, R, want_idx=True)
         Ko, Vo, Mo, Bo, Io = m.retrieve(q, R, True)
         assert np.array_equal(Mg.cpu().numpy(), Mo), (name, R)
-        assert np.array_equal(Ig.cpu().numpy(), Io), (name, R)
-        np.testing.assert_allclose(Kg.float().cpu().numpy(), Ko, rtol=rtol, atol=atol)
-        np.testing.assert_allclose(Vg.float().cpu().numpy(), Vo, rtol=rtol, atol=atol)
+        same = _same_order_up_to_near_ties(Ig.cpu().numpy(), Io, m, (name, R))
+        np.testing.assert_allclose(Kg.float().cpu().numpy()[same], Ko[same], rtol=rtol, atol=atol)
+        np.testing.assert_allclose(Vg.float().cpu().numpy()[same], Vo[same], rtol=rtol, atol=atol)
         fin = np.isfinite(Bo)
         assert np.array_equal(np.isfinite(Bg.cpu().numpy()), fin)
-        np.testing.assert_allclose(Bg.cpu().numpy()[fin], Bo[fin], rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(Bg.cpu().numpy()[fin & same], Bo[fin & same], rtol=1e-5, atol=1e-6)
     # unbounded mode (retrieve_size <= 0): width = #voxels * P, optionally followed by buffer tokens
     q = rs.randint(0, t.num_voxels, size=min(t.num_voxels, 40)).astype(np.int64)
     for rb in (False, True):
