@@ -1088,6 +1088,7 @@ struct ColSmem {
   uint64_t s_free[2];
   uint64_t x_full[kColStages];            // the row-term operand of a query stage is written
   uint32_t tmem_base;
+  int join_flag;                          // arrival count seen at a shared item
   alignas(16) uint8_t ax[kColXBytes];     // ones in K columns 0..2, same for every key
   alignas(16) uint8_t bx[kColStages][kColXBytes];   // per query row: -lse2 / c2 as hi, mid, lo bf16
   alignas(16) float lse2[4];  // (without the fold) flexible: n_q_tiles * 128 floats follow (negated, one head)
@@ -1109,6 +1110,13 @@ struct ColParams {
   long long lse2_stride;
   float* colsum;  // [H, colsum_stride], hot keys first then retrieved
   long long colsum_stride;
+  // Fewer items than CTAs: an item may be shared by three or more CTAs.  Each writes its partial
+  // sums to a slot of its own (two per CTA: [0] an item that began in an earlier CTA, [1] an
+  // item that goes on in the next one), counts its arrival at the item, and the CTA that arrives
+  // last adds the parts in CTA order and stores the result: same bits whoever does it.  nullptr:
+  // an item has at most two parts, added onto the zeroed output with one atomic each.
+  float* parts;       // [2 * gridDim.x][kColGroup * kBN]
+  int* part_count;    // [n_items], zero on entry, left zero
   int* err;
 };
 
@@ -1439,9 +1447,35 @@ attn_colsum_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         sum *= p.correction;
         if (b2_small) sum *= exp2f(b2);
         if (masked) sum = 0.f;
-        float* dst = p.colsum + static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key;
-        if (i0 == 0 && i1 == nq) *dst = sum;
-        else atomicAdd(dst, sum);
+      }
+      float* dst = p.colsum + static_cast<long long>(h) * p.colsum_stride + (is_ret ? p.T_hot : 0) + n0 + key;
+      if (i0 == 0 && i1 == nq) {
+        if (key < valid) *dst = sum;
+      } else if (p.parts == nullptr) {
+        if (key < valid) atomicAdd(dst, sum);
+      } else {
+        constexpr int kSlot = kColGroup * kBN;
+        float* slot = p.parts + static_cast<size_t>(2 * blockIdx.x + (i0 > 0 ? 0 : 1)) * kSlot;
+        slot[w * kBN + key] = key < valid ? sum : 0.f;
+        __threadfence();                          // this thread's part is visible device-wide ...
+        named_bar_sync(1, kColExpThreads);        // ... and so is every other key's
+        if (tid == 0) sm.join_flag = atomicAdd(p.part_count + item, 1);
+        named_bar_sync(1, kColExpThreads);
+        // CTA c owns the units [total * c / G, total * (c + 1) / G): owner(u) = ((u + 1) * G - 1) / total
+        const long long total = static_cast<long long>(p.n_items) * nq, G = gridDim.x;
+        const int c_first = static_cast<int>(((static_cast<long long>(item) * nq + 1) * G - 1) / total);
+        const int c_last = static_cast<int>(((static_cast<long long>(item + 1) * nq) * G - 1) / total);
+        if (sm.join_flag == c_last - c_first) {
+          // every other part was complete before its counter increment, which came earlier
+          __threadfence();
+          if (key < valid) {
+            float acc = 0.f;
+            for (int c = c_first; c <= c_last; ++c)
+              acc = __fadd_rn(acc, __ldcg(p.parts + static_cast<size_t>(2 * c + (c == c_first ? 1 : 0)) * kSlot + w * kBN + key));
+            *dst = acc;
+          }
+          if (tid == 0) p.part_count[item] = 0;
+        }
       }
     }
   }
@@ -1512,10 +1546,13 @@ void attn_subsample_plan(int M, float ratio, int* m_sub, int* stride, float* cor
 // row log-sum-exps [H, M] followed by the fallback flag (64 floats of padding keep it aligned)
 // fallback flag and the arrival counters of the split forward kernel follow the [H, M] values
 size_t attn_lse2_elems(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 64; }
-size_t attn_lse2_elems_split(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 256; }
+size_t attn_lse2_elems_split(int M, int H) { return static_cast<size_t>(H) * static_cast<size_t>(M) + 512; }
 
-// partial results of the split forward kernel: two slots per CTA
-size_t attn_part_elems() { return static_cast<size_t>(2) * kFastMaxCtas * kPartFloats; }
+// partial results of the split forward kernel (two slots per CTA), then the partial column sums of
+// a column-sum launch with fewer items than CTAs (two slots per CTA)
+constexpr size_t kFwdPartElems = static_cast<size_t>(2) * kFastMaxCtas * kPartFloats;
+constexpr size_t kColPartElems = static_cast<size_t>(2) * kFastMaxCtas * kColGroup * kBN;
+size_t attn_part_elems() { return kFwdPartElems + kColPartElems; }
 
 // Launch with programmatic stream serialization: the kernel may become resident while the
 // kernel before it in the stream drains; it calls grid_dep_wait() before it touches anything
@@ -1640,12 +1677,21 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
   fp.part = part;
   fp.part_count = fp.fallback + 1;      // only used (and only present in the workspace) when split
   const int grid_fast = fp.split ? grid_split : fp.n_items;
-  if (cudaMemsetAsync(fp.fallback, 0, sizeof(int) * (fp.split ? 1 + kFastMaxCtas : 1), stream) != cudaSuccess)
+  // Column sums: with at least one item per SM the units are cut evenly over one CTA per SM and an
+  // item on a cut gets one atomic add per key from each of its two CTAs (the forward kernel clears
+  // the output for that).  With fewer items (few heads, short key ranges) and a workspace, the
+  // units are still cut evenly; an item may then have three or more parts, which go through the
+  // workspace and are added in CTA order by the CTA that finishes last.
+  const int col_items = ((fp.n_hot_tiles + fp.n_ret_tiles + kColGroup - 1) / kColGroup) * a.H;
+  const bool col_split = a.colsum != nullptr && col_items >= n_sm;
+  // (worth it from about six units per CTA: below that the extra key-tile loads and the join of a
+  // CTA that touches two items cost more than the even cut gains; measured at M = 1041, N = 2082)
+  const bool col_parts = a.colsum != nullptr && !col_split && part != nullptr && n_sm <= kFastMaxCtas &&
+                         static_cast<long long>(col_items) * ((m_sub + kBM - 1) / kBM) >= 6ll * n_sm;
+  // flag, arrival counters of the forward cuts, arrival counters of the shared column-sum items
+  if (cudaMemsetAsync(fp.fallback, 0, sizeof(int) * (col_parts ? 1 + 2 * kFastMaxCtas : fp.split ? 1 + kFastMaxCtas : 1),
+                      stream) != cudaSuccess)
     return STAC_ERR_CUDA;
-  // the column-sum kernel adds partial sums with atomics when its own units are cut evenly over
-  // the SMs (same rule as below): the forward kernel clears the output for it
-  const bool col_split = a.colsum != nullptr &&
-                         ((fp.n_hot_tiles + fp.n_ret_tiles + kColGroup - 1) / kColGroup) * a.H >= n_sm;
   fp.zero_colsum = col_split ? a.colsum : nullptr;
   fp.zero_stride = a.colsum_head_stride;
   fp.zero_width = a.T_hot + a.T_ret;
@@ -1670,7 +1716,9 @@ int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cu
     cp.err = err;
     // enough items: cut the units evenly over one CTA per SM (an item is then shared by at most
     // two CTAs, which add their partial sums onto zeros); else one item per CTA
-    cp.split = cp.n_items >= n_sm ? 1 : 0;      // then the forward kernel has cleared a.colsum
+    cp.split = (col_split || col_parts) ? 1 : 0;      // col_split: the forward kernel has cleared a.colsum
+    cp.parts = col_parts ? part + kFwdPartElems : nullptr;
+    cp.part_count = fp.fallback + 1 + kFastMaxCtas;
     const int grid_c = cp.split ? n_sm : cp.n_items;
     if (launch_behind(attn_colsum_kernel, dim3(grid_c), dim3(kColThreads), col_smem, stream, tm_qs, tm_kh, tm_kr,
                       cp) != cudaSuccess)

@@ -104,6 +104,21 @@ def test_forward_items_cut_in_two_halves(M, H, T_hot, T_ret, spread):
     _assert_close(got, ref)
     again, _ = _run_two_segment(M, H, T_hot, T_ret, seed=M + H, spread=spread)
     assert np.array_equal(got[0], again[0]) and np.array_equal(got[1], again[1])   # same bits every run
+    assert np.array_equal(got[2], again[2])
+
+
+@pytest.mark.parametrize("M,H,T_hot,T_ret", [(2600, 3, 6000, 0), (4164, 2, 5000, 300), (900, 5, 1500, 260),
+                                             (1300, 1, 700, 0)])
+def test_column_sums_of_items_shared_by_several_ctas(M, H, T_hot, T_ret):
+    """Fewer (head, key group) items than SMs but six and more units per SM (the first two shapes):
+    the column-sum units are still cut evenly over the SMs, an item is then shared by three and
+    more CTAs whose partial sums meet in the workspace and are added in a fixed order (same bits
+    every run).  The last two shapes stay below that and run one item per CTA."""
+    got, ref = _run_two_segment(M, H, T_hot, T_ret, seed=3 * M + H)
+    _assert_close(got, ref)
+    for _ in range(2):
+        again, _ref = _run_two_segment(M, H, T_hot, T_ret, seed=3 * M + H)
+        assert np.array_equal(got[2], again[2])
 
 
 def test_forward_split_with_peaked_scores():

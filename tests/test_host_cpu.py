@@ -33,9 +33,10 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.lib()
     assert lib.stac_abi_version() == 2
     assert lib.stac_status_string(1) == b"bad argument"
-    # row log-sum-exps (+ 256 words of flags and counters, rounded up to 256 bytes) + two partial results per CTA
-    lse_bytes = ((1041 * 16 + 256) * 4 + 255) // 256 * 256
-    assert lib.stac_attn_workspace_bytes(1041, 16) == lse_bytes + 2 * 160 * (128 * 64 + 2 * 128) * 4
+    # row log-sum-exps (+ 512 words of flags and counters, rounded up to 256 bytes) + two partial forward
+    # results and two partial column-sum groups (3 x 128 keys) per CTA
+    lse_bytes = ((1041 * 16 + 512) * 4 + 255) // 256 * 256
+    assert lib.stac_attn_workspace_bytes(1041, 16) == lse_bytes + 2 * 160 * (128 * 64 + 2 * 128 + 3 * 128) * 4
     assert lib.stac_merge_scratch_bytes(4, 100, 1000) > 0
     assert lib.stac_voxel_scratch_bytes(10) == (10 + 16) * 8 + 16   # keys, key list padded to 16, counter
 
