@@ -1554,28 +1554,6 @@ constexpr size_t kFwdPartElems = static_cast<size_t>(2) * kFastMaxCtas * kPartFl
 constexpr size_t kColPartElems = static_cast<size_t>(2) * kFastMaxCtas * kColGroup * kBN;
 size_t attn_part_elems() { return kFwdPartElems + kColPartElems; }
 
-// Launch with programmatic stream serialization: the kernel may become resident while the
-// kernel before it in the stream drains; it calls grid_dep_wait() before it touches anything
-// that kernel wrote.  STAC_PDL=0 builds fall back to plain stream order.
-#ifndef STAC_PDL
-#define STAC_PDL 1
-#endif
-template <typename... KArgs, typename... Args>
-cudaError_t launch_behind(void (*kernel)(KArgs...), dim3 grid, dim3 block, int smem, cudaStream_t stream,
-                          const Args&... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = STAC_PDL;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
 int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cudaStream_t stream) {
   if (a.D != kD) return STAC_ERR_BAD_ARG;
   if (a.M <= 0 || a.H <= 0 || a.T_hot < 0 || a.T_ret < 0 || a.T_hot + a.T_ret <= 0) return STAC_ERR_BAD_ARG;

@@ -15,6 +15,7 @@ namespace {
 __global__ void scores_update_kernel(const float* __restrict__ colsum, long long colsum_stride,
                                      float* __restrict__ scores, float* __restrict__ counts, long long row_stride,
                                      int H, int T_live, int old_T, float t_live_f, float tq_f, float temperature) {
+  grid_dep_wait();   // launched with programmatic serialization behind the column-sum kernel
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int h = blockIdx.y;
   if (t >= T_live) return;
@@ -188,6 +189,7 @@ __global__ void append_kv_kernel(const uint4* __restrict__ k, const uint4* __res
                                  long long cache_head_stride_vec, long long* __restrict__ token_idx,
                                  long long idx_head_stride, int T_new, int old_T, long long first_id,
                                  int vec_per_token) {
+  grid_dep_wait();   // launched with programmatic serialization: whatever produced k and v is complete now
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int h = blockIdx.y;
   const long long t = gid / vec_per_token;
@@ -214,6 +216,7 @@ __global__ void __launch_bounds__(256) qkv_epilogue_kernel(
     int n_pos, __nv_bfloat16* __restrict__ q_out, long long q_row_stride, __nv_bfloat16* __restrict__ k_cache,
     __nv_bfloat16* __restrict__ v_cache, long long cache_head_stride, long long* __restrict__ token_idx,
     long long idx_head_stride, int T_new, int old_T, long long first_id) {
+  grid_dep_wait();   // launched with programmatic serialization: the projection that wrote qkv is complete now
   const int lane = threadIdx.x & 31;
   const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (w >= static_cast<long long>(T_new) * H) return;
@@ -285,12 +288,13 @@ int stac_qkv_epilogue_append(const void* qkv, int64_t qkv_token_stride, const fl
   if (T_new == 0) return STAC_OK;
   const long long warps = static_cast<long long>(T_new) * H;
   const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
-  stac::qkv_epilogue_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  if (stac::launch_behind(stac::qkv_epilogue_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(qkv), qkv_token_stride, H, q_norm_w, q_norm_b, k_norm_w, k_norm_b, eps,
       reinterpret_cast<const long long*>(pos), cos_table, sin_table, n_pos, static_cast<__nv_bfloat16*>(q_out),
       q_out_row_stride, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), cache_head_stride,
-      reinterpret_cast<long long*>(token_idx), idx_head_stride, T_new, old_T, first_token_id);
-  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+      reinterpret_cast<long long*>(token_idx), idx_head_stride, T_new, old_T, first_token_id) != cudaSuccess)
+    return STAC_ERR_CUDA;
+  return STAC_OK;
 }
 
 int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
@@ -313,12 +317,13 @@ int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t 
   const int vpt = token_bytes / 16;
   const long long total = static_cast<long long>(T_new) * vpt;
   dim3 grid(static_cast<unsigned>((total + 255) / 256), H);
-  stac::append_kv_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  if (stac::launch_behind(stac::append_kv_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       static_cast<const uint4*>(k), static_cast<const uint4*>(v), k_head_stride / epv, k_row_stride / epv,
       v_head_stride / epv, v_row_stride / epv, static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
       cache_head_stride / epv, reinterpret_cast<long long*>(token_idx), idx_head_stride, T_new, old_T, first_token_id,
-      vpt);
-  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+      vpt) != cudaSuccess)
+    return STAC_ERR_CUDA;
+  return STAC_OK;
 }
 
 int stac_scores_update(const float* colsum, int64_t colsum_head_stride, float* scores, float* counts,
@@ -328,10 +333,11 @@ int stac_scores_update(const float* colsum, int64_t colsum_head_stride, float* s
     return STAC_ERR_BAD_ARG;
   if (T_live == 0) return STAC_OK;
   dim3 grid((T_live + 255) / 256, H);
-  stac::scores_update_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      colsum, colsum_head_stride, scores, counts, row_stride, H, T_live, old_T, static_cast<float>(T_live),
-      static_cast<float>(Tq), temperature);
-  return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
+  if (stac::launch_behind(stac::scores_update_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                          colsum, colsum_head_stride, scores, counts, row_stride, H, T_live, old_T,
+                          static_cast<float>(T_live), static_cast<float>(Tq), temperature) != cudaSuccess)
+    return STAC_ERR_CUDA;
+  return STAC_OK;
 }
 
 int stac_h2o_select(const float* scores, int64_t row_stride, int n_rows, const uint8_t* is_base, int T, int n_keep,

@@ -1083,6 +1083,8 @@ __global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p) 
 // the weighted mean; the second read hits the cache) so that few registers are live and many
 // rows are in flight per SM.
 template <typename T>
+// (holding all eight key rows of a row in registers, at four CTAs per SM, measured 15 % slower for
+// the whole merge than streaming them at eight CTAs per SM: these per-row kernels want threads)
 __global__ void __launch_bounds__(128, 8) rows_phase_b2_kernel(const MergeParams p) {
   const int lane = threadIdx.x & 31, sub = threadIdx.x & 7;
   const int gbase = lane & 24;                       // first lane of this group

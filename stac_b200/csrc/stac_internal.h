@@ -46,4 +46,26 @@ size_t attn_part_elems();
 // `part`: attn_part_elems() floats for the split forward kernel, or nullptr (one CTA per item then)
 int attn_colsum_launch(const AttnArgs& a, float* lse2, float* part, int* err, cudaStream_t stream);
 
+// Launch with programmatic stream serialization: the kernel may become resident while the
+// kernel before it in the stream drains; it calls grid_dep_wait() before it touches anything
+// that kernel wrote.  STAC_PDL=0 builds fall back to plain stream order.
+#ifndef STAC_PDL
+#define STAC_PDL 1
+#endif
+template <typename... KArgs, typename... Args>
+cudaError_t launch_behind(void (*kernel)(KArgs...), dim3 grid, dim3 block, int smem, cudaStream_t stream,
+                          const Args&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = STAC_PDL;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 }  // namespace stac
