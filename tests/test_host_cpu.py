@@ -89,6 +89,25 @@ def test_bench_helpers():
     assert bench.job_throughput(32, 1000.0, 8) == 256.0
 
 
+def test_cpu_arms_of_the_bench_step(monkeypatch):
+    """The two CPU legs of bench.py (`cpu_baseline`, `--impl reference`): one chunk of one layer and
+    one head through the numpy port and, where its sources are staged, through the reference's
+    own manager; the record says what was measured and how it is scaled."""
+    sys.path.insert(0, ROOT)
+    import bench
+    monkeypatch.setattr(bench, "CPU_SAMPLE", (1, 1))
+    arms = [bench.PortCpuStream(1, 1)]
+    if bench._reference_available():
+        arms.append(bench.ReferenceCpuStream(1, 1))
+    for st in arms:
+        dt = st.step() + st.step()
+        assert dt > 0.0
+        rec = bench._cpu_record(st, dt, 2)
+        assert rec["kind"] == st.kind and rec["scale_factor"] == 384.0 and rec["sample_rows"] == 1
+        assert rec["value"] == round(bench.CFG["chunk"] * 2 / (dt * 384.0), 5)
+        assert rec["cores"] >= 1 and "scaled x384" in rec["sample"]
+
+
 def _rank_main(rank, world, port, q):
     import torch
     import torch.distributed as dist
