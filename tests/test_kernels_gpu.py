@@ -64,6 +64,32 @@ def test_upsert_integer_coordinates_entry():
     assert np.array_equal(ids, VoxelTable(0.05).upsert(ijk))
 
 
+def test_empty_and_fully_masked_inputs_are_no_ops():
+    """Zero points, zero tokens, all-masked points, tokens without a valid voxel, an empty query:
+    every entry point returns cleanly and leaves the state untouched."""
+    from stac_b200.stac.merger import VoxelKVMerger
+    t_gpu, st = _table()
+    assert t_gpu.upsert_points(torch.zeros((0, 3))).numel() == 0
+    assert t_gpu.upsert(torch.zeros((0, 3), dtype=torch.int32)).numel() == 0
+    ids = t_gpu.upsert_points(torch.rand(50, 3), torch.zeros(50, dtype=torch.bool))
+    assert (ids.cpu().numpy() == -1).all() and t_gpu.get_voxel_num() == 0
+    _, cnt = t_gpu.neighbor_ids(torch.zeros(0, dtype=torch.int32, device=DEV), 2)
+    assert int(cnt.item()) == 0
+    g = VoxelKVMerger(2, 64, init_voxels=8, pivot_cap=4, budget_cap=8, sim_thresh=0.8, replace_thresh=0.8,
+                      score_thresh=0.2, dtype=torch.bfloat16, device=DEV, status=st)
+    z = torch.zeros((2, 0, 64), dtype=torch.bfloat16, device=DEV)
+    assert g.insert_and_merge(z, z, torch.zeros((2, 0), device=DEV), None,
+                              torch.zeros((2, 0), dtype=torch.int32, device=DEV), 0) == {}
+    k = torch.randn((2, 10, 64), device=DEV).to(torch.bfloat16)
+    g.insert_and_merge(k, k, torch.rand((2, 10), device=DEV), None,
+                       torch.full((2, 10), -1, dtype=torch.int32, device=DEV), 4)
+    info = g.info()
+    assert info["buffer_pool_used"] == 0 and info["pivot_pool_used"] == 0
+    K, V, M, B = g.retrieve(torch.zeros(0, dtype=torch.int64), True, 16)
+    assert K.shape == (2, 16, 64) and not bool(M.any()) and bool(torch.isinf(B).all())
+    st.raise_if_set("empty inputs")
+
+
 def test_upsert_of_a_long_chunk_sorts_its_new_keys_outside_shared_memory():
     """More new voxels in one call than the in-CTA sort holds (16 384): 40 frames of 1041 points
     on unseen ground, then a second call that mixes known and new voxels."""
