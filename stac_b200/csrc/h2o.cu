@@ -65,7 +65,8 @@ __device__ __forceinline__ int block_scan_1024(int v, int* warp_sums, int* total
 // One CTA per (layer, head) row.  Positions flagged in `is_base` (pinned and recent tokens)
 // are always kept; of the others the `k` highest scores are kept (ties: lower position
 // first).  Emits the kept positions and the dropped positions, both ascending.
-__global__ void __launch_bounds__(1024, 1)
+// (two CTAs per SM: 384 rows run in two waves instead of three)
+__global__ void __launch_bounds__(1024, 2)
 h2o_select_kernel(const float* __restrict__ scores, long long row_stride, const unsigned char* __restrict__ is_base,
                   int T, int n_keep, int* __restrict__ keep_idx, int* __restrict__ drop_idx) {
   extern __shared__ unsigned int keys[];
@@ -76,7 +77,22 @@ h2o_select_kernel(const float* __restrict__ scores, long long row_stride, const 
   __shared__ int sh_remaining;
   const int row = blockIdx.x;
   const float* srow = scores + row * row_stride;
-  for (int t = threadIdx.x; t < T; t += blockDim.x) keys[t] = is_base[t] ? 0xFFFFFFFFu : float_key(srow[t]);
+  // four independent loads per thread in flight
+  for (int base = 0; base < T; base += 4 * 1024) {
+    float sc[4];
+    unsigned char bs[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = base + j * 1024 + static_cast<int>(threadIdx.x);
+      sc[j] = t < T ? srow[t] : 0.f;
+      bs[j] = t < T ? is_base[t] : static_cast<unsigned char>(0);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = base + j * 1024 + static_cast<int>(threadIdx.x);
+      if (t < T) keys[t] = bs[j] ? 0xFFFFFFFFu : float_key(sc[j]);
+    }
+  }
   if (threadIdx.x == 0) {
     sh_prefix = 0;
     sh_remaining = n_keep;
@@ -90,7 +106,13 @@ h2o_select_kernel(const float* __restrict__ scores, long long row_stride, const 
     const unsigned int hi_mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
     for (int t = threadIdx.x; t < T; t += blockDim.x) {
       const unsigned int k = keys[t];
-      if ((k & hi_mask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+      if ((k & hi_mask) == prefix) {
+        // scores of one row share their exponent: most keys fall into a few bins of the upper
+        // digits, so a counter is bumped once per warp and distinct digit, not once per lane
+        const unsigned int bin = (k >> shift) & 255u;
+        const unsigned int peers = __match_any_sync(__activemask(), bin);
+        if ((peers & ((1u << (threadIdx.x & 31)) - 1u)) == 0u) atomicAdd(&hist[bin], __popc(peers));
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -116,25 +138,45 @@ h2o_select_kernel(const float* __restrict__ scores, long long row_stride, const 
   __syncthreads();
   int* krow = keep_idx + static_cast<long long>(row) * n_keep;
   int* drow = drop_idx + static_cast<long long>(row) * (T - n_keep);
-  for (int base = 0; base < T; base += blockDim.x) {
-    const int t = base + threadIdx.x;
-    const bool in = t < T;
-    const unsigned int k = in ? keys[t] : 0u;
-    const int eq = (in && k == tau) ? 1 : 0;
-    const int eq_rank = eq_carry + block_scan_1024(eq, warp_sums, &sh_total);
+  // four consecutive positions per thread: two block scans per 4096 positions
+  for (int base = 0; base < T; base += 4096) {
+    const int t0 = base + static_cast<int>(threadIdx.x) * 4;
+    unsigned int k[4];
+    int eq[4], keep[4];
+    int n_eq = 0, n_keep_here = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool in = t0 + j < T;
+      k[j] = in ? keys[t0 + j] : 0u;
+      eq[j] = (in && k[j] == tau) ? 1 : 0;
+      n_eq += eq[j];
+    }
+    int eq_rank = eq_carry + block_scan_1024(n_eq, warp_sums, &sh_total);
     const int eq_total = sh_total;
-    const int keep = (in && (k > tau || (eq && eq_rank < need_eq))) ? 1 : 0;
-    const int keep_rank = keep_carry + block_scan_1024(keep, warp_sums, &sh_total);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool in = t0 + j < T;
+      keep[j] = (in && (k[j] > tau || (eq[j] && eq_rank < need_eq))) ? 1 : 0;
+      eq_rank += eq[j];
+      n_keep_here += keep[j];
+    }
+    int keep_rank = keep_carry + block_scan_1024(n_keep_here, warp_sums, &sh_total);
     const int keep_total = sh_total;
-    if (in) {
-      if (keep) krow[keep_rank] = t;
-      else drow[drop_carry + (threadIdx.x - (keep_rank - keep_carry))] = t;
+    // positions before this thread's in the block that are not kept (they are all inside the row
+    // whenever this thread has a position inside it)
+    int drop_rank = drop_carry + (static_cast<int>(threadIdx.x) * 4 - (keep_rank - keep_carry));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (t0 + j < T) {
+        if (keep[j]) krow[keep_rank++] = t0 + j;
+        else drow[drop_rank++] = t0 + j;
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
       eq_carry += eq_total;
       keep_carry += keep_total;
-      drop_carry += min(static_cast<int>(blockDim.x), T - base) - keep_total;
+      drop_carry += min(4096, T - base) - keep_total;
     }
     __syncthreads();
   }
