@@ -444,8 +444,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // item.  An item on a cut is computed in two parts by two CTAs, each with its own row
 // references; the parts (unnormalised accumulator, row sums, references) go to a workspace, each
 // CTA counts its arrival at the cut and the one that arrives second joins the two parts (plain
-// split-softmax algebra, operands in a fixed order: same bits whichever CTA does it).  Barrier phases, the score ring and the K/V rings run on
-// across segments; the query tile, the row references and the partial row sums are double
+// split-softmax algebra, operands in a fixed order: same bits whichever CTA does it).  With at
+// most half as many items as SMs every item is cut in exactly two halves instead.  Barrier
+// phases, the score ring and the K/V rings run on across segments; the query tile, the row references and the partial row sums are double
 // buffered by segment parity, and so are the barriers that several warpgroups arrive on per
 // segment: a warpgroup without a tile in a short first or last segment runs one segment ahead,
 // never two (a CTA's middle segments are whole items of at least kFastMinSplitTiles tiles, far
