@@ -279,6 +279,87 @@ def test_merge_and_retrieve_match_oracle(name):
         np.testing.assert_allclose(Bg.cpu().numpy()[fin], Bo[fin], rtol=1e-5, atol=1e-6)
 
 
+def _full_size_run(steps, seed):
+    """384 pool heads x 8328 evicted tokens per call (the pool-stress shape), bf16: tokens fall on
+    1500 voxels, half of their keys cluster around a per-voxel direction so that similarity
+    merges, full rows, pivot insertion and victim re-merges all happen."""
+    from stac_b200 import ops
+    from stac_b200.stac.merger import VoxelKVMerger
+    H, D, Tn, NV = 384, 64, 8328, 1500
+    st = ops.DeviceStatus(torch.device(DEV))
+    g = VoxelKVMerger(H, D, init_voxels=NV, pivot_cap=4, budget_cap=8, sim_thresh=0.8, replace_thresh=0.8,
+                      score_thresh=0.2, dtype=torch.bfloat16, device=DEV, status=st)
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    dirs = torch.randn((NV, D), generator=gen, device=DEV)
+    n_valid = 0
+    for _ in range(steps):
+        vx = torch.randint(0, NV, (Tn,), generator=gen, device=DEV, dtype=torch.int32)
+        vx[torch.rand(Tn, generator=gen, device=DEV) < 0.03] = -1
+        near = (torch.rand(Tn, generator=gen, device=DEV) < 0.5).view(1, Tn, 1)
+        noise = torch.randn((H, Tn, D), generator=gen, device=DEV)
+        K = torch.where(near, dirs[vx.clamp(min=0).long()].unsqueeze(0) + 0.3 * noise, noise).to(torch.bfloat16)
+        V = torch.randn((H, Tn, D), generator=gen, device=DEV).to(torch.bfloat16)
+        S = torch.rand((H, Tn), generator=gen, device=DEV)
+        g.insert_and_merge(K, V, S, None, vx.view(1, Tn).expand(H, Tn).contiguous(), NV)
+        n_valid += H * int((vx >= 0).sum())
+        del K, V, S, noise
+    st.raise_if_set("full-size merge")
+    return g, n_valid
+
+
+def test_full_size_voxel_memory_properties():
+    """Properties that do not depend on the size, checked at the pool-stress size: no segment is
+    handed out twice, rows stay inside their caps, buffered scores of a row are stored in rank
+    order, no token is counted twice, retrieval returns distinct pivots in weight order, and
+    a second run of the same stream ends in the same bits."""
+    g, n_valid = _full_size_run(6, seed=7)
+    H, P, B = g.H, g.P, g.B
+    pc, bc = g._piv_row_cnt.long(), g._buf_row_cnt.long()
+    assert int(pc.min()) >= 0 and int(pc.max()) <= P and int(bc.min()) >= 0 and int(bc.max()) <= B
+    info = g.info()
+    for cnt, seg, used in ((pc, g._piv_row_seg, info["pivot_pool_used"]), (bc, g._buf_row_seg, info["buffer_pool_used"])):
+        live = torch.arange(seg.shape[2], device=DEV).view(1, 1, -1) < cnt.unsqueeze(-1)
+        ids = seg[live]
+        assert int(ids.numel()) == used and int(ids.min()) >= 0
+        assert int(torch.unique(ids).numel()) == used            # every live segment belongs to one (row, column)
+    assert int(pc.sum()) > 100000 and int((pc == P).sum()) > 0   # pivots formed, some rows saturated
+    # buffered scores of a row: descending with the column
+    sc = g._buf_S[g._buf_row_seg.clamp(min=0).long()]
+    col = torch.arange(B, device=DEV).view(1, 1, B)
+    both = (col[..., 1:] < bc.unsqueeze(-1))
+    assert bool(((sc[..., :-1] >= sc[..., 1:]) | ~both).all())
+    # tokens: pivots count what they absorbed, the rest is buffered, carried over or fell to the score gate
+    live_p = torch.arange(P, device=DEV).view(1, 1, P) < pc.unsqueeze(-1)
+    absorbed = float(g._piv_C[g._piv_row_seg[live_p].long()].double().sum())
+    assert absorbed + info["buffer_pool_used"] <= n_valid and absorbed > 0.1 * n_valid
+    # retrieval around every voxel: distinct pivots, weights descending, as many as there are (up to R)
+    R = 2048
+    K, V, M, Bz, I = g.retrieve(None, True, R, want_idx=True)
+    n_piv = pc.sum(dim=1)
+    assert torch.equal(M.sum(dim=1), torch.clamp(n_piv, max=R))
+    w = g._piv_W[g._piv_row_seg[torch.arange(H, device=DEV).view(H, 1), I[..., 0].clamp(min=0).long(),
+                                I[..., 1].clamp(min=0).long()].clamp(min=0).long()]
+    ok = M[:, 1:] & M[:, :-1]
+    assert bool(((w[:, :-1] >= w[:, 1:]) | ~ok).all())
+    flat = (I[..., 0].long() * P + I[..., 1].long())
+    for h in (0, 191, 383):
+        sel = flat[h][M[h]]
+        assert int(torch.unique(sel).numel()) == int(sel.numel())
+    cnt_sel = g._piv_C[g._piv_row_seg[torch.arange(H, device=DEV).view(H, 1), I[..., 0].clamp(min=0).long(),
+                                      I[..., 1].clamp(min=0).long()].clamp(min=0).long()]
+    assert torch.allclose(Bz[M], torch.log(cnt_sel[M].clamp(min=1e-9)), rtol=1e-6, atol=1e-6)
+    assert bool(torch.isinf(Bz[~M]).all())
+    # same stream again: same bits
+    g2, _ = _full_size_run(6, seed=7)
+    for name in ("_piv_row_cnt", "_piv_row_seg", "_buf_row_cnt", "_buf_row_seg"):
+        assert torch.equal(getattr(g, name), getattr(g2, name)), name
+    n_p, n_b = info["pivot_pool_used"], info["buffer_pool_used"]
+    for name in ("_piv_K", "_piv_V", "_piv_W", "_piv_S", "_piv_C"):
+        a, b = getattr(g, name), getattr(g2, name)
+        assert torch.equal(a[g._piv_row_seg[live_p].long()], b[g2._piv_row_seg[live_p].long()]), name
+    del g2
+
+
 def test_merge_is_deterministic():
     """Two pools fed the same stream end in bit-identical state (no atomics on values or slots)."""
     from stac_b200.stac.merger import VoxelKVMerger
