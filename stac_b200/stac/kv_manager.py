@@ -98,8 +98,17 @@ class KVManager:
                 continue
             tok.extend(range(idx * self.token_per_f, (idx + 1) * self.token_per_f))
         self._pinned_token_index = torch.tensor(tok, dtype=torch.long)
+        # The kernels compute and store in bfloat16.  float16 (the bare default of the reference's
+        # StreamSession.register_kv_mgr, stream_session.py:580) is accepted for drop-in use: keys,
+        # values and queries are converted at this boundary and outputs come back as float16.
+        self.io_dtype = dtype
+        if dtype == torch.float16:
+            import warnings
+            warnings.warn("stac_b200: dtype=float16 requested; the sm_100a kernels compute in bfloat16, tensors are "
+                          "converted at the manager boundary", stacklevel=2)
+            dtype = torch.bfloat16
         if dtype not in (torch.bfloat16,):
-            raise ValueError("the sm_100a path computes in bfloat16; pass dtype=torch.bfloat16")
+            raise ValueError("the sm_100a path computes in bfloat16; pass dtype=torch.bfloat16 (float16 is converted)")
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else torch.device("cuda")
         if self.device.type != "cuda":
@@ -276,7 +285,11 @@ class KVManager:
         H, D = self.num_heads, self.head_dim
         if D != 64:
             raise ValueError("the fused epilogue supports head_dim 64")
-        assert qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.shape[0] == 1, "qkv: [1, T, 3*H*D] bf16 on the GPU"
+        assert qkv.is_cuda and qkv.shape[0] == 1, "qkv: [1, T, 3*H*D] on the GPU"
+        out_dtype = qkv.dtype
+        if qkv.dtype != torch.bfloat16:
+            assert qkv.dtype == self.io_dtype, "qkv must be bf16 (or the float16 the manager was created with)"
+            qkv = qkv.to(torch.bfloat16)
         T_new = qkv.shape[1]
         x = qkv.reshape(T_new, 3 * H * D)
         if x.stride(1) != 1 or x.data_ptr() % 4:
@@ -318,7 +331,7 @@ class KVManager:
         if slot == self._L_eff - 1:
             self._processed_frames += T_new // self.token_per_f
         self._offset_hot[slot] = old_T + T_new
-        return q_out
+        return q_out if out_dtype == torch.bfloat16 else q_out.to(out_dtype)
 
     @torch.no_grad()
     def prefill(self, query_states, key_states, value_states, layer_idx: int):
@@ -344,7 +357,10 @@ class KVManager:
         assert H == self.num_heads and D == self.head_dim, "Incompatible head or head_dim."
         assert B == 1, "Batch size > 1 not supported in decode_sparse_attn()."
         assert query_states.is_cuda, "decode_sparse_attn requires CUDA tensors"
-        assert query_states.dtype == torch.bfloat16, "q must be bf16"
+        out_dtype = query_states.dtype
+        if out_dtype != torch.bfloat16:
+            assert out_dtype == self.io_dtype, "q must be bf16 (or the float16 the manager was created with)"
+            query_states = query_states.to(torch.bfloat16)
         q = query_states[0]
         if q.stride(2) != 1 or q.stride(1) != D:
             q = q.contiguous()
@@ -352,7 +368,8 @@ class KVManager:
         out, _, colsum = ops.attn_colsum(q, self.key_cache_hot[slot], self.value_cache_hot[slot], T_main,
                                          k_ret, v_ret, bias_ret, T_ret, subsample_ratio=subsample_ratio,
                                          want_colsum=want_colsum, status=self._status)
-        return out.unsqueeze(0), colsum
+        out = out.unsqueeze(0)
+        return (out if out_dtype == torch.bfloat16 else out.to(out_dtype)), colsum
 
     @torch.no_grad()
     def decode_sparse_attn(self, query_states: torch.Tensor, layer_idx: int) -> torch.Tensor:

@@ -127,6 +127,35 @@ def test_attention_drives_scores():
     kv.free()
 
 
+def test_float16_is_converted_at_the_manager_boundary():
+    """dtype=float16 (the bare default of the reference's register_kv_mgr) is accepted: the cache
+    and the kernels are bf16, keys / values / queries are converted on the way in and the output
+    comes back as float16, equal to the bf16 manager's output on the same (bf16-representable) inputs."""
+    from stac_b200.stac import HeavyHittersKV
+    L, H, D, tpf = 1, 2, 64, 16
+    common = dict(num_layers=L, num_heads=H, head_dim=D, token_per_frame=tpf, chunk_size=1, recent_size=2,
+                  pinned_idx=[0], device=torch.device(DEV), buffer_size=5, hh_size=1, temperature=0.9)
+    with pytest.warns(UserWarning, match="float16"):
+        a = HeavyHittersKV(dtype=torch.float16, **common)
+    b = HeavyHittersKV(dtype=torch.bfloat16, **common)
+    a.reset()
+    b.reset()
+    g = torch.Generator().manual_seed(4)
+    for _ in range(3):
+        k = (torch.randn(1, H, tpf, D, generator=g) / 2).to(torch.bfloat16)
+        v = torch.randn(1, H, tpf, D, generator=g).to(torch.bfloat16)
+        q = (torch.randn(1, tpf, H, D, generator=g) / 2).to(torch.bfloat16)
+        a.append_kv(k.to(torch.float16).to(DEV), v.to(torch.float16).to(DEV), 0)
+        b.append_kv(k.to(DEV), v.to(DEV), 0)
+        oa = a.decode_sparse_attn(q.to(torch.float16).to(DEV), 0)
+        ob = b.decode_sparse_attn(q.to(DEV), 0)
+        assert oa.dtype == torch.float16 and ob.dtype == torch.bfloat16
+        assert torch.allclose(oa.float(), ob.float(), rtol=0, atol=1e-6)   # bf16 -> fp16 is exact above 2^-14
+    assert torch.equal(a.get_scores()[0], b.get_scores()[0])
+    with pytest.raises(ValueError):
+        HeavyHittersKV(dtype=torch.float32, **common)
+
+
 def test_window_manager_and_h2o_manager():
     """KVManager (recent + pinned) and HeavyHittersKV (no voxel memory) prune like the oracle."""
     from oracle.manager import h2o_keep_indices
