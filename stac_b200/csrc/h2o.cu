@@ -232,15 +232,34 @@ __global__ void append_kv_kernel(const uint4* __restrict__ k, const uint4* __res
                                  long long idx_head_stride, int T_new, int old_T, long long first_id,
                                  int vec_per_token) {
   grid_dep_wait();   // launched with programmatic serialization: whatever produced k and v is complete now
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int h = blockIdx.y;
-  const long long t = gid / vec_per_token;
-  const int part = static_cast<int>(gid % vec_per_token);
-  if (t >= T_new) return;
-  const long long dst = h * cache_head_stride_vec + (old_T + t) * vec_per_token + part;
-  k_cache[dst] = k[h * k_head_stride_vec + t * k_row_stride_vec + part];
-  v_cache[dst] = v[h * v_head_stride_vec + t * v_row_stride_vec + part];
-  if (part == 0) token_idx[h * idx_head_stride + old_T + t] = first_id + t;
+  const long long total = static_cast<long long>(T_new) * vec_per_token;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long g0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // four 16-byte vectors of K and of V per thread, all loads before the stores
+  uint4 kv[4], vv[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const long long gid = g0 + j * stride;
+    if (gid < total) {
+      const long long t = gid / vec_per_token;
+      const int part = static_cast<int>(gid - t * vec_per_token);
+      kv[j] = k[h * k_head_stride_vec + t * k_row_stride_vec + part];
+      vv[j] = v[h * v_head_stride_vec + t * v_row_stride_vec + part];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const long long gid = g0 + j * stride;
+    if (gid < total) {
+      const long long t = gid / vec_per_token;
+      const int part = static_cast<int>(gid - t * vec_per_token);
+      const long long dst = h * cache_head_stride_vec + (old_T + t) * vec_per_token + part;
+      k_cache[dst] = kv[j];
+      v_cache[dst] = vv[j];
+      if (part == 0) token_idx[h * idx_head_stride + old_T + t] = first_id + t;
+    }
+  }
 }
 
 // The epilogue of the attention layer's QKV projection fused with append_kv
@@ -358,7 +377,7 @@ int stac_append_kv(const void* k, const void* v, int64_t k_head_stride, int64_t 
   if (T_new == 0) return STAC_OK;
   const int vpt = token_bytes / 16;
   const long long total = static_cast<long long>(T_new) * vpt;
-  dim3 grid(static_cast<unsigned>((total + 255) / 256), H);
+  dim3 grid(static_cast<unsigned>((total + 4 * 256 - 1) / (4 * 256)), H);   // four vectors per thread
   if (stac::launch_behind(stac::append_kv_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       static_cast<const uint4*>(k), static_cast<const uint4*>(v), k_head_stride / epv, k_row_stride / epv,
       v_head_stride / epv, v_row_stride / epv, static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache),
