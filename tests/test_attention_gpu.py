@@ -232,6 +232,41 @@ def test_leading_masked_tile_then_faint_keys():
     _assert_close((out.float().cpu().numpy(), lse.cpu().numpy(), cs.cpu().numpy()), (o_ref, lse_ref, cs_ref))
 
 
+def test_calls_replay_from_a_cuda_graph():
+    """The entry point neither allocates nor synchronises, so calls can be captured into a CUDA
+    graph (the programmatic-serialization edges between its kernels included); a replay gives the
+    bits of the eager call."""
+    from stac_b200 import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(12)
+    M, H, T_hot, T_ret, D = 700, 4, 2000, 150, 64
+    q = (torch.randn(M, H, D, generator=g) / 2).to(torch.bfloat16).to(dev)
+    kh = (torch.randn(H, T_hot, D, generator=g) / 2).to(torch.bfloat16).to(dev)
+    vh = torch.randn(H, T_hot, D, generator=g).to(torch.bfloat16).to(dev)
+    kr = (torch.randn(H, T_ret, D, generator=g) / 2).to(torch.bfloat16).to(dev)
+    vr = torch.randn(H, T_ret, D, generator=g).to(torch.bfloat16).to(dev)
+    bias = torch.log(torch.randint(1, 9, (H, T_ret), generator=g).float()).to(dev)
+    status = ops.DeviceStatus(dev)
+
+    def call():
+        return ops.attn_colsum(q, kh, vh, T_hot, kr, vr, bias, T_ret, want_lse=True, status=status)
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        eager = [t.clone() for t in call()]          # also sizes the workspace of this stream
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            first = call()
+            second = call()
+        for t in first + second:
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+    status.raise_if_set("graph replay")
+    for a, b, c in zip(eager, first, second):
+        assert torch.equal(a, b) and torch.equal(a, c)
+
+
 def test_bounded_wait_reports_and_returns():
     """A wait on a barrier nothing completes runs out, sets the status word and the kernel
     returns; the context stays usable."""
