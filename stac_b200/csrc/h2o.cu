@@ -69,6 +69,7 @@ __device__ __forceinline__ int block_scan_1024(int v, int* warp_sums, int* total
 __global__ void __launch_bounds__(1024, 2)
 h2o_select_kernel(const float* __restrict__ scores, long long row_stride, const unsigned char* __restrict__ is_base,
                   int T, int n_keep, int* __restrict__ keep_idx, int* __restrict__ drop_idx) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   extern __shared__ unsigned int keys[];
   __shared__ int hist[256];
   __shared__ int warp_sums[32];
@@ -188,6 +189,7 @@ h2o_select_kernel(const float* __restrict__ scores, long long row_stride, const 
 __global__ void compact_kv_kernel(const int* __restrict__ keep_idx, int n_keep, const uint4* __restrict__ k_src,
                                   const uint4* __restrict__ v_src, uint4* __restrict__ k_dst,
                                   uint4* __restrict__ v_dst, long long row_stride_vec, int vec_per_token) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int row = blockIdx.y;
   const long long tok = gid / vec_per_token;
@@ -205,6 +207,7 @@ __global__ void compact_meta_kernel(const int* __restrict__ keep_idx, int n_keep
                                     const float* __restrict__ s_src, float* __restrict__ s_dst,
                                     const float* __restrict__ c_src, float* __restrict__ c_dst,
                                     const int* __restrict__ vx_src, int* __restrict__ vx_dst) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int row = blockIdx.y;
   if (j >= T_buf) return;
@@ -417,8 +420,9 @@ int stac_h2o_select(const float* scores, int64_t row_stride, int n_rows, const u
       return STAC_ERR_CUDA;
     attr_done.mark(dev);
   }
-  stac::h2o_select_kernel<<<n_rows, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      scores, row_stride, is_base, T, n_keep, keep_idx, drop_idx);
+  if (stac::launch_behind(stac::h2o_select_kernel, dim3(n_rows), dim3(1024), smem, reinterpret_cast<cudaStream_t>(stream),
+                          scores, row_stride, is_base, T, n_keep, keep_idx, drop_idx) != cudaSuccess)
+    return STAC_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 
@@ -438,16 +442,17 @@ int stac_compact(const int* keep_idx, int n_rows, int n_keep, int T_buf, int hea
   if (n_keep > 0) {
     const long long total = static_cast<long long>(n_keep) * vpt;
     dim3 grid(static_cast<unsigned>((total + 255) / 256), n_rows);
-    stac::compact_kv_kernel<<<grid, 256, 0, st>>>(keep_idx, n_keep, static_cast<const uint4*>(k_src),
-                                                 static_cast<const uint4*>(v_src), static_cast<uint4*>(k_dst),
-                                                 static_cast<uint4*>(v_dst),
-                                                 static_cast<long long>(T_buf) * vpt, vpt);
+    if (stac::launch_behind(stac::compact_kv_kernel, grid, dim3(256), 0, st, keep_idx, n_keep,
+                            static_cast<const uint4*>(k_src), static_cast<const uint4*>(v_src),
+                            static_cast<uint4*>(k_dst), static_cast<uint4*>(v_dst),
+                            static_cast<long long>(T_buf) * vpt, vpt) != cudaSuccess)
+      return STAC_ERR_CUDA;
   }
   dim3 grid_m((T_buf + 255) / 256, n_rows);
-  stac::compact_meta_kernel<<<grid_m, 256, 0, st>>>(keep_idx, n_keep, T_buf,
-                                                   reinterpret_cast<const long long*>(ti_src),
-                                                   reinterpret_cast<long long*>(ti_dst), s_src, s_dst, c_src, c_dst,
-                                                   vx_src, vx_dst);
+  if (stac::launch_behind(stac::compact_meta_kernel, grid_m, dim3(256), 0, st, keep_idx, n_keep, T_buf,
+                          reinterpret_cast<const long long*>(ti_src), reinterpret_cast<long long*>(ti_dst), s_src,
+                          s_dst, c_src, c_dst, vx_src, vx_dst) != cudaSuccess)
+    return STAC_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 

@@ -172,6 +172,7 @@ __device__ __forceinline__ int block_scan(int v, int* warp_sums, int* total) {
 
 // ------------------------------------------------------------------------------------ sort
 __global__ void __launch_bounds__(1024, 2) sort_tokens_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   __shared__ int hist[256 * 32];  // [digit][warp]
   __shared__ int warp_sums[32];
   __shared__ int sh_total;
@@ -467,6 +468,7 @@ __device__ __forceinline__ float token_score(const MergeParams& p, int h, int co
 // reference's vectorised code does.
 template <typename T>
 __global__ void __launch_bounds__(256) tokens_sim_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int h = blockIdx.y;
   if (p.plan[kPlanAnyValid] == 0) return;
   const int lane = threadIdx.x & 31, sub = threadIdx.x & 7;
@@ -539,6 +541,7 @@ __global__ void __launch_bounds__(256) tokens_sim_kernel(const MergeParams p) {
 // scores, C += count; the result is stored in the pool dtype (stac/merger.py:660-760).
 template <typename T, int EPL>
 __global__ void __launch_bounds__(256) rows_merge_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   if (p.plan[kPlanAnyValid] == 0) return;
@@ -714,6 +717,7 @@ __device__ __forceinline__ void rank_row_warp(const MergeParams& p, const int h,
 // The same for short rows, one thread per row; rows with more than 32 tokens are queued for the
 // warp-per-row kernel.
 __global__ void __launch_bounds__(256) rows_rank_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int h = blockIdx.y;
   const int ri = blockIdx.x * blockDim.x + threadIdx.x;
   if (p.plan[kPlanAnyValid] == 0) return;
@@ -780,6 +784,7 @@ __global__ void __launch_bounds__(256) rows_rank_kernel(const MergeParams p) {
 }
 
 __global__ void __launch_bounds__(256) rows_rank_long_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int n = p.plan[kPlanDeferCount];
@@ -792,6 +797,7 @@ __global__ void __launch_bounds__(256) rows_rank_long_kernel(const MergeParams p
 // ------------------------------------------------------------------------------------ scans
 // pass 0 always runs; pass 1 only when pass 0 found the pools too small and rows were trimmed
 __global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p, const int pass) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   __shared__ int warp_sums[32];
   __shared__ int sh_total;
   __shared__ int carry[4];
@@ -826,6 +832,7 @@ __global__ void __launch_bounds__(1024, 1) scan_heads_kernel(const MergeParams p
 }
 
 __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p, const int pass) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   __shared__ int warp_sums[32];
   __shared__ int sh_total;
   __shared__ int carry[4];
@@ -906,6 +913,7 @@ __global__ void __launch_bounds__(1024, 1) scan_plan_kernel(const MergeParams p,
 // was).  The cut follows the allocation order, i.e. (head, voxel) ascending, so it is
 // deterministic; merges into existing pivots done in phase A stay.
 __global__ void __launch_bounds__(256) trim_rows_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int h = blockIdx.y;
   const int ri = blockIdx.x * blockDim.x + threadIdx.x;
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanShort] == 0) return;
@@ -934,6 +942,7 @@ __global__ void __launch_bounds__(256) trim_rows_kernel(const MergeParams p) {
 // (row, column) order from the allocation plan, publish the new occupancy, and queue the rows
 // whose buffered tokens change column or whose buffer filled up.
 __global__ void __launch_bounds__(256) rows_phase_b1a_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int h = blockIdx.y;
   const int ri = blockIdx.x * blockDim.x + threadIdx.x;
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
@@ -964,6 +973,7 @@ __global__ void __launch_bounds__(256) rows_phase_b1a_kernel(const MergeParams p
 // moves each one into a slot whose old content has already left.
 template <typename T, int EPL>
 __global__ void __launch_bounds__(256) rows_phase_b1m_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
@@ -1030,6 +1040,7 @@ __global__ void __launch_bounds__(256) rows_phase_b1m_kernel(const MergeParams p
 // of V, all four loads in flight before the stores.
 template <typename T>
 __global__ void __launch_bounds__(256) tokens_place_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   constexpr int kVec = static_cast<int>(sizeof(T)) * 8 / 16;   // 16-byte vectors per lane and row
   const int h = blockIdx.y;
   const int sub = threadIdx.x & 7;
@@ -1086,6 +1097,7 @@ template <typename T>
 // (holding all eight key rows of a row in registers, at four CTAs per SM, measured 15 % slower for
 // the whole merge than streaming them at eight CTAs per SM: these per-row kernels want threads)
 __global__ void __launch_bounds__(128, 8) rows_phase_b2_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   const int lane = threadIdx.x & 31, sub = threadIdx.x & 7;
   const int gbase = lane & 24;                       // first lane of this group
   const unsigned gmask = 0xffu << gbase;
@@ -1280,6 +1292,7 @@ __global__ void __launch_bounds__(128, 8) rows_phase_b2_kernel(const MergeParams
 
 // Freed ids are appended after the part of the free list that was not handed out.
 __global__ void finalize_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   if (p.plan[kPlanAnyValid] == 0 || p.plan[kPlanAbort] != 0) return;
   const int n_freed = p.plan[kPlanTotalFull] * p.B;
   const int base = p.plan[kPlanFreeLen] - p.plan[kPlanK];
@@ -1291,6 +1304,7 @@ __global__ void finalize_kernel(const MergeParams p) {
 // carried overflow (stac/merger.py:1203-1208), so the list is carried over unchanged.
 template <typename T>
 __global__ void carry_overflow_kernel(const MergeParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel of the call
   if (p.plan[kPlanAnyValid] != 0 && p.plan[kPlanAbort] == 0) return;
   const int n = p.over_start_in[p.heads];
   const long long total = static_cast<long long>(n) * p.D;
@@ -1342,26 +1356,26 @@ template <typename T>
 int launch_merge(MergeParams& mp, cudaStream_t st) {
   if (cudaMemsetAsync(mp.plan, 0, kPlanSize * 4, st) != cudaSuccess) return STAC_ERR_CUDA;
   if (cudaMemsetAsync(mp.row_flag, 0, static_cast<size_t>(mp.heads) * mp.ncap * 4, st) != cudaSuccess) return STAC_ERR_CUDA;
-  sort_tokens_kernel<<<mp.heads, 1024, 0, st>>>(mp);
+  if (launch_behind(sort_tokens_kernel, dim3(mp.heads), dim3(1024), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
   const int warps = 8;
   dim3 grid_rows((mp.ncap + warps - 1) / warps, mp.heads);
   dim3 grid_a1((mp.ncap + 255) / 256, mp.heads);
   dim3 grid_sim(static_cast<unsigned>((static_cast<long long>(mp.ncap) * 8 + 255) / 256), mp.heads);
-  tokens_sim_kernel<T><<<grid_sim, 256, 0, st>>>(mp);
-  rows_merge_kernel<T, 2><<<148 * 4, 256, 0, st>>>(mp);
-  rows_rank_kernel<<<grid_a1, 256, 0, st>>>(mp);
-  rows_rank_long_kernel<<<148 * 4, 256, 0, st>>>(mp);
-  scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp, 0);
-  scan_plan_kernel<<<1, 1024, 0, st>>>(mp, 0);
-  trim_rows_kernel<<<grid_a1, 256, 0, st>>>(mp);
-  scan_heads_kernel<<<mp.heads, 1024, 0, st>>>(mp, 1);
-  scan_plan_kernel<<<1, 1024, 0, st>>>(mp, 1);
-  rows_phase_b1a_kernel<<<grid_a1, 256, 0, st>>>(mp);
-  rows_phase_b1m_kernel<T, 2><<<148 * 6, 256, 0, st>>>(mp);
-  tokens_place_kernel<T><<<grid_sim, 256, 0, st>>>(mp);
-  rows_phase_b2_kernel<T><<<148 * 16, 128, 0, st>>>(mp);
-  finalize_kernel<<<148 * 4, 256, 0, st>>>(mp);   // grid-stride over the freed ids (known on the device only)
-  carry_overflow_kernel<T><<<148, 256, 0, st>>>(mp);
+  if (launch_behind(tokens_sim_kernel<T>, dim3(grid_sim), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(rows_merge_kernel<T, 2>, dim3(148 * 4), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(rows_rank_kernel, dim3(grid_a1), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(rows_rank_long_kernel, dim3(148 * 4), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(scan_heads_kernel, dim3(mp.heads), dim3(1024), 0, st, mp, 0) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(scan_plan_kernel, dim3(1), dim3(1024), 0, st, mp, 0) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(trim_rows_kernel, dim3(grid_a1), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(scan_heads_kernel, dim3(mp.heads), dim3(1024), 0, st, mp, 1) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(scan_plan_kernel, dim3(1), dim3(1024), 0, st, mp, 1) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(rows_phase_b1a_kernel, dim3(grid_a1), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(rows_phase_b1m_kernel<T, 2>, dim3(148 * 6), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(tokens_place_kernel<T>, dim3(grid_sim), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(rows_phase_b2_kernel<T>, dim3(148 * 16), dim3(128), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
+  if (launch_behind(finalize_kernel, dim3(148 * 4), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;   // grid-stride over the freed ids (known on the device only)
+  if (launch_behind(carry_overflow_kernel<T>, dim3(148), dim3(256), 0, st, mp) != cudaSuccess) return STAC_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 

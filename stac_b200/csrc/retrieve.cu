@@ -129,6 +129,7 @@ __device__ __forceinline__ int list_push(int* counter) {
 // first digit, i.e. two passes.  Only when more than kSelCap - R candidates share one exact
 // weight is the last group taken in candidate order by an ordered pass.
 __global__ void __launch_bounds__(kSelThreads, 3) retrieve_select_kernel(const RetrieveParams p) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   // kSelCap keys; the digit counters live in the same 64 KB (they are dead once the threshold is
   // known and the keys are collected), so three CTAs fit one SM and 384 heads run in one wave
   extern __shared__ unsigned long long cand[];
@@ -283,6 +284,7 @@ __global__ void __launch_bounds__(kSelThreads, 3) retrieve_select_kernel(const R
 }
 
 __global__ void retrieve_gather_kernel(const RetrieveParams p, int vec_per_token) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int h = blockIdx.y;
   const long long tok = gid / vec_per_token;
@@ -343,11 +345,12 @@ int stac_retrieve(const stac_pool* pool, const int* query_ids, const int* query_
       return STAC_ERR_CUDA;
     attr_done.mark(dev);
   }
-  stac::retrieve_select_kernel<<<pool->heads, stac::kSelThreads, smem, st>>>(rp);
+  if (stac::launch_behind(stac::retrieve_select_kernel, dim3(pool->heads), dim3(stac::kSelThreads), smem, st, rp) != cudaSuccess)
+    return STAC_ERR_CUDA;
   const int vpt = token_bytes / 16;
   const long long total = static_cast<long long>(retrieve_size) * vpt;
   dim3 grid(static_cast<unsigned>((total + 255) / 256), pool->heads);
-  stac::retrieve_gather_kernel<<<grid, 256, 0, st>>>(rp, vpt);
+  if (stac::launch_behind(stac::retrieve_gather_kernel, grid, dim3(256), 0, st, rp, vpt) != cudaSuccess) return STAC_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 

@@ -57,6 +57,7 @@ __global__ void quantize_lookup_kernel(const float* __restrict__ pts, const int*
                                        const int* __restrict__ hv, int hcap, long long* __restrict__ pt_keys,
                                        int* __restrict__ ids, long long* __restrict__ new_keys,
                                        int* __restrict__ new_cnt) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   if (mask != nullptr && mask[i] == 0) {
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(1024, 1)
 insert_new_kernel(long long* new_keys, const int* __restrict__ new_cnt,
                   long long* __restrict__ table_keys, int table_cap, unsigned long long* __restrict__ hk,
                   int* __restrict__ hv, int hcap, int* __restrict__ n_voxels, int* err) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   extern __shared__ unsigned long long smem_keys[];
   __shared__ int warp_sums[32];
   __shared__ int carry;
@@ -188,6 +190,7 @@ insert_new_kernel(long long* new_keys, const int* __restrict__ new_cnt,
 __global__ void resolve_pending_kernel(const long long* __restrict__ pt_keys, int n,
                                        const unsigned long long* __restrict__ hk, const int* __restrict__ hv,
                                        int hcap, int* __restrict__ ids) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   if (ids[i] == -2) ids[i] = hash_lookup(hk, hv, hcap, pt_keys[i]);
@@ -198,6 +201,7 @@ __global__ void neighbor_flag_kernel(const int* __restrict__ token_vx, int n_tok
                                      const long long* __restrict__ table_keys, const int* __restrict__ n_voxels,
                                      const unsigned long long* __restrict__ hk, const int* __restrict__ hv, int hcap,
                                      unsigned char* __restrict__ flags) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   const int side = 2 * R + 1;
   const int cube = side * side * side;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -220,6 +224,7 @@ __global__ void neighbor_flag_kernel(const int* __restrict__ token_vx, int n_tok
 __global__ void __launch_bounds__(1024, 1)
 compact_flags_kernel(unsigned char* __restrict__ flags, const int* __restrict__ n_voxels, int all_ids,
                      int* __restrict__ out_ids, int* __restrict__ out_count) {
+  grid_dep_wait();   // launched with programmatic serialization behind the previous kernel in the stream
   __shared__ int warp_sums[32];
   __shared__ int carry;
   const int n = *n_voxels;
@@ -401,10 +406,10 @@ int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* ma
   if (cudaMemsetAsync(new_cnt, 0, sizeof(int), st) != cudaSuccess) return STAC_ERR_CUDA;
   const int threads = 256;
   const int blocks = (n_points + threads - 1) / threads;
-  stac::quantize_lookup_kernel<<<blocks, threads, 0, st>>>(points, ijk, mask, n_points, voxel_size,
-                                                          static_cast<const unsigned long long*>(hash_keys),
-                                                          hash_vals, static_cast<int>(hash_cap), pt_keys, ids_out,
-                                                          new_keys, new_cnt);
+  if (stac::launch_behind(stac::quantize_lookup_kernel, dim3(blocks), dim3(threads), 0, st, points, ijk, mask, n_points,
+                          voxel_size, static_cast<const unsigned long long*>(hash_keys), hash_vals,
+                          static_cast<int>(hash_cap), pt_keys, ids_out, new_keys, new_cnt) != cudaSuccess)
+    return STAC_ERR_CUDA;
   int dev = 0;
   if (stac::current_device(&dev) != STAC_OK) return STAC_ERR_CUDA;
   static stac::PerDeviceFlag attr_done;   // the shared-memory opt-in is made once per device
@@ -415,12 +420,15 @@ int stac_voxel_upsert(const float* points, const int32_t* ijk, const uint8_t* ma
       return STAC_ERR_CUDA;
     attr_done.mark(dev);
   }
-  stac::insert_new_kernel<<<1, 1024, smem, st>>>(new_keys, new_cnt, reinterpret_cast<long long*>(table_keys),
-                                                 table_cap, static_cast<unsigned long long*>(hash_keys), hash_vals,
-                                                 static_cast<int>(hash_cap), n_voxels, dev_status);
-  stac::resolve_pending_kernel<<<blocks, threads, 0, st>>>(pt_keys, n_points,
-                                                          static_cast<const unsigned long long*>(hash_keys),
-                                                          hash_vals, static_cast<int>(hash_cap), ids_out);
+  if (stac::launch_behind(stac::insert_new_kernel, dim3(1), dim3(1024), smem, st, new_keys, new_cnt,
+                          reinterpret_cast<long long*>(table_keys), table_cap,
+                          static_cast<unsigned long long*>(hash_keys), hash_vals, static_cast<int>(hash_cap), n_voxels,
+                          dev_status) != cudaSuccess)
+    return STAC_ERR_CUDA;
+  if (stac::launch_behind(stac::resolve_pending_kernel, dim3(blocks), dim3(threads), 0, st, pt_keys, n_points,
+                          static_cast<const unsigned long long*>(hash_keys), hash_vals, static_cast<int>(hash_cap),
+                          ids_out) != cudaSuccess)
+    return STAC_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 
@@ -442,11 +450,15 @@ int stac_voxel_neighbors(const int* token_voxel_ids, int n_tokens, int radius_ce
     const long long total = static_cast<long long>(n_tokens) * side * side * side;
     const int threads = 256;
     const long long blocks = (total + threads - 1) / threads;
-    stac::neighbor_flag_kernel<<<static_cast<unsigned>(blocks), threads, 0, st>>>(
-        token_voxel_ids, n_tokens, radius_cells, reinterpret_cast<const long long*>(table_keys), n_voxels,
-        static_cast<const unsigned long long*>(hash_keys), hash_vals, static_cast<int>(hash_cap), flags);
+    if (stac::launch_behind(stac::neighbor_flag_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, st,
+                            token_voxel_ids, n_tokens, radius_cells, reinterpret_cast<const long long*>(table_keys),
+                            n_voxels, static_cast<const unsigned long long*>(hash_keys), hash_vals,
+                            static_cast<int>(hash_cap), flags) != cudaSuccess)
+      return STAC_ERR_CUDA;
   }
-  stac::compact_flags_kernel<<<1, 1024, 0, st>>>(flags, n_voxels, all_ids, out_ids, out_count);
+  if (stac::launch_behind(stac::compact_flags_kernel, dim3(1), dim3(1024), 0, st, flags, n_voxels, all_ids, out_ids,
+                          out_count) != cudaSuccess)
+    return STAC_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? STAC_OK : STAC_ERR_CUDA;
 }
 
